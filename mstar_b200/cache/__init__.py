@@ -1,0 +1,4 @@
+"""Paged key/value cache and per-request state slots."""
+from .manager import BatchIndex, CacheExhausted, CacheManager, GroupConfig, NoFreeSlot
+
+__all__ = ["BatchIndex", "CacheExhausted", "CacheManager", "GroupConfig", "NoFreeSlot"]

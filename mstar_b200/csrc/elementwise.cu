@@ -1,0 +1,267 @@
+// Memory-bound kernels of the decoder: embedding gather, fused residual-add +
+// RMSNorm, rotary position encoding fused with the write of keys and values into
+// cache pages, SiLU(gate)*up, row gather, dtype conversion.
+//
+// Formulas follow the reference model: RMSNorm x*rsqrt(mean(x^2)+eps)*w
+// (mstar/model/components/norm.py:45-59, mstar/utils/attention.py:457-474),
+// split-half rotary pairs (mstar/utils/attention.py:224-253), down(silu(gate)*up)
+// (mstar/model/components/distributed/mlp.py:78-81), plain residual adds
+// (mstar/model/components/decoder_layer.py:58-71).  The residual stream is kept in
+// float in both dtypes so that the residual sum is a 32-bit sum.
+#include "common.cuh"
+
+// ---------------------------------------------------------------- embedding
+template <typename W>
+__global__ void embed_rows_kernel(const W* __restrict__ table, const int* __restrict__ ids,
+                                  float* __restrict__ out, int vocab, int hidden) {
+    const int t = blockIdx.x;
+    const int id = ids[t];
+    float* o = out + (size_t)t * hidden;
+    if (id < 0 || id >= vocab) {  // host validates ids; never read out of the table
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = 0.f;
+        return;
+    }
+    const W* row = table + (size_t)id * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(row[i]);
+}
+
+MSTAR_API int mstar_embed_rows(const void* table, int table_dtype, const int* ids, float* out,
+                               int num_tokens, int vocab, int hidden, void* stream) {
+    if (num_tokens <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (table_dtype == MSTAR_F32)
+        embed_rows_kernel<float><<<num_tokens, threads, 0, s>>>((const float*)table, ids, out, vocab, hidden);
+    else
+        embed_rows_kernel<bf16><<<num_tokens, threads, 0, s>>>((const bf16*)table, ids, out, vocab, hidden);
+    return launch_status();
+}
+
+// ------------------------------------------------- residual add + RMSNorm
+// resid (float, [rows, hidden]) is updated in place with resid + delta when delta
+// is given; out = resid * rsqrt(mean(resid^2) + eps) * (w + w_offset) in type A.
+// One block per row.  The sum of squares is accumulated per thread over a fixed
+// stride and then reduced in a fixed tree, so a row's result does not depend on
+// which other rows are in the batch.
+template <typename A, typename W>
+__global__ void add_rmsnorm_kernel(float* __restrict__ resid, const A* __restrict__ delta,
+                                   const W* __restrict__ weight, A* __restrict__ out, int hidden,
+                                   float eps, float w_offset) {
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * hidden;
+    float* r = resid + base;
+    float ss = 0.f;
+    if (delta != nullptr) {
+        const A* d = delta + base;
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float v = r[i] + to_float(d[i]);
+            r[i] = v;
+            ss = fmaf(v, v, ss);
+        }
+    } else {
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+            const float v = r[i];
+            ss = fmaf(v, v, ss);
+        }
+    }
+    const float total = block_sum(ss, scratch);
+    const float inv = rsqrtf(total / (float)hidden + eps);
+    A* o = out + base;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        // each thread re-reads only what it wrote itself, so no barrier is needed
+        o[i] = from_float<A>(r[i] * inv * (to_float(weight[i]) + w_offset));
+    }
+}
+
+MSTAR_API int mstar_add_rmsnorm(float* resid, const void* delta, const void* weight,
+                                int weight_dtype, void* out, int act_dtype, int rows, int hidden,
+                                float eps, float w_offset, void* stream) {
+    if (rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+#define LAUNCH(A, W)                                                                        \
+    add_rmsnorm_kernel<A, W><<<rows, threads, 0, s>>>(resid, (const A*)delta, (const W*)weight, \
+                                                      (A*)out, hidden, eps, w_offset)
+    if (act_dtype == MSTAR_F32) {
+        if (weight_dtype == MSTAR_F32) LAUNCH(float, float); else LAUNCH(float, bf16);
+    } else {
+        if (weight_dtype == MSTAR_F32) LAUNCH(bf16, float); else LAUNCH(bf16, bf16);
+    }
+#undef LAUNCH
+    return launch_status();
+}
+
+// ------------------------------------------------------ gather (+add) rows
+// out[i] = resid[rows[i]] (+ delta[rows[i]]), float.  Used to pick the rows whose
+// logits are wanted before the final norm, so norm and LM head run on those only.
+template <typename A>
+__global__ void gather_add_rows_kernel(const float* __restrict__ resid, const A* __restrict__ delta,
+                                       const int* __restrict__ rows, float* __restrict__ out,
+                                       int hidden) {
+    const size_t src = (size_t)rows[blockIdx.x] * hidden;
+    const size_t dst = (size_t)blockIdx.x * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float v = resid[src + i];
+        if (delta != nullptr) v += to_float(delta[src + i]);
+        out[dst + i] = v;
+    }
+}
+
+MSTAR_API int mstar_gather_add_rows(const float* resid, const void* delta, int act_dtype,
+                                    const int* rows, float* out, int num_rows, int hidden,
+                                    void* stream) {
+    if (num_rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (act_dtype == MSTAR_F32)
+        gather_add_rows_kernel<float><<<num_rows, 256, 0, s>>>(resid, (const float*)delta, rows, out, hidden);
+    else
+        gather_add_rows_kernel<bf16><<<num_rows, 256, 0, s>>>(resid, (const bf16*)delta, rows, out, hidden);
+    return launch_status();
+}
+
+// ------------------------------------------------------------ SiLU(gate)*up
+// gate_up: [rows, 2*inter] with gate first (mstar/model/components/distributed/
+// mlp.py:78-81); out: [rows, inter].  silu(x) = x / (1 + exp(-x)) in float.
+template <typename A>
+__global__ void silu_mul_kernel(const A* __restrict__ gate_up, A* __restrict__ out, int inter,
+                                size_t total) {
+    for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+         idx += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = idx / inter;
+        const int col = (int)(idx - row * inter);
+        const A* p = gate_up + row * 2 * (size_t)inter;
+        const float g = to_float(p[col]);
+        const float u = to_float(p[inter + col]);
+        const float act = g / (1.f + expf(-g));
+        out[idx] = from_float<A>(act * u);
+    }
+}
+
+MSTAR_API int mstar_silu_mul(const void* gate_up, void* out, int act_dtype, int rows, int inter,
+                             void* stream) {
+    const size_t total = (size_t)rows * inter;
+    if (total == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = 256;
+    size_t blocks = (total + threads - 1) / threads;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (act_dtype == MSTAR_F32)
+        silu_mul_kernel<float><<<(int)blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, total);
+    else
+        silu_mul_kernel<bf16><<<(int)blocks, threads, 0, s>>>((const bf16*)gate_up, (bf16*)out, inter, total);
+    return launch_status();
+}
+
+// ------------------------------------------------------------- conversion
+template <typename S, typename D>
+__global__ void convert_kernel(const S* __restrict__ src, D* __restrict__ dst, size_t n) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x)
+        dst[i] = from_float<D>(to_float(src[i]));
+}
+
+MSTAR_API int mstar_convert(const void* src, int src_dtype, void* dst, int dst_dtype, long long n,
+                            void* stream) {
+    if (n <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    size_t blocks = ((size_t)n + 255) / 256;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    if (src_dtype == MSTAR_F32 && dst_dtype == MSTAR_BF16)
+        convert_kernel<float, bf16><<<(int)blocks, 256, 0, s>>>((const float*)src, (bf16*)dst, (size_t)n);
+    else if (src_dtype == MSTAR_BF16 && dst_dtype == MSTAR_F32)
+        convert_kernel<bf16, float><<<(int)blocks, 256, 0, s>>>((const bf16*)src, (float*)dst, (size_t)n);
+    else if (src_dtype == MSTAR_F32 && dst_dtype == MSTAR_F32)
+        convert_kernel<float, float><<<(int)blocks, 256, 0, s>>>((const float*)src, (float*)dst, (size_t)n);
+    else
+        convert_kernel<bf16, bf16><<<(int)blocks, 256, 0, s>>>((const bf16*)src, (bf16*)dst, (size_t)n);
+    return launch_status();
+}
+
+// ------------------------------------- rotary encoding + key/value page write
+// qkv: [T, (nq + 2*nkv) * hd], rows [q heads | k heads | v heads].  Queries are
+// rotated in place; keys are rotated and written, values copied, into the paged
+// cache [pages, 2, nkv, page_size, hd] at (page, slot) of the token's cache
+// position.  Angle = float(position) * inv_freq[j] in float, sincosf without
+// fast-math (full range reduction).  rotary_dim == 0 writes keys unrotated.
+// kv_cache == nullptr (a layer that reads another layer's cache): queries only.
+struct RopeArgs {
+    int nq, nkv, hd, rotary_dim, interleaved;
+    int page_size, bt_stride;
+};
+
+template <typename A>
+__global__ void rope_kv_write_kernel(A* __restrict__ qkv, const int* __restrict__ positions,
+                                     const int* __restrict__ cache_pos,
+                                     const int* __restrict__ token_req,
+                                     const int* __restrict__ block_table,
+                                     const float* __restrict__ inv_freq, A* __restrict__ kv_cache,
+                                     RopeArgs a) {
+    const int t = blockIdx.x;
+    const int hd = a.hd, half = a.rotary_dim / 2;
+    const int row_elems = (a.nq + 2 * a.nkv) * hd;
+    A* row = qkv + (size_t)t * row_elems;
+    const float pos = (float)positions[t];
+
+    A* kdst = nullptr;
+    A* vdst = nullptr;
+    if (kv_cache != nullptr) {
+        const int cp = cache_pos[t];
+        const int page = block_table[(size_t)token_req[t] * a.bt_stride + cp / a.page_size];
+        const int slot = cp % a.page_size;
+        const size_t page_elems = (size_t)2 * a.nkv * a.page_size * hd;
+        kdst = kv_cache + (size_t)page * page_elems + (size_t)slot * hd;
+        vdst = kdst + (size_t)a.nkv * a.page_size * hd;
+    }
+    const int rot_heads = (kv_cache != nullptr) ? a.nq + a.nkv : a.nq;
+
+    // rotated pairs of q (in place) and k (to the cache)
+    for (int item = threadIdx.x; item < rot_heads * half; item += blockDim.x) {
+        const int h = item / half, j = item - h * half;
+        const int i0 = a.interleaved ? 2 * j : j;
+        const int i1 = a.interleaved ? 2 * j + 1 : j + half;
+        float sn, cs;
+        sincosf(pos * inv_freq[j], &sn, &cs);
+        A* src = row + (size_t)h * hd;
+        const float x0 = to_float(src[i0]), x1 = to_float(src[i1]);
+        const float y0 = x0 * cs - x1 * sn;
+        const float y1 = x1 * cs + x0 * sn;
+        if (h < a.nq) {
+            src[i0] = from_float<A>(y0);
+            src[i1] = from_float<A>(y1);
+        } else {
+            A* dst = kdst + (size_t)(h - a.nq) * a.page_size * hd;
+            dst[i0] = from_float<A>(y0);
+            dst[i1] = from_float<A>(y1);
+        }
+    }
+    if (kv_cache == nullptr) return;
+    // features of k beyond rotary_dim are copied unrotated
+    const int tail = hd - a.rotary_dim;
+    for (int item = threadIdx.x; item < a.nkv * tail; item += blockDim.x) {
+        const int h = item / tail, d = a.rotary_dim + (item - h * tail);
+        kdst[(size_t)h * a.page_size * hd + d] = row[(size_t)(a.nq + h) * hd + d];
+    }
+    // values
+    for (int item = threadIdx.x; item < a.nkv * hd; item += blockDim.x) {
+        const int h = item / hd, d = item - h * hd;
+        vdst[(size_t)h * a.page_size * hd + d] = row[(size_t)(a.nq + a.nkv + h) * hd + d];
+    }
+}
+
+MSTAR_API int mstar_rope_kv_write(void* qkv, int act_dtype, const int* positions,
+                                  const int* cache_pos, const int* token_req,
+                                  const int* block_table, int bt_stride, const float* inv_freq,
+                                  void* kv_cache, int num_tokens, int nq, int nkv, int hd,
+                                  int rotary_dim, int interleaved, int page_size, void* stream) {
+    if (num_tokens <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    RopeArgs a{nq, nkv, hd, rotary_dim, interleaved, page_size, bt_stride};
+    const int threads = 128;
+    if (act_dtype == MSTAR_F32)
+        rope_kv_write_kernel<float><<<num_tokens, threads, 0, s>>>(
+            (float*)qkv, positions, cache_pos, token_req, block_table, inv_freq, (float*)kv_cache, a);
+    else
+        rope_kv_write_kernel<bf16><<<num_tokens, threads, 0, s>>>(
+            (bf16*)qkv, positions, cache_pos, token_req, block_table, inv_freq, (bf16*)kv_cache, a);
+    return launch_status();
+}

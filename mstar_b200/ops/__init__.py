@@ -1,0 +1,220 @@
+"""Python entry points of the hand-written kernels.
+
+Each function validates shapes and dtypes, then launches a kernel from
+``csrc/`` on the current CUDA stream.  Tensors must live on the GPU; nothing
+here computes on the CPU.  Matrix products in bfloat16 use the library GEMM
+(cuBLAS through ``torch.mm``), as the reference does for every linear layer
+(mstar/model/components/distributed/linear.py:101, 412); the float32 product
+is this package's own true-32-bit kernel.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import lib
+from .lib import BF16, F32, KernelError, check
+
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"dtype {t.dtype} is not supported (float32 and bfloat16 are)") from None
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _need_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("mstar_b200 kernels run on CUDA tensors only; got a "
+                              f"{t.device} tensor (there is no CPU path)")
+
+
+def _ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None):
+    """out[t] = float(table[ids[t]]); the residual stream is float in both dtypes."""
+    _need_cuda(table, ids)
+    assert ids.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
+    n, (vocab, hidden) = ids.numel(), table.shape
+    if out is None:
+        out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    check(lib.get("elementwise").mstar_embed_rows(
+        table.data_ptr(), _dt(table), ids.data_ptr(), out.data_ptr(), n, vocab, hidden,
+        _stream()), "embed_rows")
+    return out
+
+
+def add_rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, eps: float,
+                out_dtype: torch.dtype, weight_offset: float = 0.0, out=None):
+    """resid += delta (if given), in place in float; returns rmsnorm(resid)*weight."""
+    _need_cuda(resid, delta, weight)
+    assert resid.dtype == torch.float32 and resid.dim() == 2 and resid.is_contiguous()
+    rows, hidden = resid.shape
+    assert weight.numel() == hidden and weight.is_contiguous()
+    if delta is not None:
+        assert delta.shape == resid.shape and delta.dtype == out_dtype and delta.is_contiguous()
+    if out is None:
+        out = torch.empty((rows, hidden), dtype=out_dtype, device=resid.device)
+    check(lib.get("elementwise").mstar_add_rmsnorm(
+        resid.data_ptr(), _ptr(delta), weight.data_ptr(), _dt(weight), out.data_ptr(), _dt(out),
+        rows, hidden, float(eps), float(weight_offset), _stream()), "add_rmsnorm")
+    return out
+
+
+def gather_add_rows(resid: torch.Tensor, delta, rows: torch.Tensor):
+    """float(resid[rows] + delta[rows]) as a new [len(rows), hidden] tensor."""
+    _need_cuda(resid, delta, rows)
+    assert resid.dtype == torch.float32 and resid.is_contiguous() and rows.dtype == torch.int32
+    hidden = resid.shape[1]
+    out = torch.empty((rows.numel(), hidden), dtype=torch.float32, device=resid.device)
+    act = _dt(delta) if delta is not None else F32
+    if delta is not None:
+        assert delta.shape == resid.shape and delta.is_contiguous()
+    check(lib.get("elementwise").mstar_gather_add_rows(
+        resid.data_ptr(), _ptr(delta), act, rows.data_ptr(), out.data_ptr(), rows.numel(),
+        hidden, _stream()), "gather_add_rows")
+    return out
+
+
+def silu_mul(gate_up: torch.Tensor, out=None):
+    """silu(gate_up[:, :I]) * gate_up[:, I:]."""
+    _need_cuda(gate_up)
+    assert gate_up.dim() == 2 and gate_up.is_contiguous() and gate_up.shape[1] % 2 == 0
+    rows, inter = gate_up.shape[0], gate_up.shape[1] // 2
+    if out is None:
+        out = torch.empty((rows, inter), dtype=gate_up.dtype, device=gate_up.device)
+    check(lib.get("elementwise").mstar_silu_mul(
+        gate_up.data_ptr(), out.data_ptr(), _dt(gate_up), rows, inter, _stream()), "silu_mul")
+    return out
+
+
+def convert(src: torch.Tensor, dtype: torch.dtype):
+    _need_cuda(src)
+    if src.dtype == dtype:
+        return src
+    assert src.is_contiguous()
+    out = torch.empty(src.shape, dtype=dtype, device=src.device)
+    check(lib.get("elementwise").mstar_convert(
+        src.data_ptr(), _dt(src), out.data_ptr(), _dt(out), src.numel(), _stream()), "convert")
+    return out
+
+
+def rope_kv_write(qkv: torch.Tensor, positions, cache_pos, token_req, block_table,
+                  inv_freq, kv_cache, num_heads: int, num_kv_heads: int, head_dim: int,
+                  rotary_dim: int, interleaved: bool, page_size: int) -> None:
+    """Rotate queries in place; rotate keys and copy values into their cache pages.
+
+    ``kv_cache``: [pages, 2, kv_heads, page_size, head_dim] or None (queries only).
+    ``inv_freq``: float [rotary_dim / 2] or None when rotary_dim == 0."""
+    _need_cuda(qkv, positions, cache_pos, token_req, block_table, inv_freq, kv_cache)
+    assert qkv.dim() == 2 and qkv.is_contiguous()
+    n = qkv.shape[0]
+    assert qkv.shape[1] == (num_heads + 2 * num_kv_heads) * head_dim
+    assert rotary_dim % 2 == 0 and 0 <= rotary_dim <= head_dim
+    if rotary_dim:
+        assert inv_freq is not None and inv_freq.dtype == torch.float32
+        assert inv_freq.numel() == rotary_dim // 2
+    if kv_cache is not None:
+        assert kv_cache.dtype == qkv.dtype and kv_cache.is_contiguous()
+        assert tuple(kv_cache.shape[1:]) == (2, num_kv_heads, page_size, head_dim)
+    check(lib.get("elementwise").mstar_rope_kv_write(
+        qkv.data_ptr(), _dt(qkv), positions.data_ptr(), cache_pos.data_ptr(),
+        token_req.data_ptr(), block_table.data_ptr(), block_table.stride(0), _ptr(inv_freq),
+        _ptr(kv_cache), n, num_heads, num_kv_heads, head_dim, rotary_dim, int(interleaved),
+        page_size, _stream()), "rope_kv_write")
+
+
+def paged_attention_generic(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv_cache,
+                            block_table, token_req, cache_pos, num_tokens: int, num_heads: int,
+                            num_kv_heads: int, head_dim: int, page_size: int, window: int,
+                            scale: float) -> None:
+    """Attention of ``num_tokens`` query rows (portions and decoded tokens alike)
+    over the paged cache; ``q`` may be a view into the fused qkv buffer with
+    ``q_stride`` elements between tokens."""
+    _need_cuda(q, out, kv_cache, block_table, token_req, cache_pos)
+    assert out.is_contiguous() and kv_cache.is_contiguous()
+    code = lib.get("attention_generic").mstar_paged_attention_generic(
+        q.data_ptr(), q_stride, out.data_ptr(), kv_cache.data_ptr(), block_table.data_ptr(),
+        block_table.stride(0), token_req.data_ptr(), cache_pos.data_ptr(), num_tokens,
+        num_heads, num_kv_heads, head_dim, page_size, window, float(scale), _dt(out), _stream())
+    if code == -1:
+        raise KernelError(
+            f"paged attention refuses heads={num_heads}, kv_heads={num_kv_heads}, "
+            f"head_dim={head_dim}: it needs head_dim <= 256 and (heads/kv_heads)*head_dim <= 4096")
+    check(code, "paged_attention_generic")
+
+
+def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out=None):
+    """a[M,K] @ w[N,K]^T in true float32 (FMA, no tensor-core reduced precision)."""
+    _need_cuda(a, w)
+    assert a.dtype == torch.float32 and w.dtype == torch.float32
+    assert a.dim() == 2 and w.dim() == 2 and a.shape[1] == w.shape[1]
+    assert a.stride(1) == 1 and w.stride(1) == 1
+    m, k = a.shape
+    n = w.shape[0]
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.float32, device=a.device)
+    assert out.stride(1) == 1
+    check(lib.get("gemm_f32").mstar_sgemm_nt(
+        a.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, a.stride(0), w.stride(0),
+        out.stride(0), _stream()), "sgemm_nt")
+    return out
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None):
+    """x[M,K] @ w[N,K]^T.  bfloat16 x bfloat16 -> library GEMM with float
+    accumulation; anything involving a float32 operand runs in true float32."""
+    _need_cuda(x, w)
+    out_dtype = out_dtype or x.dtype
+    if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
+        if out_dtype == torch.float32:
+            try:
+                return torch.mm(x, w.t(), out_dtype=torch.float32)
+            except (TypeError, RuntimeError):
+                return torch.mm(x, w.t()).float()
+        return torch.mm(x, w.t())
+    xf = convert(x, torch.float32)
+    wf = convert(w, torch.float32)
+    y = sgemm_nt(xf, wf)
+    return convert(y, out_dtype)
+
+
+def argmax(logits: torch.Tensor):
+    _need_cuda(logits)
+    assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
+    rows, vocab = logits.shape
+    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    check(lib.get("sampling").mstar_argmax(
+        logits.data_ptr(), logits.stride(0), rows, vocab, out.data_ptr(), _stream()), "argmax")
+    return out
+
+
+def sample(logits: torch.Tensor, temperature, top_k=None, top_p=None, penalty=None,
+           seen_mask=None, seen_rows=None, seed=None, offset=None):
+    """One token per row.  Per-row tensors: temperature float32, top_k int32,
+    top_p float32, penalty float32, seed/offset int64; ``seen_mask`` uint8
+    [slots, vocab] with ``seen_rows`` int32 naming each row's slot (or -1)."""
+    _need_cuda(logits, temperature, top_k, top_p, penalty, seen_mask, seen_rows, seed, offset)
+    assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
+    rows, vocab = logits.shape
+    assert temperature.dtype == torch.float32 and temperature.numel() == rows
+    for t, dt in ((top_k, torch.int32), (top_p, torch.float32), (penalty, torch.float32),
+                  (seen_rows, torch.int32), (seed, torch.int64), (offset, torch.int64)):
+        assert t is None or (t.dtype == dt and t.numel() == rows)
+    if seen_mask is not None:
+        assert seen_mask.dtype == torch.uint8 and seen_mask.shape[1] == vocab
+        assert seen_mask.is_contiguous()
+    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    check(lib.get("sampling").mstar_sample(
+        logits.data_ptr(), logits.stride(0), rows, vocab, temperature.data_ptr(), _ptr(top_k),
+        _ptr(top_p), _ptr(penalty), _ptr(seen_mask), _ptr(seen_rows), _ptr(seed), _ptr(offset),
+        out.data_ptr(), _stream()), "sample")
+    return out

@@ -1,0 +1,84 @@
+"""ctypes bindings of the CUDA libraries, loaded (and compiled) on first use.
+
+Every exported kernel launcher returns 0, a CUDA error code, or a negative
+refusal code; ``check`` turns anything but 0 into an exception.  There is no
+fallback: on a machine without the compiler or without a GPU the call fails.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+
+from .build import build_library
+
+F32, BF16 = 0, 1
+
+_c = ctypes
+_vp, _i, _f, _ll = _c.c_void_p, _c.c_int, _c.c_float, _c.c_longlong
+
+# library -> {function: argtypes}
+_SIGNATURES = {
+    "elementwise": {
+        "mstar_embed_rows": [_vp, _i, _vp, _vp, _i, _i, _i, _vp],
+        "mstar_add_rmsnorm": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _f, _f, _vp],
+        "mstar_gather_add_rows": [_vp, _vp, _i, _vp, _vp, _i, _i, _vp],
+        "mstar_silu_mul": [_vp, _vp, _i, _i, _i, _vp],
+        "mstar_convert": [_vp, _i, _vp, _i, _ll, _vp],
+        "mstar_rope_kv_write": [_vp, _i, _vp, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i, _i,
+                                _i, _i, _vp],
+    },
+    "attention_generic": {
+        "mstar_paged_attention_generic": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i,
+                                          _i, _i, _f, _i, _vp],
+    },
+    "gemm_f32": {
+        "mstar_sgemm_nt": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
+    },
+    "sampling": {
+        "mstar_sample": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
+        "mstar_argmax": [_vp, _i, _i, _i, _vp, _vp],
+    },
+}
+
+_libs: dict = {}
+_lock = threading.Lock()
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def register_signatures(library: str, signatures: dict) -> None:
+    """Let a further library (added to ``build.LIBRARIES``) declare its functions."""
+    _SIGNATURES.setdefault(library, {}).update(signatures)
+    _libs.pop(library, None)
+
+
+def get(library: str):
+    lib = _libs.get(library)
+    if lib is not None:
+        return lib
+    with _lock:
+        lib = _libs.get(library)
+        if lib is not None:
+            return lib
+        path = build_library(library)
+        lib = ctypes.CDLL(str(path))
+        for fn, argtypes in _SIGNATURES.get(library, {}).items():
+            f = getattr(lib, fn)
+            f.argtypes = argtypes
+            f.restype = _i
+        _libs[library] = lib
+        return lib
+
+
+def loaded_libraries() -> dict:
+    return {name: lib._name for name, lib in _libs.items()}
+
+
+def check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: the kernel refuses this shape (code {code})")
+    raise KernelError(f"{what}: CUDA error {code}")
