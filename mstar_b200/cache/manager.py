@@ -245,10 +245,11 @@ class CacheManager:
 
     # -- per-step index arrays ---------------------------------------------
     def fill_batch(self, requests: Sequence[Hashable], n_new: Sequence[int],
-                   out: Optional[np.ndarray] = None) -> BatchIndex:
-        """Index arrays for a batch whose pages are reserved.  ``out``: an int32
-        buffer to write into (pinned memory for the copy to the device); it must
-        hold ``packed_size`` elements."""
+                   extra: Sequence[tuple] = (), alloc=None) -> BatchIndex:
+        """Index arrays for a batch whose pages are reserved, packed in one int32
+        buffer so that one copy brings them to the device.  ``extra``: further
+        (name, length) sections the caller fills itself (token ids, wanted rows);
+        ``alloc(n)`` returns the int32 array to pack into (pinned memory)."""
         n = len(requests)
         rids = _i64([self._rid(r) for r in requests])
         counts = [int(c) for c in n_new]
@@ -274,13 +275,16 @@ class CacheManager:
         take("slots", n)
         for g, w in enumerate(widths):
             take(f"table{g}", n * w)
-        size = cursor
-        if out is None:
+        for name, length in extra:
+            take(name, int(length))
+        size = max(cursor, 4)
+        if alloc is None:
             packed = np.zeros(size, dtype=np.int32)
         else:
-            if out.dtype != np.int32 or out.size < size:
-                raise ValueError(f"index buffer too small: need {size} int32, got {out.size}")
-            packed = out[:size]
+            packed = alloc(size)
+            if packed.dtype != np.int32 or packed.size < size:
+                raise ValueError(f"index buffer too small: need {size} int32")
+            packed = packed[:size]
 
         def view(name: str) -> np.ndarray:
             o, length = offsets[name]

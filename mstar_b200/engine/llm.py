@@ -1,0 +1,169 @@
+"""Python entry point: load a model folder, generate tokens for token-id prompts.
+
+    from mstar_b200 import LLM, SamplingParams
+    llm = LLM("/models/orpheus", dtype="bfloat16")
+    results = llm.generate([[128259, 5, 17, 128009]], SamplingParams(temperature=0))
+
+The reference's Python entry point is an HTTP client (mstar/__init__.py:17-30) and its
+engine options live in a YAML file (``max_concurrent_requests``, ``kv_cache:`` with
+``page_size`` and ``max_num_pages``; docs/serving.rst:161-238, mstar/engine/kv_store.py:
+71-101); the same option names are constructor arguments here.  Prompts are token ids:
+tokenisation happens in the reference's API server, which is outside this engine.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Hashable, Optional, Sequence
+
+import torch
+
+from ..cache.storage import CacheStorage, bytes_per_page, plan_groups
+from ..config.base import GenerationDefaults
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler
+from .model import Model, load_model
+from .scheduler import Request, Scheduler, SchedulerConfig
+from .step import StepEntry, Stepper
+
+
+@dataclass
+class GenerationResult:
+    request_id: Hashable
+    prompt_token_ids: list
+    token_ids: list
+    finish_reason: str
+    preemptions: int = 0
+
+
+@dataclass
+class EngineStats:
+    steps: int = 0
+    prompt_tokens: int = 0
+    generated_tokens: int = 0
+    preemptions: int = 0
+    step_seconds: list = field(default_factory=list)
+
+
+class LLM:
+    def __init__(self, model, dtype: str = "bfloat16", device: str = "cuda:0", *,
+                 page_size: int = 16, max_num_pages: Optional[int] = None,
+                 kv_cache_memory_fraction: float = 0.85,
+                 max_num_batched_tokens: int = 2048,
+                 max_concurrent_requests: Optional[int] = 64, max_batch_size: int = 64,
+                 log_stats: bool = False):
+        """``model``: a folder with config.json and safetensors, or a built ``Model``.
+        ``max_num_pages``: pages of ``page_size`` tokens per cache group; None sizes
+        the pool from ``kv_cache_memory_fraction`` of the memory free after loading."""
+        self.model: Model = model if isinstance(model, Model) else load_model(
+            model, dtype=dtype, device=device)
+        self.device = self.model.runtime.device
+        slots = max_concurrent_requests or max_batch_size
+        if max_num_pages is None:
+            max_num_pages = self._pages_from_memory(page_size, kv_cache_memory_fraction)
+        storage = CacheStorage(self.model.cache_needs, self.model.runtime.dtype, self.device,
+                               page_size, max_num_pages, slots)
+        self.stepper = Stepper(self.model, storage)
+        self.sampler = Sampler(self.model.vocab_size, slots, self.device)
+        cfg = self.model.config
+        stops = cfg.stop_token_ids() if cfg is not None else ()
+        self.scheduler = Scheduler(
+            SchedulerConfig(max_num_batched_tokens=max_num_batched_tokens,
+                            max_concurrent_requests=max_concurrent_requests,
+                            max_batch_size=max_batch_size),
+            storage.manager, stops, admit=self.stepper.add_request,
+            release=self._release)
+        self.log_stats = log_stats
+        self.stats = EngineStats()
+        self._auto_id = 0
+
+    def _pages_from_memory(self, page_size: int, fraction: float) -> list:
+        free, _ = torch.cuda.mem_get_info(self.device)
+        windows, group_of = plan_groups(self.model.cache_needs)
+        if not windows:
+            return []
+        per_group = int(free * fraction) // len(windows)
+        pages = []
+        for g in range(len(windows)):
+            b = bytes_per_page(self.model.cache_needs, group_of, g, page_size,
+                               self.model.runtime.dtype)
+            pages.append(max(per_group // max(b, 1), 1))
+        return pages
+
+    def _release(self, request_id: Hashable) -> None:
+        self.stepper.free_request(request_id)
+        self.sampler.remove_request(request_id)
+
+    # -- requests ---------------------------------------------------------
+    def add_request(self, prompt_token_ids: Sequence[int],
+                    sampling_params: Optional[SamplingParams] = None,
+                    request_id: Optional[Hashable] = None) -> Hashable:
+        if request_id is None:
+            request_id = f"req-{self._auto_id}"
+            self._auto_id += 1
+        params = sampling_params or SamplingParams()
+        vocab = self.model.vocab_size
+        prompt = [int(t) for t in prompt_token_ids]
+        if any(t < 0 or t >= vocab for t in prompt):
+            raise ValueError(f"prompt of {request_id!r} has a token id outside [0, {vocab})")
+        self.scheduler.add(Request(request_id, prompt, params))
+        return request_id
+
+    def has_unfinished(self) -> bool:
+        return self.scheduler.has_work()
+
+    def step(self) -> list:
+        """Schedule and run one batch; returns the requests that finished."""
+        t0 = time.perf_counter()
+        plan = self.scheduler.schedule()
+        finished = list(plan.finished)
+        self.stats.preemptions += len(plan.preempted)
+        for r in plan.admitted:
+            self.sampler.add_request(r.request_id, r.params, r.slot, generated=r.output)
+        if plan.entries:
+            entries = [StepEntry(e.request.request_id, e.tokens,
+                                 (len(e.tokens) - 1,) if e.samples else ())
+                       for e in plan.entries]
+            logits = self.stepper.step(entries)
+            sampling = [e.request.request_id for e in plan.entries if e.samples]
+            sampled = {}
+            if sampling:
+                tokens = self.sampler.sample(sampling, logits).tolist()
+                sampled = dict(zip(sampling, tokens))
+            finished += self.scheduler.update(plan, sampled)
+            self.stats.steps += 1
+            self.stats.prompt_tokens += sum(len(e.tokens) for e in plan.entries if not (
+                e.samples and len(e.tokens) == 1))
+            self.stats.generated_tokens += len(sampled)
+        elif not plan.preempted and not plan.finished and self.scheduler.has_work():
+            raise RuntimeError("the scheduler can make no progress: no request fits the cache")
+        if self.log_stats:
+            self.stats.step_seconds.append(time.perf_counter() - t0)
+        return finished
+
+    def generate(self, prompts, sampling_params=None, request_ids=None) -> list:
+        """Generate for one prompt (a list of token ids) or several (a list of lists).
+        ``sampling_params``: one for all, or one per prompt.  Results come in the order
+        of the prompts."""
+        single = bool(prompts) and isinstance(prompts[0], int)
+        if single:
+            prompts = [prompts]
+        n = len(prompts)
+        if sampling_params is None or isinstance(sampling_params, SamplingParams):
+            sampling_params = [sampling_params] * n
+        if request_ids is None:
+            request_ids = [None] * n
+        if len(sampling_params) != n or len(request_ids) != n:
+            raise ValueError("sampling_params and request_ids must match the prompts")
+        ids = [self.add_request(p, sp, rid)
+               for p, sp, rid in zip(prompts, sampling_params, request_ids)]
+        done: dict = {}
+        while self.has_unfinished():
+            for r in self.step():
+                done[r.request_id] = r
+        results = [GenerationResult(i, done[i].prompt, done[i].output, done[i].finish_reason,
+                                    done[i].preemptions) for i in ids]
+        return results[0] if single else results
+
+    def generation_defaults(self, folder) -> GenerationDefaults:
+        return GenerationDefaults.from_folder(folder)

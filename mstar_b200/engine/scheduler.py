@@ -1,0 +1,287 @@
+"""Continuous-batching scheduler: admission, prompt portions under a token budget,
+decoding, finishing, and what happens when pages run out.
+
+Taken from the reference: first-come admission behind ``max_concurrent_requests``,
+re-run whenever a request finishes (mstar/conductor/conductor.py:573-607, 794-825); a
+cap on requests per batch (largest captured decode batch, 64: mstar/engine/
+cuda_graph_runner.py:45); finishing on the stop token unless ``ignore_eos``, or on
+``max_output_tokens`` (mstar/model/orpheus/submodules.py:277-290, mstar/model/base.py:30).
+
+Designed here (the reference has neither a token budget, nor prompt portions, nor
+mixed batches, mstar/worker/micro_scheduler.py:97-103, 272-273): each step first gives
+every running request that is decoding its one token, then fills the rest of
+``max_num_batched_tokens`` with prompt portions, oldest request first, admitting
+waiting requests while slots and pages allow.
+
+When pages run out: the reference holds the batch and retries every 50 ms, optionally
+offloading a victim's pages to host memory (mstar/worker/worker.py:1245-1293).  Here
+the decision is pre-emption by recomputation: the request admitted last gives back
+all its pages and returns to the head of the waiting queue; its prompt plus the tokens
+it has generated are computed again once all of that fits in the free pages.  Decoding requests are never
+starved by prompts: prompt portions only take pages that decoding does not need in
+this step.  A request that cannot fit even alone in the whole pool is finished with
+reason "cache_exhausted" instead of waiting forever.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Callable, Hashable, Optional, Sequence
+
+from ..cache.manager import CacheManager
+from ..sampling.params import SamplingParams
+
+
+@dataclass
+class SchedulerConfig:
+    max_num_batched_tokens: int = 2048
+    max_concurrent_requests: Optional[int] = None   # None: as many as there are slots
+    max_batch_size: int = 64                        # requests per step
+
+    def validate(self) -> None:
+        if self.max_num_batched_tokens < 1:
+            raise ValueError("max_num_batched_tokens must be >= 1")
+        if self.max_batch_size < 1:
+            raise ValueError("max_batch_size must be >= 1")
+        if self.max_concurrent_requests is not None and self.max_concurrent_requests < 1:
+            raise ValueError("max_concurrent_requests must be >= 1")
+
+
+@dataclass
+class Request:
+    request_id: Hashable
+    prompt: list
+    params: SamplingParams
+    output: list = field(default_factory=list)
+    num_computed: int = 0          # tokens whose keys and values are in the cache
+    status: str = "waiting"        # waiting | running | finished
+    finish_reason: Optional[str] = None
+    slot: int = -1
+    preemptions: int = 0
+
+    def all_tokens(self) -> list:
+        return self.prompt + self.output
+
+    def num_pending(self) -> int:
+        return len(self.prompt) + len(self.output) - self.num_computed
+
+
+@dataclass
+class ScheduledEntry:
+    request: Request
+    tokens: list
+    samples: bool      # the portion ends at the request's last token: sample after it
+
+
+@dataclass
+class StepPlan:
+    entries: list = field(default_factory=list)
+    admitted: list = field(default_factory=list)
+    preempted: list = field(default_factory=list)
+    finished: list = field(default_factory=list)   # finished without running (errors)
+
+    def num_tokens(self) -> int:
+        return sum(len(e.tokens) for e in self.entries)
+
+
+class Scheduler:
+    def __init__(self, config: SchedulerConfig, manager: CacheManager,
+                 stop_token_ids: Sequence[int] = (),
+                 admit: Optional[Callable] = None, release: Optional[Callable] = None):
+        config.validate()
+        self.config = config
+        self.manager = manager
+        self.stop_token_ids = frozenset(int(t) for t in stop_token_ids)
+        self._admit = admit or manager.add_request
+        self._release = release or manager.free_request
+        self.waiting: deque = deque()
+        self.running: list = []       # in order of admission
+        self.finished: list = []
+
+    # -- queue ------------------------------------------------------------
+    def add(self, request: Request) -> None:
+        if not request.prompt:
+            raise ValueError(f"request {request.request_id!r} has an empty prompt")
+        request.params.validate()
+        request.status = "waiting"
+        self.waiting.append(request)
+
+    def abort(self, request_id: Hashable) -> bool:
+        for r in list(self.waiting):
+            if r.request_id == request_id:
+                self.waiting.remove(r)
+                self._finish(r, "abort", held=False)
+                return True
+        for r in self.running:
+            if r.request_id == request_id:
+                self._finish(r, "abort", held=True)
+                return True
+        return False
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # -- helpers ----------------------------------------------------------
+    def _finish(self, r: Request, reason: str, held: bool) -> None:
+        if held:
+            self._release(r.request_id)
+            self.running.remove(r)
+        r.status = "finished"
+        r.finish_reason = reason
+        self.finished.append(r)
+
+    def _capacity_tokens(self) -> int:
+        """Tokens one request can hold if it has every page of the smallest pool."""
+        if not self.manager.groups:
+            return 1 << 62
+        return min(g.num_pages * g.page_size for g in self.manager.groups)
+
+    def _fits(self, requests: list, counts: list) -> bool:
+        if not requests:
+            return True
+        need = self.manager.pages_needed([r.request_id for r in requests], counts)
+        return all(n <= self.manager.free_pages(g) for g, n in enumerate(need))
+
+    def _preempt_last(self, plan: StepPlan, keep: Optional[Request] = None) -> bool:
+        """Take the pages of the request admitted last (other than ``keep``)."""
+        for victim in reversed(self.running):
+            if victim is keep:
+                continue
+            self._release(victim.request_id)
+            self.running.remove(victim)
+            victim.status = "waiting"
+            victim.num_computed = 0
+            victim.slot = -1
+            victim.preemptions += 1
+            self.waiting.appendleft(victim)
+            plan.preempted.append(victim)
+            plan.entries = [e for e in plan.entries if e.request is not victim]
+            return True
+        return False
+
+    # -- one step ---------------------------------------------------------
+    def schedule(self) -> StepPlan:
+        cfg = self.config
+        plan = StepPlan()
+        budget = cfg.max_num_batched_tokens
+        chosen: list = []
+        counts: list = []
+
+        # 1. one token for every request that is decoding, oldest first
+        for r in list(self.running):
+            if r not in self.running or r.num_pending() != 1:
+                continue
+            if len(chosen) >= cfg.max_batch_size or budget < 1:
+                break
+            while not self._fits(chosen + [r], counts + [1]):
+                if not self._preempt_last(plan, keep=r):
+                    break
+                kept = [(c, n) for c, n in zip(chosen, counts) if c in self.running]
+                chosen, counts = [c for c, _ in kept], [n for _, n in kept]
+            if r not in self.running:
+                continue
+            if not self._fits(chosen + [r], counts + [1]):
+                # alone and still no page: the pool cannot hold this request
+                self._finish(r, "cache_exhausted", held=True)
+                plan.finished.append(r)
+                continue
+            chosen.append(r)
+            counts.append(1)
+            budget -= 1
+
+        # 2. prompt portions of running requests, oldest first
+        for r in list(self.running):
+            if r in chosen or r.num_pending() < 1:
+                continue
+            if len(chosen) >= cfg.max_batch_size or budget < 1:
+                break
+            n = self._portion(r, budget, chosen, counts)
+            if n > 0:
+                chosen.append(r)
+                counts.append(n)
+                budget -= n
+
+        # 3. admit waiting requests while slots, the cap and pages allow
+        while (self.waiting and not plan.preempted and budget >= 1
+               and len(chosen) < cfg.max_batch_size):
+            cap = cfg.max_concurrent_requests
+            if cap is not None and len(self.running) >= cap:
+                break
+            if self.manager.free_slots() < 1:
+                break
+            r = self.waiting[0]
+            if len(r.all_tokens()) + 1 > self._capacity_tokens():
+                self.waiting.popleft()
+                self._finish(r, "cache_exhausted", held=False)
+                plan.finished.append(r)
+                continue
+            r.slot = self._admit(r.request_id)
+            n = self._portion(r, budget, chosen, counts)
+            if n > 0 and r.preemptions and not self._fits(chosen + [r],
+                                                          counts + [r.num_pending() + 1]):
+                n = 0    # a pre-empted request returns only when all it had fits again
+            if n <= 0:
+                self._release(r.request_id)   # no page for even one token now
+                r.slot = -1
+                break
+            self.waiting.popleft()
+            r.status = "running"
+            self.running.append(r)
+            plan.admitted.append(r)
+            chosen.append(r)
+            counts.append(n)
+            budget -= n
+
+        # nothing can run although requests hold pages: they block one another (or one
+        # alone is too large).  The oldest keeps its pages; the newest gives its up.
+        if not chosen and self.running and not plan.preempted:
+            oldest = self.running[0]
+            if len(self.running) == 1:
+                self._finish(oldest, "cache_exhausted", held=True)
+                plan.finished.append(oldest)
+            else:
+                self._preempt_last(plan, keep=oldest)
+
+        for r, n in zip(chosen, counts):
+            toks = r.all_tokens()[r.num_computed:r.num_computed + n]
+            plan.entries.append(ScheduledEntry(r, toks, r.num_computed + n == len(r.prompt)
+                                               + len(r.output)))
+        return plan
+
+    def _portion(self, r: Request, budget: int, chosen: list, counts: list) -> int:
+        """Largest portion of r's pending tokens that the budget and the free pages
+        (after what is already chosen) allow; 0 if not even one token fits."""
+        hi = min(r.num_pending(), budget)
+        if hi <= 0:
+            return 0
+        if self._fits(chosen + [r], counts + [hi]):
+            return hi
+        lo = 0                       # largest count known to fit (0: none yet)
+        while hi - lo > 1:           # invariant: lo fits (or is 0), hi does not
+            mid = (lo + hi) // 2
+            if self._fits(chosen + [r], counts + [mid]):
+                lo = mid
+            else:
+                hi = mid
+        return lo
+
+    # -- after the forward pass -------------------------------------------
+    def update(self, plan: StepPlan, sampled: dict) -> list:
+        """``sampled``: request id -> token for every entry with ``samples``.  Advances
+        computed counts, appends tokens, finishes and frees.  Returns the requests that
+        finished in this step."""
+        done = []
+        for e in plan.entries:
+            r = e.request
+            r.num_computed += len(e.tokens)
+            if not e.samples:
+                continue
+            tok = int(sampled[r.request_id])
+            r.output.append(tok)
+            if (not r.params.ignore_eos) and tok in self.stop_token_ids:
+                self._finish(r, "stop", held=True)
+                done.append(r)
+            elif len(r.output) >= r.params.max_output_tokens:
+                self._finish(r, "length", held=True)
+                done.append(r)
+        return done

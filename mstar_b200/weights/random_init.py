@@ -66,13 +66,16 @@ def random_checkpoint(config: ModelConfig, seed: int, *, std: float = 0.02,
     return out
 
 
-def write_model_folder(folder: str | Path, config: ModelConfig, seed: int, **kwargs) -> Path:
-    """Write ``config.json`` and ``model.safetensors`` for a random model."""
+def write_model_folder(folder: str | Path, config: ModelConfig, seed: int, *,
+                       tensors: Optional[Mapping] = None, **kwargs) -> Path:
+    """Write ``config.json`` and ``model.safetensors`` for a random model; ``tensors``
+    (checkpoint name -> tensor) are written instead of freshly drawn ones if given."""
     from safetensors.torch import save_file
 
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
-    tensors = random_checkpoint(config, seed, **kwargs)
+    if tensors is None:
+        tensors = random_checkpoint(config, seed, **kwargs)
     raw = config.to_dict()
     (folder / "config.json").write_text(json.dumps(raw, indent=2, sort_keys=True) + "\n")
     save_file({k: v.contiguous().cpu() for k, v in tensors.items()},

@@ -54,7 +54,14 @@ def model_folders(tmp_path_factory):
         # std 0.05 instead of 0.02: tiny widths need larger weights for logits that
         # differ visibly between tokens
         kwargs = dict(std=0.05, norm_noise=opts["norm_noise"], vector_dtype=torch.float32)
-        write_model_folder(folder, cfg, opts["seed"], **kwargs)
         tensors = random_checkpoint(cfg, opts["seed"], **kwargs)
+        # sharper attention than N(0, 0.05) projections give: with near-uniform
+        # attention weights a wrong or missing key would barely move the logits.  Not
+        # sharper than x3: at x6 the model amplifies rounding so much that the plain
+        # model run in float32 instead of float64 already differs by 8e-5.
+        for key in tensors:
+            if key.endswith("q_proj.weight") or key.endswith("k_proj.weight"):
+                tensors[key] = (tensors[key].float() * 3.0).to(torch.bfloat16)
+        write_model_folder(folder, cfg, opts["seed"], tensors=tensors)
         out[name] = (folder, raw, tensors)
     return out

@@ -1,0 +1,122 @@
+"""Generation through the Python entry point and the command line."""
+import json
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import helpers as H
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+
+
+def check_greedy(results, prompts, tensors, raw, dtype, n_new):
+    for prompt, res in zip(prompts, results):
+        assert res.finish_reason == "length" and len(res.token_ids) == n_new
+        ids = list(prompt)
+        for k, tok in enumerate(res.token_ids):
+            logits = P.plain_logits(tensors, raw, ids)[-1]
+            best = int(logits.argmax())
+            if tok != best:
+                # only a near-tie may be decided differently, and only in bfloat16
+                assert dtype == "bfloat16", (prompt, k, tok, best)
+                assert (logits[best] - logits[tok]).item() < 2 * H.TOL["bfloat16"], (k, tok, best)
+            ids.append(tok)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_greedy_generation_matches_the_plain_model(model_folders, name, dtype):
+    from mstar_b200 import LLM, SamplingParams
+
+    folder, raw, tensors = model_folders[name]
+    lengths = [5, 9, 17] if name == "tiny_a" else [1, 7, 33, 40]
+    prompts = [H.request_tokens(raw["vocab_size"], n, seed=200 + n) for n in lengths]
+    # portions of 16 tokens at most, small pages: prompts are cut and mixed with decoding
+    llm = LLM(folder, dtype=dtype, page_size=4 if name == "tiny_a" else 8, max_num_pages=64,
+              max_num_batched_tokens=16)
+    params = SamplingParams(temperature=0.0, max_output_tokens=8, ignore_eos=True)
+    results = llm.generate(prompts, params)
+    check_greedy(results, prompts, tensors, raw, dtype, 8)
+    assert llm.stepper.manager.num_requests() == 0 and llm.stepper.manager.check() == 0
+
+
+def test_preemption_does_not_change_greedy_tokens(model_folders):
+    from mstar_b200 import LLM, SamplingParams
+
+    folder, raw, tensors = model_folders["tiny_b"]
+    prompts = [H.request_tokens(raw["vocab_size"], n, seed=300 + n) for n in (20, 22, 24)]
+    params = SamplingParams(temperature=0.0, max_output_tokens=24, ignore_eos=True)
+    roomy = LLM(folder, dtype="float32", page_size=8, max_num_pages=64).generate(prompts, params)
+    tight_llm = LLM(folder, dtype="float32", page_size=8, max_num_pages=12)
+    tight = tight_llm.generate(prompts, params)
+    assert tight_llm.stats.preemptions > 0
+    assert [r.token_ids for r in tight] == [r.token_ids for r in roomy]
+    assert sum(r.preemptions for r in tight) == tight_llm.stats.preemptions
+
+
+def test_sampling_options_through_the_entry_point(model_folders):
+    from mstar_b200 import LLM, SamplingParams
+
+    folder, raw, tensors = model_folders["tiny_a"]
+    llm = LLM(folder, dtype="float32", page_size=4, max_num_pages=64)
+    prompt = H.request_tokens(raw["vocab_size"], 9, seed=1)
+
+    def gen(**kw):
+        opts = dict(temperature=0.8, max_output_tokens=12, ignore_eos=True)
+        opts.update(kw)
+        return llm.generate(prompt, SamplingParams(**opts), request_ids=None).token_ids
+
+    a, b, c = gen(seed=5), gen(seed=5), gen(seed=6)
+    assert a == b and a != c                               # the seed decides the draw
+    r1 = llm.generate(prompt, SamplingParams(temperature=0.8, max_output_tokens=6,
+                                             ignore_eos=True), request_ids=None)
+    assert len(r1.token_ids) == 6
+    # top_k=1 is greedy whatever the temperature
+    greedy = gen(temperature=0.0)
+    assert gen(top_k=1, seed=9) == greedy
+    # every sampled token lies in the top-k set of the plain distribution
+    toks = gen(top_k=3, top_p=0.9, seed=11)
+    ids = list(prompt)
+    for tok in toks:
+        p = P.plain_sampling_distribution(P.plain_logits(tensors, raw, ids)[-1], 0.8, top_k=3,
+                                          top_p=0.9)
+        assert p[tok] > 0
+        ids.append(tok)
+    # a strong repetition penalty forbids repeating a generated token under greedy decoding
+    rep = gen(temperature=0.0, repetition_penalty=50.0, max_output_tokens=20)
+    assert len(set(rep)) == len(rep)
+
+
+def test_stop_token_ends_a_request(model_folders, tmp_path):
+    from mstar_b200 import LLM, SamplingParams
+    from mstar_b200.config.registry import config_from_dict
+    from mstar_b200.weights.random_init import write_model_folder
+
+    folder, raw, tensors = model_folders["tiny_a"]
+    prompt = H.request_tokens(raw["vocab_size"], 9, seed=1)
+    greedy = P.plain_greedy(tensors, raw, prompt, 6)
+    raw2 = {**raw, "eos_token_id": greedy[3]}
+    write_model_folder(tmp_path, config_from_dict(raw2), 0, tensors=tensors)
+    llm = LLM(tmp_path, dtype="float32", page_size=4, max_num_pages=32)
+    res = llm.generate(prompt, SamplingParams(temperature=0.0, max_output_tokens=6))
+    first = greedy.index(greedy[3])
+    assert res.token_ids == greedy[:first + 1] and res.finish_reason == "stop"
+    res = llm.generate(prompt, SamplingParams(temperature=0.0, max_output_tokens=6,
+                                              ignore_eos=True))
+    assert res.token_ids == greedy and res.finish_reason == "length"
+
+
+def test_command_line(model_folders):
+    folder, raw, tensors = model_folders["tiny_a"]
+    prompt = H.request_tokens(raw["vocab_size"], 9, seed=1)
+    cmd = [sys.executable, str(H.ROOT / "bin" / "mstar"), "generate", str(folder), "--dtype",
+           "float32", "--prompt-ids", ",".join(map(str, prompt)), "--temperature", "0",
+           "--max-output-tokens", "5", "--ignore-eos", "--max-num-pages", "32", "--log-stats"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    record = json.loads(out.stdout.strip().splitlines()[-1])
+    assert record["token_ids"] == P.plain_greedy(tensors, raw, prompt, 5)
+    assert "generated_tokens=5" in out.stderr

@@ -1,0 +1,340 @@
+"""Each kernel alone against a plain float64 reference of the same op, at sizes other
+than the engine's test models use (odd widths, head sizes in steps of 16, groups of
+1, 3 and 5, permuted pages, windows)."""
+import math
+
+import pytest
+import torch
+
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, f32=1e-5, bf16=2e-2):
+    return f32 if dtype == torch.float32 else bf16
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (scale * torch.randn(*shape, generator=g)).to(dtype).to(DEV)
+
+
+# --------------------------------------------------------------------- elementwise
+@pytest.mark.parametrize("table_dtype", DTYPES)
+def test_embed_rows(table_dtype):
+    from mstar_b200 import ops
+
+    table = rnd(301, 100, dtype=table_dtype)
+    ids = torch.tensor([0, 300, 7, 7, 150], dtype=torch.int32, device=DEV)
+    out = ops.embed_rows(table, ids)
+    assert out.dtype == torch.float32
+    assert torch.equal(out, table.float()[ids.long()])
+
+
+@pytest.mark.parametrize("act", DTYPES)
+@pytest.mark.parametrize("wdtype", DTYPES)
+@pytest.mark.parametrize("hidden", [100, 3000])
+def test_add_rmsnorm(act, wdtype, hidden):
+    from mstar_b200 import ops
+
+    rows = 7
+    resid = rnd(rows, hidden, seed=1)
+    delta = rnd(rows, hidden, dtype=act, seed=2)
+    w = (1 + 0.1 * rnd(hidden, seed=3)).to(wdtype)
+    want_resid = resid.double() + delta.double()
+    want = P.plain_rms_norm(want_resid.cpu(), w.cpu(), 1e-5)
+    r = resid.clone()
+    out = ops.add_rmsnorm(r, delta, w, 1e-5, act)
+    assert (r.double() - want_resid).abs().max() < 1e-6          # the residual sum is float
+    assert (out.double().cpu() - want).abs().max() < tol(act)
+    # without a delta the residual is untouched; weight_offset gives the (1 + w) form
+    r2 = resid.clone()
+    out2 = ops.add_rmsnorm(r2, None, w, 1e-6, act, weight_offset=1.0)
+    assert torch.equal(r2, resid)
+    want2 = P.plain_rms_norm(resid.cpu(), (w.double() + 1).cpu(), 1e-6)
+    assert (out2.double().cpu() - want2).abs().max() < tol(act, bf16=4e-2)
+
+
+@pytest.mark.parametrize("act", DTYPES)
+def test_silu_mul_and_gather(act):
+    from mstar_b200 import ops
+
+    gu = rnd(5, 2 * 37, dtype=act, seed=4, scale=2.0)
+    out = ops.silu_mul(gu)
+    g, u = gu.double()[:, :37], gu.double()[:, 37:]
+    assert (out.double() - g * torch.sigmoid(g) * u).abs().max() < tol(act, bf16=3e-2)
+
+    resid = rnd(9, 50, seed=5)
+    delta = rnd(9, 50, dtype=act, seed=6)
+    rows = torch.tensor([8, 0, 3], dtype=torch.int32, device=DEV)
+    got = ops.gather_add_rows(resid, delta, rows)
+    assert (got.double() - (resid.double() + delta.double())[rows.long()]).abs().max() < 1e-6
+    assert torch.equal(ops.gather_add_rows(resid, None, rows), resid[rows.long()])
+
+
+def scatter_cache(num_pages, nkv, page, hd, dtype):
+    return torch.zeros(num_pages, 2, nkv, page, hd, dtype=dtype, device=DEV)
+
+
+def read_cache(kv, table, length, page):
+    """Keys and values [length, nkv, hd] of one request, gathered through its table."""
+    ks, vs = [], []
+    for pos in range(length):
+        pg = table[pos // page]
+        ks.append(kv[pg, 0, :, pos % page])
+        vs.append(kv[pg, 1, :, pos % page])
+    return torch.stack(ks), torch.stack(vs)
+
+
+@pytest.mark.parametrize("act", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd,rot,inter", [(6, 3, 48, 48, False), (5, 1, 32, 16, False),
+                                                 (4, 4, 16, 16, True), (2, 1, 64, 0, False)])
+def test_rope_kv_write(act, nq, nkv, hd, rot, inter):
+    from mstar_b200 import ops
+
+    page, T = 4, 11
+    # two requests: one continues at cache position 6, one starts at 0
+    lens = [(6, 7), (0, 4)]
+    token_req = torch.tensor([0] * 7 + [1] * 4, dtype=torch.int32, device=DEV)
+    pos = torch.tensor([6 + i for i in range(7)] + list(range(4)), dtype=torch.int32, device=DEV)
+    table = torch.tensor([[9, 2, 5, 0], [7, -1, -1, -1]], dtype=torch.int32, device=DEV)
+    qkv = rnd(T, (nq + 2 * nkv) * hd, dtype=act, seed=7)
+    kv = scatter_cache(10, nkv, page, hd, act)
+    inv = None
+    if rot:
+        inv = torch.tensor([10000.0 ** (-2.0 * j / rot) for j in range(rot // 2)],
+                           dtype=torch.float32, device=DEV)
+    orig = qkv.clone()
+    ops.rope_kv_write(qkv, pos, pos, token_req, table, inv, kv, nq, nkv, hd, rot, inter, page)
+
+    def rotate(x):  # [T, heads, hd] float64 reference
+        x = x.double().cpu()
+        if not rot:
+            return x
+        xr = x[..., :rot]
+        if inter:
+            xr = torch.cat([xr[..., 0::2], xr[..., 1::2]], dim=-1)
+        y = P.plain_apply_rope(xr, pos.cpu(), inv.double().cpu())
+        if inter:
+            z = torch.empty_like(y)
+            z[..., 0::2], z[..., 1::2] = y[..., :rot // 2], y[..., rot // 2:]
+            y = z
+        return torch.cat([y, x[..., rot:]], dim=-1)
+
+    q0 = orig[:, :nq * hd].view(T, nq, hd)
+    k0 = orig[:, nq * hd:(nq + nkv) * hd].view(T, nkv, hd)
+    v0 = orig[:, (nq + nkv) * hd:].view(T, nkv, hd)
+    assert (qkv[:, :nq * hd].view(T, nq, hd).double().cpu() - rotate(q0)).abs().max() < tol(act)
+    assert torch.equal(qkv[:, nq * hd:], orig[:, nq * hd:])       # k, v rows stay as they were
+    kref, t0 = rotate(k0), 0
+    for r, (start, n) in enumerate(lens):
+        ks, vs = read_cache(kv, table[r].tolist(), start + n, page)
+        assert (ks[start:].double().cpu() - kref[t0:t0 + n]).abs().max() < tol(act)
+        assert torch.equal(vs[start:], v0[t0:t0 + n])
+        assert ks[:start].abs().max() == 0 if start else True     # nothing else is touched
+        t0 += n
+
+
+# ----------------------------------------------------------------------- attention
+def paged_case(lens_q, lens_kv, nq, nkv, hd, page, act, seed, window=0, spike=None):
+    """Random q and paged k/v for requests with lens_kv keys of which the last lens_q are
+    this step's queries; pages are handed out in a scrambled order.  ``spike`` =
+    (request, key index): that key is made to dominate every query's softmax."""
+    from mstar_b200 import ops
+
+    g = torch.Generator().manual_seed(seed)
+    n_req = len(lens_q)
+    pages_per = [-(-n // page) for n in lens_kv]
+    perm = torch.randperm(sum(pages_per) + 3, generator=g).tolist()
+    width = max(pages_per)
+    table = torch.full((n_req, width), -1, dtype=torch.int32)
+    kv = torch.zeros(sum(pages_per) + 3, 2, nkv, page, hd, dtype=act)
+    ks, vs = [], []
+    it = iter(perm)
+    for r in range(n_req):
+        k = torch.randn(lens_kv[r], nkv, hd, generator=g)
+        v = torch.randn(lens_kv[r], nkv, hd, generator=g)
+        if spike and spike[0] == r:
+            k[spike[1]] *= 0.0
+            k[spike[1], :, 0] = 30.0
+        k, v = k.to(act), v.to(act)
+        ks.append(k), vs.append(v)
+        for p in range(pages_per[r]):
+            pg = next(it)
+            table[r, p] = pg
+            chunk = slice(p * page, min((p + 1) * page, lens_kv[r]))
+            n = chunk.stop - chunk.start
+            kv[pg, 0, :, :n] = k[chunk].transpose(0, 1)
+            kv[pg, 1, :, :n] = v[chunk].transpose(0, 1)
+    T = sum(lens_q)
+    q = torch.randn(T, nq, hd, generator=g)
+    if spike:
+        q[..., 0] = 3.0 + q[..., 0].abs()
+    q = q.to(act)
+    token_req = torch.tensor([r for r in range(n_req) for _ in range(lens_q[r])],
+                             dtype=torch.int32)
+    cache_pos = torch.tensor([lens_kv[r] - lens_q[r] + i for r in range(n_req)
+                              for i in range(lens_q[r])], dtype=torch.int32)
+    out = torch.empty(T, nq * hd, dtype=act, device=DEV)
+    qd = q.reshape(T, nq * hd).to(DEV).contiguous()
+    ops.paged_attention_generic(qd, nq * hd, out, kv.to(DEV), table.to(DEV), token_req.to(DEV),
+                                cache_pos.to(DEV), T, nq, nkv, hd, page, window, hd ** -0.5)
+    # plain reference: whole-sequence attention with the queries placed at the end
+    want = torch.empty(T, nq, hd, dtype=torch.float64)
+    t0 = 0
+    for r in range(n_req):
+        full_q = torch.zeros(lens_kv[r], nq, hd, dtype=torch.float64)
+        full_q[lens_kv[r] - lens_q[r]:] = q[t0:t0 + lens_q[r]].double()
+        ref = P.plain_attention(full_q, ks[r], vs[r], window=window or None)
+        want[t0:t0 + lens_q[r]] = ref[lens_kv[r] - lens_q[r]:]
+        t0 += lens_q[r]
+    return out.view(T, nq, hd).double().cpu(), want, vs
+
+
+@pytest.mark.parametrize("act", DTYPES)
+@pytest.mark.parametrize("nq,nkv,hd,page", [(6, 2, 48, 4), (5, 1, 32, 16), (3, 3, 16, 8),
+                                            (8, 2, 128, 16), (2, 1, 256, 2)])
+def test_paged_attention_mixed_batch(act, nq, nkv, hd, page):
+    got, want, _ = paged_case([1, 7, 1, 40, 2], [33, 7, 1, 75, 130], nq, nkv, hd, page, act,
+                              seed=nq * 100 + hd)
+    assert (got - want).abs().max() < tol(act, f32=2e-5, bf16=2e-2)
+
+
+@pytest.mark.parametrize("act", DTYPES)
+def test_paged_attention_far_key_among_hundreds(act):
+    # key 3 of 700 dominates: the output must be its value, wherever its page lies
+    got, want, vs = paged_case([1, 5], [700, 650], 6, 2, 32, 8, act, seed=11, spike=(0, 3))
+    assert (got - want).abs().max() < tol(act, f32=2e-5, bf16=2e-2)
+    v3 = vs[0][3].double()                        # [nkv, hd]
+    for h in range(6):
+        assert (got[0, h] - v3[h // 3]).abs().max() < 3e-2
+
+
+@pytest.mark.parametrize("act", DTYPES)
+def test_paged_attention_window_edge(act):
+    # window 20 on 100 keys: key 80 is the oldest one the last query sees, key 79 is out
+    for spike_key, inside in ((80, True), (79, False)):
+        got, want, vs = paged_case([1], [100], 4, 2, 32, 8, act, seed=13, window=20,
+                                   spike=(0, spike_key))
+        assert (got - want).abs().max() < tol(act, f32=2e-5, bf16=2e-2)
+        hit = (got[0, 0] - vs[0][spike_key, 0].double()).abs().max() < 3e-2
+        assert bool(hit) == inside
+
+
+def test_paged_attention_refuses_what_it_cannot_do():
+    from mstar_b200 import ops
+    from mstar_b200.ops import KernelError
+
+    q = torch.zeros(1, 64 * 128, device=DEV)
+    with pytest.raises(KernelError, match="refuses"):
+        ops.paged_attention_generic(q, 64 * 128, q.clone(), torch.zeros(1, 2, 1, 4, 128, device=DEV),
+                                    torch.zeros(1, 1, dtype=torch.int32, device=DEV),
+                                    torch.zeros(1, dtype=torch.int32, device=DEV),
+                                    torch.zeros(1, dtype=torch.int32, device=DEV),
+                                    1, 64, 1, 128, 4, 0, 1.0)
+
+
+# ---------------------------------------------------------------------------- GEMM
+@pytest.mark.parametrize("m,n,k", [(1, 91, 53), (37, 130, 200), (130, 64, 17), (64, 1000, 96)])
+def test_sgemm_is_true_float32(m, n, k):
+    from mstar_b200 import ops
+
+    a, w = rnd(m, k, seed=1), rnd(n, k, seed=2)
+    got = ops.sgemm_nt(a, w)
+    want = a.double() @ w.double().T
+    # float rounding only: far below what a TF32 product (10-bit mantissa) would give
+    assert (got.double() - want).abs().max() < 2e-5 * math.sqrt(k)
+    # a row's result does not depend on the other rows of the batch
+    assert torch.equal(ops.sgemm_nt(a[:1].contiguous(), w), got[:1])
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 200, 96), (50, 1000, 320)])
+def test_linear_bf16_and_mixed(m, n, k):
+    from mstar_b200 import ops
+
+    x, w = rnd(m, k, dtype=torch.bfloat16, seed=3), rnd(n, k, dtype=torch.bfloat16, seed=4)
+    want = x.double() @ w.double().T
+    y = ops.linear(x, w)
+    assert y.dtype == torch.bfloat16 and (y.double() - want).abs().max() < 0.02 * math.sqrt(k)
+    y32 = ops.linear(x, w, out_dtype=torch.float32)
+    assert y32.dtype == torch.float32 and (y32.double() - want).abs().max() < 1e-3 * math.sqrt(k)
+    # a weight kept in 32-bit is multiplied in 32-bit even on the bfloat16 path
+    ymix = ops.linear(x, w.float())
+    assert ymix.dtype == torch.bfloat16
+    assert (ymix.double() - want).abs().max() < 0.02 * math.sqrt(k)
+
+
+# ------------------------------------------------------------------------ sampling
+def test_argmax_and_greedy_rows():
+    from mstar_b200 import ops
+
+    logits = rnd(5, 1003, seed=5)
+    logits[2, 17] = logits[2, 900] = 50.0          # equal maxima: the smaller index wins
+    want = logits.argmax(-1).int()
+    want[2] = 17
+    assert torch.equal(ops.argmax(logits), want)
+    temp = torch.zeros(5, device=DEV)
+    assert torch.equal(ops.sample(logits, temp), want)
+
+
+def draw(logits, temperature, seed, offset, **kw):
+    from mstar_b200 import ops
+
+    rows = logits.shape[0]
+    t = torch.full((rows,), temperature, device=DEV)
+    s = torch.tensor(seed, dtype=torch.int64, device=DEV)
+    o = torch.tensor(offset, dtype=torch.int64, device=DEV)
+    extra = {}
+    if "top_k" in kw:
+        extra["top_k"] = torch.full((rows,), kw["top_k"], dtype=torch.int32, device=DEV)
+    if "top_p" in kw:
+        extra["top_p"] = torch.full((rows,), kw["top_p"], device=DEV)
+    return ops.sample(logits, t, seed=s, offset=o, **extra)
+
+
+@pytest.mark.parametrize("opts", [{}, {"top_k": 5}, {"top_p": 0.7}, {"top_k": 40, "top_p": 0.5}])
+def test_sample_is_the_inverse_cdf_of_the_plain_distribution(opts):
+    vocab, rows = 1537, 64
+    logits = rnd(1, vocab, seed=6, scale=2.0).repeat(rows, 1).contiguous()
+    seeds, offsets = [1234] * rows, list(range(rows))
+    got = draw(logits, 0.8, seeds, offsets, **opts).tolist()
+    p = P.plain_sampling_distribution(logits[0].cpu(), 0.8, **opts)
+    cdf = torch.cumsum(p, 0)
+    for r, tok in enumerate(got):
+        assert p[tok] > 0, f"row {r}: token {tok} is outside the kept set"
+        u = P.plain_uniform(seeds[r], offsets[r])
+        lo = cdf[tok - 1].item() if tok else 0.0
+        assert lo - 1e-4 <= u <= cdf[tok].item() + 1e-4, (r, tok, u)
+    # same (seed, offset) -> same token; another offset or seed -> another draw somewhere
+    assert draw(logits, 0.8, seeds, offsets, **opts).tolist() == got
+    assert draw(logits, 0.8, [99] * rows, offsets, **opts).tolist() != got
+
+
+def test_sample_frequencies_follow_the_distribution():
+    vocab, rows = 50, 4096
+    logits = rnd(1, vocab, seed=8).repeat(rows, 1).contiguous()
+    got = draw(logits, 1.0, [7] * rows, list(range(rows)))
+    freq = torch.bincount(got.long().cpu(), minlength=vocab).double() / rows
+    p = torch.softmax(logits[0].double().cpu(), -1)
+    assert (freq - p).abs().max() < 0.03
+
+
+def test_repetition_penalty_and_seen_mask():
+    from mstar_b200 import ops
+
+    vocab = 300
+    logits = torch.zeros(2, vocab, device=DEV)
+    logits[:, 5] = 4.0
+    logits[:, 9] = 3.0
+    seen = torch.zeros(4, vocab, dtype=torch.uint8, device=DEV)
+    seen[2, 5] = 1                                  # row 0 uses mask row 2, row 1 none
+    rows = torch.tensor([2, -1], dtype=torch.int32, device=DEV)
+    pen = torch.tensor([2.0, 2.0], device=DEV)
+    temp = torch.zeros(2, device=DEV)
+    got = ops.sample(logits, temp, penalty=pen, seen_mask=seen, seen_rows=rows)
+    assert got.tolist() == [9, 5]                   # 4.0 / 2 < 3.0 where 5 was seen
+    assert seen[2, 9] == 1 and seen.sum() == 2      # the sampled token is marked

@@ -1,0 +1,311 @@
+"""Parts alone against their plain counterparts, and the generality of the assembly:
+a toy architecture, defined here and registered without touching the framework, whose
+layers mix a mixer with state of its own, a windowed attention in a page group of its
+own, a layer that reads another layer's cache, and a block that runs twice."""
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def rnd(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (scale * torch.randn(*shape, generator=g)).to(dtype).to(DEV)
+
+
+def runtime(dtype):
+    from mstar_b200.parts import Runtime
+    return Runtime(dtype=dtype, device=torch.device(DEV))
+
+
+def simple_ctx(q_lens, starts):
+    """A StepContext for requests that bring q_lens tokens after ``starts`` cached ones."""
+    from mstar_b200.parts import StepContext
+
+    token_req = [i for i, n in enumerate(q_lens) for _ in range(n)]
+    pos = [s + k for s, n in zip(starts, q_lens) for k in range(n)]
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    indptr = [0]
+    for n in q_lens:
+        indptr.append(indptr[-1] + n)
+    return StepContext(num_tokens=len(pos), num_entries=len(q_lens), token_req=i32(token_req),
+                       positions=i32(pos), cache_pos=i32(pos), qo_indptr=i32(indptr),
+                       kv_len=i32([s + n for s, n in zip(starts, q_lens)]),
+                       slots=i32(list(range(len(q_lens)))), q_lens=list(q_lens),
+                       kv_lens=[s + n for s, n in zip(starts, q_lens)],
+                       host_slots=list(range(len(q_lens))), max_q_len=max(q_lens),
+                       max_kv_len=max(s + n for s, n in zip(starts, q_lens)),
+                       num_decode=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_norm_part(dtype):
+    from mstar_b200.config.layout import NormSpec
+    from mstar_b200.parts import ResidualStream, build_part
+
+    spec = NormSpec(size=200, eps=1e-4)
+    w = (1 + 0.2 * rnd(200, seed=1))
+    norm = build_part("norm", spec, {"weight": w}, runtime(dtype))
+    h, d = rnd(6, 200, seed=2), rnd(6, 200, dtype=dtype, seed=3)
+    stream = ResidualStream(h.clone())
+    stream.push(d)
+    out = norm.add_norm(stream)
+    want = P.plain_rms_norm((h.double() + d.double()).cpu(), w.cpu(), 1e-4)
+    assert stream.delta is None and out.dtype == dtype
+    assert (out.double().cpu() - want).abs().max() < (1e-5 if dtype == torch.float32 else 3e-2)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_gated_mlp_part(dtype):
+    from mstar_b200.config.layout import GatedMLPSpec
+    from mstar_b200.parts import build_part
+
+    spec = GatedMLPSpec(hidden_size=72, intermediate_size=200)
+    gu, dn = rnd(400, 72, dtype=dtype, seed=4, scale=0.1), rnd(72, 200, dtype=dtype, seed=5, scale=0.1)
+    mlp = build_part("ffn", spec, {"gate_up.weight": gu, "down.weight": dn}, runtime(dtype))
+    x = rnd(9, 72, dtype=dtype, seed=6)
+    want = P.plain_swiglu(x.cpu(), gu[:200].cpu(), gu[200:].cpu(), dn.cpu())
+    got = mlp.forward(x, None)
+    assert (got.double().cpu() - want).abs().max() < (1e-5 if dtype == torch.float32 else 2e-2)
+    with pytest.raises(ValueError, match="gelu"):
+        build_part("ffn", GatedMLPSpec(72, 200, activation="gelu"),
+                   {"gate_up.weight": gu, "down.weight": dn}, runtime(dtype))
+
+
+def test_rope_part_frequencies_match_the_plain_rule():
+    from mstar_b200.config.layout import PositionSpec, RopeScalingSpec
+    from mstar_b200.parts import build_part
+
+    for hd, theta, sc in ((48, 10000.0, None), (128, 500000.0, (32.0, 1.0, 4.0, 8192)),
+                          (32, 500000.0, (8.0, 1.0, 4.0, 32))):
+        scaling = None if sc is None else RopeScalingSpec("llama3", *sc)
+        part = build_part("position", PositionSpec("rope", hd, hd, theta, scaling), {},
+                          runtime(torch.float32))
+        cfg = dict(head_dim=hd, rope_theta=theta, hidden_size=hd, num_attention_heads=1,
+                   rope_scaling=None if sc is None else dict(
+                       rope_type="llama3", factor=sc[0], low_freq_factor=sc[1],
+                       high_freq_factor=sc[2], original_max_position_embeddings=sc[3]))
+        want = P.plain_rope_frequencies(cfg).float()
+        assert torch.allclose(part.inv_freq.cpu(), want, rtol=2e-7, atol=0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_part_with_its_cache(dtype):
+    """The mixer alone: a prompt portion, then another portion, against whole-sequence
+    plain attention with the same weights."""
+    from mstar_b200.config.layout import AttentionSpec, PositionSpec
+    from mstar_b200.parts import LayerCache, build_part
+
+    H, nh, nkv, hd, page = 80, 6, 2, 48, 4
+    spec = AttentionSpec(hidden_size=H, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
+                         position=PositionSpec("rope", hd, hd, 10000.0))
+    qkv = rnd((nh + 2 * nkv) * hd, H, dtype=dtype, seed=7, scale=0.15)
+    o = rnd(H, nh * hd, dtype=dtype, seed=8, scale=0.1)
+    attn = build_part("mixer", spec, {"qkv.weight": qkv, "o.weight": o}, runtime(dtype))
+    x = rnd(23, H, dtype=dtype, seed=9)
+    kv = torch.zeros(8, 2, nkv, page, hd, dtype=dtype, device=DEV)
+    table = torch.tensor([[5, 1, 7, 2, 0, 6]], dtype=torch.int32, device=DEV)
+    cache = LayerCache(kv=kv, page_size=page, block_table=table)
+    first = attn.forward(x[:14].contiguous(), simple_ctx([14], [0]), cache)
+    second = attn.forward(x[14:].contiguous(), simple_ctx([9], [14]), cache)
+    got = torch.cat([first, second]).double().cpu()
+    w = {"a.q_proj.weight": qkv[:nh * hd].cpu(), "a.k_proj.weight": qkv[nh * hd:(nh + nkv) * hd].cpu(),
+         "a.v_proj.weight": qkv[(nh + nkv) * hd:].cpu(), "a.o_proj.weight": o.cpu()}
+    cfg = dict(num_attention_heads=nh, num_key_value_heads=nkv, head_dim=hd, hidden_size=H,
+               rope_theta=10000.0)
+    want = P.plain_self_attention(x.cpu(), w, "a", cfg, torch.arange(23),
+                                  P.plain_rope_frequencies(cfg))
+    assert (got - want).abs().max() < (2e-5 if dtype == torch.float32 else 5e-2)
+
+
+# ----------------------------------------------------------------- toy architecture
+@dataclass(frozen=True)
+class RunningMeanSpec:
+    """Toy mixer: y_t = W . mean(x_0 .. x_t).  Its state is the running sum."""
+    kind: str = "toy_running_mean"
+    hidden_size: int = 0
+    shares_kv: bool = False
+
+
+class RunningMeanMixer:
+    @classmethod
+    def param_specs(cls, spec):
+        from mstar_b200.weights.names import ParamSpec
+        return {"w.weight": ParamSpec((spec.hidden_size, spec.hidden_size))}
+
+    @classmethod
+    def cache_need(cls, spec):
+        from mstar_b200.parts import CacheNeed, StateNeed
+        return CacheNeed(state=StateNeed(shape=(spec.hidden_size,), dtype="float32"))
+
+    def __init__(self, spec, params, runtime):
+        self.w = params["w.weight"]
+
+    def forward(self, x, ctx, cache):
+        out = torch.empty_like(x)
+        xf, t0 = x.float(), 0
+        for i, n in enumerate(ctx.q_lens):
+            slot, before = ctx.host_slots[i], ctx.kv_lens[i] - n
+            sums = torch.cumsum(xf[t0:t0 + n], 0) + cache.state[slot]
+            cache.state[slot] = sums[-1]
+            count = torch.arange(before + 1, before + n + 1, device=x.device)[:, None].float()
+            out[t0:t0 + n] = ((sums / count) @ self.w.float().T).to(x.dtype)
+            t0 += n
+        return out
+
+
+class ToyConfig:
+    architecture = "ToyMixedForCausalLM"
+    H, NH, NKV, HD, INTER, VOCAB, WINDOW, EPS = 64, 4, 2, 16, 96, 128, 8, 1e-5
+
+    def to_dict(self):
+        return {"architectures": [self.architecture]}
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls()
+
+    def stop_token_ids(self):
+        return ()
+
+    def layout(self):
+        from mstar_b200.config.layout import (AttentionSpec, BlockSpec, GatedMLPSpec,
+                                              ModelLayout, NormSpec, PositionSpec, RunEntry)
+        pos = PositionSpec("rope", self.HD, self.HD, 10000.0)
+        norm = NormSpec(size=self.H, eps=self.EPS)
+        ffn = GatedMLPSpec(self.H, self.INTER)
+
+        def attn(**kw):
+            return AttentionSpec(hidden_size=self.H, num_heads=self.NH, num_kv_heads=self.NKV,
+                                 head_dim=self.HD, position=pos, **kw)
+
+        blocks = [BlockSpec("prenorm", attn(), ffn, norm, norm),
+                  BlockSpec("prenorm", RunningMeanSpec(hidden_size=self.H), ffn, norm, norm),
+                  BlockSpec("prenorm", attn(shares_kv=True), ffn, norm, norm),
+                  BlockSpec("prenorm", attn(window=self.WINDOW), ffn, norm, norm)]
+        # block 2 reads the cache block 0 wrote; block 1 runs twice, with a state each time
+        order = [RunEntry(0, 0), RunEntry(1, 1), RunEntry(2, 0), RunEntry(3, 2), RunEntry(1, 3)]
+        return ModelLayout(vocab_size=self.VOCAB, hidden_size=self.H, blocks=blocks, order=order,
+                           final_norm=norm, tie_word_embeddings=True)
+
+
+def toy_checkpoint_map(config, layout):
+    from mstar_b200.engine.model import model_param_specs
+    from mstar_b200.weights.names import CheckpointMap, TensorSource
+
+    sources = [TensorSource("toy." + name, name, 0, spec.shape[0])
+               for name, spec in model_param_specs(layout).items()]
+    return CheckpointMap(sources=sources, aliases={"head.weight": "embed.weight"},
+                         optional=frozenset({"toy.head.weight"}))
+
+
+def toy_plain_logits(w, cfg: ToyConfig, ids):
+    """Whole-sequence plain forward of the toy model, from the plain part functions."""
+    T = len(ids)
+    pos = torch.arange(T)
+    rope_cfg = dict(head_dim=cfg.HD, rope_theta=10000.0, hidden_size=cfg.H,
+                    num_attention_heads=cfg.NH)
+    inv = P.plain_rope_frequencies(rope_cfg)
+    h = w["toy.embed.weight"].double()[torch.tensor(ids)]
+    kv_of_cache = {}
+
+    def heads(x, mat, n):
+        return (x @ mat.double().T).view(T, n, cfg.HD)
+
+    for block, cache in ((0, 0), (1, 1), (2, 0), (3, 2), (1, 3)):
+        p = f"toy.blocks.{block}"
+        x = P.plain_rms_norm(h, w[f"{p}.norm1.weight"], cfg.EPS)
+        if block == 1:
+            mean = torch.cumsum(x, 0) / torch.arange(1, T + 1)[:, None]
+            a = mean @ w[f"{p}.mixer.w.weight"].double().T
+        else:
+            nq = cfg.NH * cfg.HD
+            if block == 2:
+                q = P.plain_apply_rope(heads(x, w[f"{p}.mixer.q.weight"], cfg.NH), pos, inv)
+                k, v = kv_of_cache[cache]
+            else:
+                qkv = w[f"{p}.mixer.qkv.weight"]
+                nk = cfg.NKV * cfg.HD
+                q = P.plain_apply_rope(heads(x, qkv[:nq], cfg.NH), pos, inv)
+                k = P.plain_apply_rope(heads(x, qkv[nq:nq + nk], cfg.NKV), pos, inv)
+                v = heads(x, qkv[nq + nk:], cfg.NKV)
+                kv_of_cache[cache] = (k, v)
+            att = P.plain_attention(q, k, v, window=cfg.WINDOW if block == 3 else None)
+            a = att.reshape(T, nq) @ w[f"{p}.mixer.o.weight"].double().T
+        h = h + a
+        y = P.plain_rms_norm(h, w[f"{p}.norm2.weight"], cfg.EPS)
+        gu = w[f"{p}.ffn.gate_up.weight"]
+        h = h + P.plain_swiglu(y, gu[:cfg.INTER], gu[cfg.INTER:], w[f"{p}.ffn.down.weight"])
+    return P.plain_rms_norm(h, w["toy.final_norm.weight"], cfg.EPS) @ w["toy.embed.weight"].double().T
+
+
+@pytest.fixture
+def toy_registered():
+    from mstar_b200.config.registry import register_architecture, unregister_architecture
+    from mstar_b200.parts import register_part, unregister_part
+
+    register_part("mixer", "toy_running_mean", RunningMeanMixer)
+    register_architecture("ToyMixedForCausalLM", ToyConfig, toy_checkpoint_map)
+    yield
+    unregister_architecture("ToyMixedForCausalLM")
+    unregister_part("mixer", "toy_running_mean")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_architecture_is_registered_built_and_stepped(toy_registered, dtype):
+    import helpers as H
+    from mstar_b200.cache.storage import plan_groups
+    from mstar_b200.engine.model import load_model, model_param_specs
+    from mstar_b200.engine.step import make_stepper
+
+    cfg = ToyConfig()
+    layout = cfg.layout()
+    g = torch.Generator().manual_seed(5)
+    tensors = {}
+    for name, spec in model_param_specs(layout).items():
+        if name == "head.weight":
+            continue
+        if spec.init == "ones":
+            t = 1 + 0.1 * torch.randn(spec.shape, generator=g)
+        else:
+            t = 0.08 * torch.randn(spec.shape, generator=g)
+            if ".mixer.q" in name:
+                t[:cfg.NH * cfg.HD + (0 if name.endswith("q.weight") else cfg.NKV * cfg.HD)] *= 3
+        tensors["toy." + name] = t.to(torch.bfloat16)
+    model = load_model(None, dtype=dtype, device=DEV, config=cfg, tensors=tensors)
+    # two page groups (all keys / window of 8) and two state caches
+    windows, group_of = plan_groups(model.cache_needs)
+    assert windows == [None, 8] and group_of == [0, None, 1, None]
+    assert [n.state is not None for n in model.cache_needs] == [False, True, False, True]
+
+    reqs = {f"t{i}": H.request_tokens(cfg.VOCAB, n, seed=40 + i) for i, n in enumerate([3, 21, 50, 77])}
+    want = {}
+    for rid, toks in reqs.items():
+        logits = toy_plain_logits(tensors, cfg, toks)
+        want.update({(rid, i): logits[i] for i in range(len(toks))})
+    for steps, what in ((H.whole(reqs), "toy whole"), (H.portions(reqs), "toy portions"),
+                        (H.prefill_then_decode(reqs, 32), "toy prefill + decode"),
+                        (H.mixed(reqs, seed=2), "toy mixed")):
+        pages = H.max_tokens_of(steps, 4) // 4
+        stepper = make_stepper(model, page_size=4, num_pages=pages, num_slots=4)
+        assert stepper.storage.state_bytes_per_request() == 2 * cfg.H * 4
+        got = H.run_steps_in_process(stepper, steps)
+        H.compare(got, want, dtype, what)
+        mgr = stepper.manager
+        assert mgr.check() == 0 and mgr.free_pages(0) == pages and mgr.free_pages(1) == pages
+
+
+def test_llama_has_an_empty_state_slot(model_folders):
+    from mstar_b200.engine.model import load_model
+    from mstar_b200.engine.step import make_stepper
+
+    model = load_model(model_folders["tiny_a"][0], dtype="float32", device=DEV)
+    stepper = make_stepper(model, page_size=4, num_pages=4, num_slots=3)
+    assert stepper.storage.state_bytes_per_request() == 0
+    assert stepper.add_request("x") == 0 and stepper.manager.free_slots() == 2

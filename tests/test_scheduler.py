@@ -1,0 +1,193 @@
+"""The scheduler's decisions (CPU): admission, portions under a token budget, decode
+first, finishing, and pre-emption by recomputation when pages run out."""
+import pytest
+
+from mstar_b200.cache import CacheManager, GroupConfig
+from mstar_b200.engine.scheduler import Request, Scheduler, SchedulerConfig
+from mstar_b200.sampling import SamplingParams
+
+
+def make(pages=100, page=4, slots=8, budget=16, cap=None, batch=64, stops=(99,)):
+    cm = CacheManager([GroupConfig(page, pages)], num_slots=slots)
+    sch = Scheduler(SchedulerConfig(max_num_batched_tokens=budget, max_concurrent_requests=cap,
+                                    max_batch_size=batch), cm, stops)
+    return cm, sch
+
+
+def req(rid, n, max_out=4, **kw):
+    return Request(rid, list(range(1, n + 1)), SamplingParams(temperature=0.0,
+                                                              max_output_tokens=max_out, **kw))
+
+
+def run_step(cm, sch, token=7):
+    """What the engine does around one plan: reserve + commit, then report tokens."""
+    plan = sch.schedule()
+    ids = [e.request.request_id for e in plan.entries]
+    counts = [len(e.tokens) for e in plan.entries]
+    cm.reserve(ids, counts)
+    for i, c in zip(ids, counts):
+        cm.commit(i, c)
+    sampled = {e.request.request_id: (token(e.request) if callable(token) else token)
+               for e in plan.entries if e.samples}
+    done = sch.update(plan, sampled)
+    assert cm.check() == 0
+    return plan, done
+
+
+def test_prompt_is_cut_into_portions_under_the_budget():
+    cm, sch = make(budget=16)
+    sch.add(req("a", 40))
+    sizes = []
+    for _ in range(3):
+        plan, _ = run_step(cm, sch)
+        sizes.append([len(e.tokens) for e in plan.entries])
+        assert plan.num_tokens() <= 16
+    assert sizes == [[16], [16], [8]]
+    assert plan.entries[0].samples                     # the last portion samples
+    assert plan.entries[0].tokens == list(range(33, 41))
+    plan, _ = run_step(cm, sch)
+    assert [len(e.tokens) for e in plan.entries] == [1] and plan.entries[0].tokens == [7]
+
+
+def test_decoding_goes_first_and_prompts_fill_the_rest():
+    cm, sch = make(budget=16)
+    sch.add(req("a", 5, max_out=10))
+    run_step(cm, sch)                                  # a: whole prompt, now decoding
+    sch.add(req("b", 40))
+    plan, _ = run_step(cm, sch)
+    assert [(e.request.request_id, len(e.tokens)) for e in plan.entries] == [("a", 1), ("b", 15)]
+    plan, _ = run_step(cm, sch)
+    assert [(e.request.request_id, len(e.tokens)) for e in plan.entries] == [("a", 1), ("b", 15)]
+    assert not plan.entries[1].samples
+
+
+def test_admission_cap_and_first_come_order():
+    cm, sch = make(budget=64, cap=2)
+    for rid in "abc":
+        sch.add(req(rid, 3, max_out=2))
+    plan, _ = run_step(cm, sch)
+    assert [r.request_id for r in plan.admitted] == ["a", "b"]
+    plan, done = run_step(cm, sch)                     # a and b reach max_output_tokens
+    assert {r.request_id for r in done} == {"a", "b"} and all(r.finish_reason == "length"
+                                                             for r in done)
+    plan, _ = run_step(cm, sch)
+    assert [r.request_id for r in plan.admitted] == ["c"]
+    assert cm.num_requests() == 1
+
+
+def test_slots_limit_admission():
+    cm, sch = make(slots=1, budget=64)
+    sch.add(req("a", 3))
+    sch.add(req("b", 3))
+    plan, _ = run_step(cm, sch)
+    assert [r.request_id for r in plan.admitted] == ["a"] and len(sch.waiting) == 1
+
+
+def test_finishing_on_stop_token_and_ignore_eos():
+    cm, sch = make()
+    sch.add(req("a", 3, max_out=10))
+    sch.add(req("b", 3, max_out=3, ignore_eos=True))
+    plan, done = run_step(cm, sch, token=99)
+    assert [(r.request_id, r.finish_reason, r.output) for r in done] == [("a", "stop", [99])]
+    _, done = run_step(cm, sch, token=99)
+    assert done == []
+    _, done = run_step(cm, sch, token=99)
+    assert [(r.request_id, r.finish_reason, r.output) for r in done] == [
+        ("b", "length", [99, 99, 99])]
+    assert not sch.has_work() and cm.num_requests() == 0 and cm.free_pages() == 100
+
+
+def test_pages_run_out_the_newest_request_is_recomputed():
+    cm, sch = make(pages=6, page=4, budget=64)         # 24 tokens in all
+    sch.add(req("old", 8, max_out=12))
+    sch.add(req("new", 8, max_out=12))
+    plan, _ = run_step(cm, sch)                        # both prompts: 2 + 2 pages
+    assert len(plan.entries) == 2 and cm.free_pages() == 2
+    seen_preemption = None
+    for step in range(12):
+        plan, _ = run_step(cm, sch, token=lambda r: 50 + len(r.output))
+        if plan.preempted:
+            seen_preemption = step
+            break
+    assert seen_preemption is not None
+    victim = plan.preempted[0]
+    assert victim.request_id == "new" and victim.status == "waiting" and victim.num_computed == 0
+    assert sch.waiting[0] is victim and not cm.has("new")
+    assert [e.request.request_id for e in plan.entries] == ["old"]   # the older one went on
+    kept = list(victim.output)
+    # "new" comes back only when its prompt and what it generated fit again (here: when
+    # "old" has ended), and recomputes all of it in one portion
+    entry = None
+    while entry is None:
+        old_running = any(r.request_id == "old" for r in sch.running)
+        plan, _ = run_step(cm, sch, token=lambda r: 50 + len(r.output))
+        hits = [e for e in plan.entries if e.request.request_id == "new"]
+        entry = hits[0] if hits else None
+    assert not old_running
+    assert entry.tokens == victim.prompt + kept and entry.samples
+    assert victim.preemptions == 1
+    while sch.has_work():
+        run_step(cm, sch, token=lambda r: 50 + len(r.output))
+    assert [len(r.output) for r in sch.finished] == [12, 12] and cm.free_pages() == 6
+
+
+def test_prompts_never_take_the_pages_decoding_needs():
+    cm, sch = make(pages=4, page=4, budget=64)
+    sch.add(req("a", 7, max_out=8))
+    run_step(cm, sch)                                  # a holds 2 pages, 7 tokens
+    sch.add(req("b", 12))                              # would need 3 pages, 2 are free
+    plan, _ = run_step(cm, sch)
+    # a decodes (its 8th token fits its second page); b gets what is left: 2 pages = 8 tokens
+    assert [(e.request.request_id, len(e.tokens)) for e in plan.entries] == [("a", 1), ("b", 8)]
+
+
+def test_a_request_larger_than_the_pool_is_finished_not_starved():
+    cm, sch = make(pages=3, page=4, budget=64)
+    sch.add(req("huge", 30))
+    sch.add(req("ok", 4, max_out=1))
+    plan, done = run_step(cm, sch)
+    assert [(r.request_id, r.finish_reason) for r in plan.finished] == [("huge", "cache_exhausted")]
+    assert [r.request_id for r in done] == ["ok"]
+    # one that fits at first but outgrows the pool while decoding alone
+    sch.add(req("grow", 10, max_out=50))
+    reasons = []
+    for _ in range(10):
+        plan, done = run_step(cm, sch)
+        reasons += [r.finish_reason for r in plan.finished + done]
+        if not sch.has_work():
+            break
+    assert reasons == ["cache_exhausted"] and cm.free_pages() == 3 and cm.check() == 0
+
+
+def test_two_prompts_that_block_each_other():
+    cm, sch = make(pages=4, page=4, budget=6)          # each prompt needs 3 pages
+    sch.add(req("a", 12, max_out=1))
+    sch.add(req("b", 12, max_out=1))
+    finished = []
+    for _ in range(20):
+        plan, done = run_step(cm, sch)
+        finished += [r.request_id for r in done]
+        if not sch.has_work():
+            break
+    assert finished == ["a", "b"]                      # both complete, the older first
+
+
+def test_abort():
+    cm, sch = make()
+    sch.add(req("a", 3))
+    sch.add(req("b", 3))
+    run_step(cm, sch)
+    sch.add(req("c", 3))
+    assert sch.abort("c") and sch.abort("a") and not sch.abort("zzz")
+    assert [r.request_id for r in sch.running] == ["b"] and cm.num_requests() == 1
+    assert {r.request_id: r.finish_reason for r in sch.finished} == {"c": "abort", "a": "abort"}
+
+
+def test_batch_size_cap():
+    cm, sch = make(budget=64, batch=2)
+    for rid in "abc":
+        sch.add(req(rid, 2, max_out=5))
+    plan, _ = run_step(cm, sch)
+    assert len(plan.entries) == 2
+    plan, _ = run_step(cm, sch)
+    assert len(plan.entries) == 2
