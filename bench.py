@@ -1,0 +1,334 @@
+#!/usr/bin/env python3
+"""Headline benchmark: decode tokens/s of the Orpheus-3B-sized Llama decoder (random
+weights, bfloat16) at batch 8 with 2,048-token cached prompts, on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line on stdout.  ``value``: decoded tokens per second of the engine's step
+function plus greedy sampling, timed on the device with CUDA events.  ``e2e``: the same
+through the Python entry point (``LLM.step``), host token ids in and out.  ``prefill``:
+one 2,048-token prompt in one step.  ``roofline``: bytes a decode step has to read (every
+weight once, and the cache of the live requests) over its time, against the measured
+copy bandwidth.  ``points``: decode at batch 1 and 64.  A step is one decode step; every
+step reads all weights (6.6 GB), far more than the 126 MB L2, so no L2 flush is needed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+# Layer sizes of the benchmark model: Orpheus 3B / Llama 3.2 3B (BASELINE configs[2]).
+ORPHEUS_3B = dict(
+    architectures=["LlamaForCausalLM"], num_hidden_layers=28, hidden_size=3072,
+    num_attention_heads=24, num_key_value_heads=8, head_dim=128, intermediate_size=8192,
+    vocab_size=156940, tie_word_embeddings=True, rope_theta=500000.0,
+    rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                  "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    rms_norm_eps=1e-5, max_position_embeddings=131072, hidden_act="silu",
+    torch_dtype="bfloat16",
+)
+PROMPT_LEN = 2048
+CONTEXT = 4096
+PAGE_SIZE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def peaks() -> dict:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            raw = json.loads(path.read_text())
+            return {"hbm_gbs": float(raw["hbm_gbs"]), "bf16_tflops": float(raw["bf16_tflops"]),
+                    "source": "measured"}
+        except (KeyError, ValueError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS)
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+    NAMES = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+
+    def _run(self):
+        while not self._stop.is_set():
+            try:
+                out = subprocess.run(
+                    ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                     "--format=csv,noheader,nounits"], capture_output=True, text=True,
+                    timeout=5).stdout.strip().splitlines()[0]
+                parts = [p.strip() for p in out.split(",")]
+                self.samples.append(float(parts[0]))
+                self.max_mhz = float(parts[1])
+                for name, val in zip(self.NAMES, parts[2:]):
+                    if val.lower().startswith("active"):
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.2)
+
+    def __enter__(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=6)
+
+    def summary(self) -> dict:
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None,
+                "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+def flops_of_step(cfg: dict, q_lens, kv_lens, rows: int) -> float:
+    """Matrix and attention FLOPs of one step (2 per multiply-add)."""
+    L, H, I, V = (cfg["num_hidden_layers"], cfg["hidden_size"], cfg["intermediate_size"],
+                  cfg["vocab_size"])
+    nq, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    T = sum(q_lens)
+    per_token = (H * (nq + 2 * nkv) * hd) + (nq * hd * H) + 3 * H * I
+    linear = 2.0 * T * L * per_token + 2.0 * rows * H * V
+    attn = 0.0
+    for q, kv in zip(q_lens, kv_lens):
+        keys = sum(kv - q + i + 1 for i in range(q))     # causal: token i sees kv-q+i+1 keys
+        attn += 4.0 * nq * hd * keys
+    return linear + L * attn
+
+
+def bytes_of_decode_step(cfg: dict, model, kv_lens) -> float:
+    """Every weight used once (tied head counted once) plus keys and values read."""
+    nkv, hd, L = cfg["num_key_value_heads"], cfg["head_dim"], cfg["num_hidden_layers"]
+    kv = sum(kv_lens) * 2 * nkv * hd * 2 * L
+    return float(model.parameter_bytes() + kv)
+
+
+def build_model(cfg_raw: dict, seed: int = 0):
+    from mstar_b200.config.registry import config_from_dict
+    from mstar_b200.engine.model import load_model
+    from mstar_b200.weights.random_init import random_checkpoint
+
+    cfg = config_from_dict(cfg_raw)
+    tensors = random_checkpoint(cfg, seed, std=0.02, device="cuda:0")
+    model = load_model(None, dtype="bfloat16", device="cuda:0", config=cfg, tensors=tensors)
+    del tensors
+    return model
+
+
+def prompts(batch: int, vocab: int, length: int, seed: int = 1) -> list:
+    import torch
+
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (batch, length), generator=g).tolist()
+
+
+def time_decode(stepper, batch: int, cfg: dict, steps: int, warmup: int) -> dict:
+    """B requests with PROMPT_LEN cached tokens each; W + K decode steps of the step
+    function plus greedy sampling, K of them timed with CUDA events."""
+    import torch
+
+    from mstar_b200 import ops
+    from mstar_b200.engine.step import StepEntry
+    from mstar_b200.ops import lib
+
+    ids = [f"d{batch}-{i}" for i in range(batch)]
+    toks = prompts(batch, cfg["vocab_size"], PROMPT_LEN + warmup + steps + 1, seed=batch)
+    for rid, t in zip(ids, toks):
+        stepper.add_request(rid)
+        stepper.step([StepEntry(rid, t[:PROMPT_LEN], ())])
+    torch.cuda.synchronize()
+
+    def one(k: int):
+        logits = stepper.step([StepEntry(rid, [t[PROMPT_LEN + k]], (0,))
+                               for rid, t in zip(ids, toks)])
+        return ops.argmax(logits)
+
+    for k in range(warmup):
+        one(k)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = lib.launch_count()
+    start.record()
+    for k in range(warmup, warmup + steps):
+        one(k)
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    launches = lib.launch_count() - launches0
+    kv_lens = [PROMPT_LEN + warmup + steps // 2] * batch
+    for rid in ids:
+        stepper.free_request(rid)
+    return {"ms_per_step": ms, "tokens_per_s": batch / (ms / 1e3), "launches": launches,
+            "kv_lens": kv_lens}
+
+
+def time_prefill(stepper, cfg: dict, reps: int = 3) -> dict:
+    import torch
+
+    from mstar_b200.engine.step import StepEntry
+
+    toks = prompts(reps + 2, cfg["vocab_size"], PROMPT_LEN, seed=99)
+    times = []
+    for i, t in enumerate(toks):
+        rid = f"p{i}"
+        stepper.add_request(rid)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        stepper.step([StepEntry(rid, t, (PROMPT_LEN - 1,))])
+        end.record()
+        torch.cuda.synchronize()
+        stepper.free_request(rid)
+        if i >= 2:                                   # two warm-up prompts
+            times.append(start.elapsed_time(end))
+    ms = statistics.median(times)
+    return {"ms": ms, "tokens_per_s": PROMPT_LEN / (ms / 1e3),
+            "flops": flops_of_step(cfg, [PROMPT_LEN], [PROMPT_LEN], 1)}
+
+
+def time_e2e(model, batch: int, cfg: dict, steps: int, warmup: int, num_pages: int) -> dict:
+    """The same decode steps through the public entry point: host token ids in (pinned
+    index buffer copied to the device every step) and sampled token ids read back."""
+    import torch
+
+    from mstar_b200 import LLM, SamplingParams
+
+    llm = LLM(model, page_size=PAGE_SIZE, max_num_pages=num_pages,
+              max_num_batched_tokens=PROMPT_LEN, max_concurrent_requests=max(batch, 1),
+              max_batch_size=max(batch, 1))
+    params = SamplingParams(temperature=0.0, ignore_eos=True,
+                            max_output_tokens=warmup + steps + batch + 8)
+    for i, t in enumerate(prompts(batch, cfg["vocab_size"], PROMPT_LEN, seed=7 + batch)):
+        llm.add_request(t, params, request_id=f"e{i}")
+    while any(r.num_pending() > 1 for r in llm.scheduler.running) or llm.scheduler.waiting:
+        llm.step()                                   # prompts, one per step
+    for _ in range(warmup):
+        llm.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        llm.step()
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - t0
+    h2d = llm.stepper.last_h2d_bytes
+    for r in list(llm.scheduler.running):
+        llm.scheduler.abort(r.request_id)
+    return {"tokens_per_s": batch * steps / seconds, "ms_per_step": seconds / steps * 1e3,
+            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch}
+
+
+def reference_arm() -> int:
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "t-avil/mstar installs offline with --no-deps, but its stock path "
+                       "(mstar serve orpheus) fetches the checkpoint, its tokenizer and the SNAC "
+                       "codec from the Hugging Face hub and needs the mooncake and snac "
+                       "packages; there is no network and neither package is installed"}))
+    return 0
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None,
+                    help="fewer layers than the model has (named in the record)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return reference_arm()
+    if args.gpus != 1:
+        print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported")
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import torch
+
+    from mstar_b200.engine.step import make_stepper
+    from mstar_b200.ops import lib
+
+    cfg = dict(ORPHEUS_3B)
+    full_layers = cfg["num_hidden_layers"]
+    if args.layers:
+        cfg["num_hidden_layers"] = args.layers
+    pk = peaks()
+    print("[bench] building the random-weight model ...", file=sys.stderr, flush=True)
+    model = build_model(cfg)
+    max_batch = max(64, args.batch)
+    pages = max_batch * (CONTEXT // PAGE_SIZE) + 64
+    stepper = make_stepper(model, page_size=PAGE_SIZE, num_pages=pages, num_slots=max_batch + 4)
+
+    print("[bench] prefill ...", file=sys.stderr, flush=True)
+    pre = time_prefill(stepper, cfg)
+    print("[bench] decode ...", file=sys.stderr, flush=True)
+    with ClockSampler() as clocks:
+        head = time_decode(stepper, args.batch, cfg, args.steps, warmup)
+    points = {}
+    for b in (1, 64):
+        r = time_decode(stepper, b, cfg, max(args.steps // 2, 8), warmup)
+        points[f"decode_b{b}"] = round(r["tokens_per_s"], 1)
+    del stepper
+    torch.cuda.empty_cache()
+    print("[bench] end to end ...", file=sys.stderr, flush=True)
+    e2e = time_e2e(model, args.batch, cfg, args.steps, warmup,
+                   args.batch * (CONTEXT // PAGE_SIZE) + 64)
+
+    step_bytes = bytes_of_decode_step(cfg, model, head["kv_lens"])
+    achieved = step_bytes / (head["ms_per_step"] / 1e3) / 1e9
+    record = {
+        "metric": "decode tok/s at batch 8 (Orpheus 3B bf16, 2,048-token cached prompts)",
+        "value": round(head["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": warmup, "ms_per_step": round(head["ms_per_step"], 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic token ids, random-init weights N(0, 0.02)",
+        "config": {
+            "model": "Orpheus 3B / Llama 3.2 3B", "global_batch": args.batch,
+            "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "parallelism": "single GPU",
+            "layers": cfg["num_hidden_layers"], "layers_of_model": full_layers,
+            "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
+            "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
+            "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+            "tied_embeddings": True, "rope": "theta 5e5, llama3 x32 (1, 4, 8192)",
+            "rms_eps": cfg["rms_norm_eps"], "page_size": PAGE_SIZE,
+            "l2": "inputs larger than L2 (weights 6.6 GB per step)",
+            "peaks": pk["source"]},
+        "e2e": {"value": round(e2e["tokens_per_s"], 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": e2e["h2d_bytes_per_step"],
+                "d2h_bytes_per_step": e2e["d2h_bytes_per_step"],
+                "ms_per_step": round(e2e["ms_per_step"], 4)},
+        "gpu_launches": head["launches"],
+        "clocks": clocks.summary(),
+        "prefill": {"value": round(pre["tokens_per_s"], 1), "tokens": PROMPT_LEN,
+                    "ms": round(pre["ms"], 3),
+                    "frac": round(pre["flops"] / (pre["ms"] / 1e3) / (pk["bf16_tflops"] * 1e12), 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "libraries": sorted(lib.loaded_libraries()),
+    }
+    print(json.dumps(record))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -43,6 +43,7 @@ class Stepper:
         self.manager = storage.manager
         self.device = model.runtime.device
         self.steps = 0
+        self.last_h2d_bytes = 0
 
     # -- requests ---------------------------------------------------------
     def add_request(self, request: Hashable) -> int:
@@ -103,6 +104,7 @@ class Stepper:
 
         dev = torch.empty(index.packed.size, dtype=torch.int32, device=self.device)
         dev.copy_(self._staging[:index.packed.size], non_blocking=True)
+        self.last_h2d_bytes = index.packed.size * 4
 
         def view(name: str) -> torch.Tensor:
             off, length = index.offsets[name]

@@ -76,7 +76,17 @@ def loaded_libraries() -> dict:
     return {name: lib._name for name, lib in _libs.items()}
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """Kernel launches of this package's own libraries since the process began."""
+    return _launches
+
+
 def check(code: int, what: str) -> None:
+    global _launches
+    _launches += 1
     if code == 0:
         return
     if code < 0:
