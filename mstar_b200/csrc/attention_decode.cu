@@ -1,0 +1,304 @@
+// Split-K paged grouped-query decode attention in bfloat16: one query token per
+// request, keys and values streamed from cache pages.
+//
+// The work of one (token, kv head) is cut along the keys into `splits` chunks; each
+// CTA streams its chunk through shared memory in tiles of 64 keys (cp.async, two
+// stages), its four warps take 16 keys each, compute S = Q K^T and O += P V with
+// m16n8k16 tensor-core MMAs (the group of query heads padded to the 16 rows of the
+// tile) and keep an online softmax in float.  Warps are merged in shared memory; if
+// the keys were split, partial (max, sum, O) go to a scratch buffer and a second
+// kernel merges them.  Decode attention is bound by the bytes of the cache, so the
+// padded rows cost nothing that matters.
+//
+// Semantics are those of attention_generic.cu: scale, causal end-aligned mask,
+// optional window, float softmax.  The reference calls a library for this
+// (mstar/utils/flashinfer_utils.py:348-366, 452-465).
+#include "common.cuh"
+#include "mma_util.cuh"
+
+#define DEC_THREADS 128
+#define DEC_TILE 64
+
+struct DecodeArgs {
+    const bf16* q;
+    const bf16* kv;
+    const int* block_table;
+    const int* token_req;
+    const int* cache_pos;
+    float* part_o;   // [tokens, nq, splits, HD]
+    float* part_ml;  // [tokens, nq, splits, 2]
+    bf16* out;       // [tokens, nq * HD]
+    int q_stride, bt_stride, nq, nkv, page_size, window, chunk, splits;
+    float scale_log2e;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(DEC_THREADS) decode_attention_kernel(DecodeArgs a) {
+    constexpr int CPR = HD / 8;  // 16-byte chunks per row
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);  // [16][HD]
+    bf16* stages = Qs + 16 * HD;                   // [2]{K [64][HD], V [64][HD]}
+
+    const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = a.nq / a.nkv;
+
+    const int hi = a.cache_pos[t] + 1;
+    const int lo = (a.window > 0 && hi > a.window) ? hi - a.window : 0;
+    const int ks = lo + split * a.chunk;
+    const int ke = min(hi, ks + a.chunk);
+    if (ks >= ke) return;  // this token has fewer chunks than the launch has splits
+
+    const int* bt = a.block_table + (size_t)a.token_req[t] * a.bt_stride;
+    const size_t page_elems = (size_t)2 * a.nkv * a.page_size * HD;
+    const size_t head_off = (size_t)kvh * a.page_size * HD;
+    const size_t v_off = (size_t)a.nkv * a.page_size * HD;
+
+    // ---- queries of the group -> shared, rows beyond the group are zero
+    const bf16* qrow = a.q + (size_t)t * a.q_stride + (size_t)kvh * G * HD;
+    for (int i = tid; i < 16 * CPR; i += DEC_THREADS) {
+        const int r = i / CPR, c = i - r * CPR;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < G) v = *reinterpret_cast<const uint4*>(qrow + (size_t)r * HD + c * 8);
+        *reinterpret_cast<uint4*>(Qs + tile_off<CPR>(r, c)) = v;
+    }
+
+    auto load_tile = [&](int stage, int base) {
+        bf16* Ks = stages + (size_t)stage * 2 * DEC_TILE * HD;
+        bf16* Vs = Ks + DEC_TILE * HD;
+        for (int i = tid; i < DEC_TILE * CPR; i += DEC_THREADS) {
+            const int r = i / CPR, c = i - r * CPR;
+            const int key = base + r;
+            const bool ok = key < ke;
+            const bf16* src = a.kv;
+            if (ok) {
+                const int page = bt[key / a.page_size];
+                const int slot = key - (key / a.page_size) * a.page_size;
+                src = a.kv + (size_t)page * page_elems + head_off + (size_t)slot * HD + c * 8;
+            }
+            const int off = tile_off<CPR>(r, c);
+            cp_async_16(smem_u32(Ks + off), src, ok ? 16 : 0);
+            cp_async_16(smem_u32(Vs + off), ok ? src + v_off : src, ok ? 16 : 0);
+        }
+    };
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;  // rows g and g+8 of the tile
+
+    const int ntiles = (ke - ks + DEC_TILE - 1) / DEC_TILE;
+    load_tile(0, ks);
+    cp_async_commit();
+    for (int it = 0; it < ntiles; ++it) {
+        if (it + 1 < ntiles) load_tile((it + 1) & 1, ks + (it + 1) * DEC_TILE);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        const bf16* Ks = stages + (size_t)(it & 1) * 2 * DEC_TILE * HD;
+        const bf16* Vs = Ks + DEC_TILE * HD;
+        const int key0 = ks + it * DEC_TILE + warp * 16;  // first key of this warp's 16
+        if (key0 < ke) {
+            // ---- S[16 heads x 16 keys] = Q K^T
+            float s[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                uint32_t qa[4], kb[4];
+                const int arow = (lane & 7) + ((lane >> 3) & 1) * 8;
+                ldmatrix_x4(qa, smem_u32(Qs + tile_off<CPR>(arow, 2 * kk + (lane >> 4))));
+                const int brow = warp * 16 + (lane & 7) + (lane >> 4) * 8;
+                ldmatrix_x4(kb, smem_u32(Ks + tile_off<CPR>(brow, 2 * kk + ((lane >> 3) & 1))));
+                mma_bf16_16816(s[0], qa, kb[0], kb[1]);
+                mma_bf16_16816(s[1], qa, kb[2], kb[3]);
+            }
+            // ---- scale (log2 domain), mask the tail, online softmax per head row
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
+                    const float v = key < ke ? s[j][e] * a.scale_log2e : -INFINITY;
+                    s[j][e] = v;
+                    if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+                }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);  // finite: key0 is valid
+            const float al0 = exp2f(m0 - mn0), al1 = exp2f(m1 - mn1);
+            m0 = mn0;
+            m1 = mn1;
+            float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                s[j][0] = exp2f(s[j][0] - mn0);
+                s[j][1] = exp2f(s[j][1] - mn0);
+                s[j][2] = exp2f(s[j][2] - mn1);
+                s[j][3] = exp2f(s[j][3] - mn1);
+                ps0 += s[j][0] + s[j][1];
+                ps1 += s[j][2] + s[j][3];
+            }
+            l0 = l0 * al0 + ps0;
+            l1 = l1 * al1 + ps1;
+#pragma unroll
+            for (int n = 0; n < HD / 8; ++n) {
+                o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1;
+            }
+            // ---- O[16 heads x HD] += P[16 x 16 keys] V[16 keys x HD]
+            uint32_t pa[4];
+            pa[0] = pack_bf16(s[0][0], s[0][1]);
+            pa[1] = pack_bf16(s[0][2], s[0][3]);
+            pa[2] = pack_bf16(s[1][0], s[1][1]);
+            pa[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+            for (int n2 = 0; n2 < HD / 16; ++n2) {
+                uint32_t vb[4];
+                const int vrow = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                ldmatrix_x4_trans(vb, smem_u32(Vs + tile_off<CPR>(vrow, 2 * n2 + (lane >> 4))));
+                mma_bf16_16816(o[2 * n2], pa, vb[0], vb[1]);
+                mma_bf16_16816(o[2 * n2 + 1], pa, vb[2], vb[3]);
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+
+    // ---- merge the four warps (the stage buffers are free now)
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    float* Om = reinterpret_cast<float*>(stages);  // [4][16][HD]
+    float* MLm = Om + 4 * 16 * HD;                 // [4][16][2]
+    const int r0 = lane >> 2;
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        const int col = n * 8 + (lane & 3) * 2;
+        float* p0 = Om + ((size_t)warp * 16 + r0) * HD + col;
+        p0[0] = o[n][0];
+        p0[1] = o[n][1];
+        float* p1 = p0 + 8 * HD;
+        p1[0] = o[n][2];
+        p1[1] = o[n][3];
+    }
+    if ((lane & 3) == 0) {
+        MLm[(warp * 16 + r0) * 2 + 0] = m0;
+        MLm[(warp * 16 + r0) * 2 + 1] = l0;
+        MLm[(warp * 16 + r0 + 8) * 2 + 0] = m1;
+        MLm[(warp * 16 + r0 + 8) * 2 + 1] = l1;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * HD; idx += DEC_THREADS) {
+        const int g = idx / HD, d = idx - g * HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, MLm[(w * 16 + g) * 2]);
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = MLm[(w * 16 + g) * 2];
+            const float wgt = mw == -INFINITY ? 0.f : exp2f(mw - m);
+            acc += wgt * Om[((size_t)w * 16 + g) * HD + d];
+            L += wgt * MLm[(w * 16 + g) * 2 + 1];
+        }
+        const int head = kvh * G + g;
+        if (a.splits == 1) {
+            a.out[(size_t)t * a.nq * HD + (size_t)head * HD + d] = __float2bfloat16_rn(acc / L);
+        } else {
+            const size_t slot = ((size_t)t * a.nq + head) * a.splits + split;
+            a.part_o[slot * HD + d] = acc;
+            if (d == 0) {
+                a.part_ml[slot * 2] = m;
+                a.part_ml[slot * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+// Merge the partial results of the splits of one (token, head).
+template <int HD>
+__global__ void decode_merge_kernel(DecodeArgs a) {
+    const int head = blockIdx.x, t = blockIdx.y;
+    const int hi = a.cache_pos[t] + 1;
+    const int lo = (a.window > 0 && hi > a.window) ? hi - a.window : 0;
+    const int n = min(a.splits, (hi - lo + a.chunk - 1) / a.chunk);
+    const size_t base = ((size_t)t * a.nq + head) * a.splits;
+    float m = -INFINITY;
+    for (int s = 0; s < n; ++s) m = fmaxf(m, a.part_ml[(base + s) * 2]);
+    float L = 0.f;
+    for (int s = 0; s < n; ++s) L += a.part_ml[(base + s) * 2 + 1] * exp2f(a.part_ml[(base + s) * 2] - m);
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < n; ++s)
+            acc += a.part_o[(base + s) * HD + d] * exp2f(a.part_ml[(base + s) * 2] - m);
+        a.out[(size_t)t * a.nq * HD + (size_t)head * HD + d] = __float2bfloat16_rn(acc / L);
+    }
+}
+
+template <int HD> static int launch_decode(const DecodeArgs& a, int tokens, cudaStream_t s) {
+    const size_t smem = (size_t)(16 * HD + 2 * 2 * DEC_TILE * HD) * sizeof(bf16);
+    static_assert((size_t)(4 * 16 * HD + 4 * 16 * 2) * sizeof(float) <=
+                      (size_t)(2 * 2 * DEC_TILE * HD) * sizeof(bf16),
+                  "merge buffer must fit in the stage buffers");
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<HD>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    dim3 grid(a.splits, a.nkv, tokens);
+    decode_attention_kernel<HD><<<grid, DEC_THREADS, smem, s>>>(a);
+    if (a.splits > 1) {
+        dim3 mgrid(a.nq, tokens);
+        decode_merge_kernel<HD><<<mgrid, HD < 128 ? HD : 128, 0, s>>>(a);
+    }
+    return launch_status();
+}
+
+// Scratch floats needed for `tokens` query tokens cut into `splits` chunks.
+MSTAR_API long long mstar_decode_attention_scratch_floats(int tokens, int nq, int hd, int splits) {
+    return splits <= 1 ? 0 : (long long)tokens * nq * splits * (hd + 2);
+}
+
+// Returns 0, a CUDA error code, or -1 when the shape is refused (head_dim not one of
+// 16/32/64/128/256, more than 16 query heads per kv head, chunk no multiple of 64).
+MSTAR_API int mstar_paged_decode_attention_bf16(
+    const void* q, int q_stride, void* out, const void* kv_cache, const int* block_table,
+    int bt_stride, const int* token_req, const int* cache_pos, int tokens, int nq, int nkv, int hd,
+    int page_size, int window, float scale, int chunk, int splits, float* scratch, void* stream) {
+    if (tokens <= 0) return 0;
+    if (nkv <= 0 || nq % nkv != 0 || nq / nkv > 16) return -1;
+    if (chunk <= 0 || chunk % DEC_TILE != 0 || splits < 1) return -1;
+    if (splits > 1 && scratch == nullptr) return -1;
+    if (tokens > 65535 || nkv > 65535) return -1;
+    DecodeArgs a;
+    a.q = (const bf16*)q;
+    a.kv = (const bf16*)kv_cache;
+    a.block_table = block_table;
+    a.token_req = token_req;
+    a.cache_pos = cache_pos;
+    a.part_o = scratch;
+    a.part_ml = scratch ? scratch + (size_t)tokens * nq * splits * hd : nullptr;
+    a.out = (bf16*)out;
+    a.q_stride = q_stride;
+    a.bt_stride = bt_stride;
+    a.nq = nq;
+    a.nkv = nkv;
+    a.page_size = page_size;
+    a.window = window;
+    a.chunk = chunk;
+    a.splits = splits;
+    a.scale_log2e = scale * 1.4426950408889634f;
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (hd) {
+        case 16: return launch_decode<16>(a, tokens, s);
+        case 32: return launch_decode<32>(a, tokens, s);
+        case 64: return launch_decode<64>(a, tokens, s);
+        case 128: return launch_decode<128>(a, tokens, s);
+        case 256: return launch_decode<256>(a, tokens, s);
+        default: return -1;
+    }
+}

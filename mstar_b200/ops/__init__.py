@@ -152,6 +152,75 @@ def paged_attention_generic(q: torch.Tensor, q_stride: int, out: torch.Tensor, k
     check(code, "paged_attention_generic")
 
 
+FAST_ATTENTION_HEAD_DIMS = (16, 32, 64, 128, 256)
+NUM_SMS = 148
+
+
+def fast_attention_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int,
+                             head_dim: int) -> bool:
+    """Whether the tensor-core attention kernels take this shape (else the generic
+    kernel does)."""
+    return (dtype == torch.bfloat16 and head_dim in FAST_ATTENTION_HEAD_DIMS
+            and num_heads % num_kv_heads == 0 and num_heads // num_kv_heads <= 16)
+
+
+def decode_split(tokens: int, num_kv_heads: int, max_len: int) -> tuple:
+    """(chunk, splits) of the keys for split-K decode attention: enough CTAs to fill
+    the GPU a few times over, chunks in whole tiles of 64 keys."""
+    pairs = max(tokens * num_kv_heads, 1)
+    want = max(1, -(-NUM_SMS * 6 // pairs))
+    chunk = max(64, -(-(-(-max_len // want)) // 64) * 64)
+    splits = max(1, -(-max_len // chunk))
+    return chunk, splits
+
+
+def paged_decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv_cache,
+                           block_table, token_req, cache_pos, tokens: int, num_heads: int,
+                           num_kv_heads: int, head_dim: int, page_size: int, window: int,
+                           scale: float, max_len: int) -> None:
+    """bfloat16 attention of ``tokens`` single-query rows (token i of q/out/token_req/
+    cache_pos); ``max_len`` bounds the keys any of them sees."""
+    _need_cuda(q, out, kv_cache, block_table, token_req, cache_pos)
+    assert q.dtype == torch.bfloat16 and kv_cache.dtype == torch.bfloat16
+    assert (q_stride * 2) % 16 == 0 and q.data_ptr() % 16 == 0 and out.is_contiguous()
+    if window:
+        max_len = min(max_len, window)
+    chunk, splits = decode_split(tokens, num_kv_heads, max(max_len, 1))
+    scratch = None
+    if splits > 1:
+        scratch = torch.empty(tokens * num_heads * splits * (head_dim + 2), dtype=torch.float32,
+                              device=q.device)
+    code = lib.get("attention_decode").mstar_paged_decode_attention_bf16(
+        q.data_ptr(), q_stride, out.data_ptr(), kv_cache.data_ptr(), block_table.data_ptr(),
+        block_table.stride(0), token_req.data_ptr(), cache_pos.data_ptr(), tokens, num_heads,
+        num_kv_heads, head_dim, page_size, window, float(scale), chunk, splits, _ptr(scratch),
+        _stream())
+    if code == -1:
+        raise KernelError(f"decode attention refuses heads={num_heads}, kv_heads={num_kv_heads}, "
+                          f"head_dim={head_dim} (head_dim in {FAST_ATTENTION_HEAD_DIMS}, at most "
+                          "16 query heads per kv head)")
+    check(code, "paged_decode_attention")
+
+
+def paged_prefill_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv_cache,
+                            block_table, qo_indptr, kv_len, first_entry: int, entries: int,
+                            max_q_len: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                            page_size: int, window: int, scale: float) -> None:
+    """bfloat16 attention of the new tokens of batch entries [first_entry, first_entry +
+    entries); q and out hold all tokens of the step, indexed through qo_indptr."""
+    _need_cuda(q, out, kv_cache, block_table, qo_indptr, kv_len)
+    assert q.dtype == torch.bfloat16 and kv_cache.dtype == torch.bfloat16
+    assert (q_stride * 2) % 16 == 0 and q.data_ptr() % 16 == 0 and out.is_contiguous()
+    code = lib.get("attention_prefill").mstar_paged_prefill_attention_bf16(
+        q.data_ptr(), q_stride, out.data_ptr(), kv_cache.data_ptr(), block_table.data_ptr(),
+        block_table.stride(0), qo_indptr.data_ptr(), kv_len.data_ptr(), first_entry, entries,
+        max_q_len, num_heads, num_kv_heads, head_dim, page_size, window, float(scale), _stream())
+    if code == -1:
+        raise KernelError(f"prefill attention refuses heads={num_heads}, kv_heads={num_kv_heads}, "
+                          f"head_dim={head_dim} (head_dim in {FAST_ATTENTION_HEAD_DIMS})")
+    check(code, "paged_prefill_attention")
+
+
 def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out=None):
     """a[M,K] @ w[N,K]^T in true float32 (FMA, no tensor-core reduced precision)."""
     _need_cuda(a, w)

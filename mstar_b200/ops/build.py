@@ -32,6 +32,8 @@ HOST_FLAGS = ["-O2", "-std=c++17", "-shared", "-fPIC", "-fvisibility=hidden", "-
 LIBRARIES = {
     "elementwise": ("cuda", ["elementwise.cu"], []),
     "attention_generic": ("cuda", ["attention_generic.cu"], []),
+    "attention_decode": ("cuda", ["attention_decode.cu"], []),
+    "attention_prefill": ("cuda", ["attention_prefill.cu"], []),
     "gemm_f32": ("cuda", ["gemm_f32.cu"], []),
     "sampling": ("cuda", ["sampling.cu"], []),
     "host": ("host", ["host/cache_manager.cpp"], []),
@@ -164,6 +166,12 @@ def build_library(name: str, *, force: bool = False) -> Path:
                 pass
             raise BuildError(f"{what} failed (exit {proc.returncode}):\n{' '.join(cmd)}\n{output}")
         os.replace(tmp, out)
+        for stale in out.parent.glob(f"libmstar_{name}-*.so"):
+            if stale != out:
+                try:
+                    stale.unlink()
+                except OSError:
+                    pass
         _log(f"  built {out.name} in {time.time() - start:.1f} s")
         return out
 

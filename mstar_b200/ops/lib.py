@@ -31,6 +31,14 @@ _SIGNATURES = {
         "mstar_paged_attention_generic": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i,
                                           _i, _i, _f, _i, _vp],
     },
+    "attention_decode": {
+        "mstar_paged_decode_attention_bf16": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i,
+                                              _i, _i, _i, _f, _i, _i, _vp, _vp],
+    },
+    "attention_prefill": {
+        "mstar_paged_prefill_attention_bf16": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i,
+                                               _i, _i, _i, _i, _i, _f, _vp],
+    },
     "gemm_f32": {
         "mstar_sgemm_nt": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     },

@@ -59,7 +59,24 @@ class Attention:
         return ops.linear(out, self.w_out)
 
     def attend(self, qkv, out, ctx: StepContext, cache: LayerCache) -> None:
+        """bfloat16 with a head size the tensor-core kernels take: single-token entries
+        (they come first in the batch) go to the split-K decode kernel, prompt portions
+        to the prefill kernel.  Everything else, float32 included, runs the generic
+        kernel."""
         s = self.spec
+        if ops.fast_attention_supported(qkv.dtype, s.num_heads, s.num_kv_heads, s.head_dim):
+            nd = ctx.num_decode
+            if nd:
+                ops.paged_decode_attention(
+                    qkv, qkv.stride(0), out, cache.kv, cache.block_table, ctx.token_req,
+                    ctx.cache_pos, nd, s.num_heads, s.num_kv_heads, s.head_dim,
+                    cache.page_size, s.window or 0, self.scale, max(ctx.kv_lens[:nd]))
+            if ctx.num_entries > nd:
+                ops.paged_prefill_attention(
+                    qkv, qkv.stride(0), out, cache.kv, cache.block_table, ctx.qo_indptr,
+                    ctx.kv_len, nd, ctx.num_entries - nd, max(ctx.q_lens[nd:]), s.num_heads,
+                    s.num_kv_heads, s.head_dim, cache.page_size, s.window or 0, self.scale)
+            return
         ops.paged_attention_generic(
             qkv, qkv.stride(0), out, cache.kv, cache.block_table, ctx.token_req, ctx.cache_pos,
             ctx.num_tokens, s.num_heads, s.num_kv_heads, s.head_dim, cache.page_size,

@@ -140,7 +140,8 @@ def test_rope_kv_write(act, nq, nkv, hd, rot, inter):
 
 
 # ----------------------------------------------------------------------- attention
-def paged_case(lens_q, lens_kv, nq, nkv, hd, page, act, seed, window=0, spike=None):
+def paged_case(lens_q, lens_kv, nq, nkv, hd, page, act, seed, window=0, spike=None,
+               kernel="generic"):
     """Random q and paged k/v for requests with lens_kv keys of which the last lens_q are
     this step's queries; pages are handed out in a scrambled order.  ``spike`` =
     (request, key index): that key is made to dominate every query's softmax."""
@@ -181,8 +182,24 @@ def paged_case(lens_q, lens_kv, nq, nkv, hd, page, act, seed, window=0, spike=No
                               for i in range(lens_q[r])], dtype=torch.int32)
     out = torch.empty(T, nq * hd, dtype=act, device=DEV)
     qd = q.reshape(T, nq * hd).to(DEV).contiguous()
-    ops.paged_attention_generic(qd, nq * hd, out, kv.to(DEV), table.to(DEV), token_req.to(DEV),
-                                cache_pos.to(DEV), T, nq, nkv, hd, page, window, hd ** -0.5)
+    if kernel == "generic":
+        ops.paged_attention_generic(qd, nq * hd, out, kv.to(DEV), table.to(DEV),
+                                    token_req.to(DEV), cache_pos.to(DEV), T, nq, nkv, hd, page,
+                                    window, hd ** -0.5)
+    elif kernel == "decode":
+        assert all(n == 1 for n in lens_q)
+        ops.paged_decode_attention(qd, nq * hd, out, kv.to(DEV), table.to(DEV), token_req.to(DEV),
+                                   cache_pos.to(DEV), T, nq, nkv, hd, page, window, hd ** -0.5,
+                                   max(lens_kv))
+    else:
+        indptr = [0]
+        for n in lens_q:
+            indptr.append(indptr[-1] + n)
+        ops.paged_prefill_attention(
+            qd, nq * hd, out, kv.to(DEV), table.to(DEV),
+            torch.tensor(indptr, dtype=torch.int32, device=DEV),
+            torch.tensor(lens_kv, dtype=torch.int32, device=DEV), 0, n_req, max(lens_q), nq, nkv,
+            hd, page, window, hd ** -0.5)
     # plain reference: whole-sequence attention with the queries placed at the end
     want = torch.empty(T, nq, hd, dtype=torch.float64)
     t0 = 0
@@ -223,6 +240,72 @@ def test_paged_attention_window_edge(act):
         assert (got - want).abs().max() < tol(act, f32=2e-5, bf16=2e-2)
         hit = (got[0, 0] - vs[0][spike_key, 0].double()).abs().max() < 3e-2
         assert bool(hit) == inside
+
+
+SHAPES_FAST = [(6, 2, 64, 4), (5, 1, 32, 16), (3, 3, 16, 8), (24, 8, 128, 16), (2, 1, 256, 2),
+               (16, 1, 64, 16)]
+
+
+@pytest.mark.parametrize("nq,nkv,hd,page", SHAPES_FAST)
+def test_decode_attention_kernel(nq, nkv, hd, page):
+    # lengths around tile (64) and chunk edges, one long enough to be split many times
+    lens = [1, 63, 64, 65, 200, 1500, 17]
+    got, want, _ = paged_case([1] * len(lens), lens, nq, nkv, hd, page, torch.bfloat16,
+                              seed=nq + hd, kernel="decode")
+    assert (got - want).abs().max() < 2e-2
+    got, want, _ = paged_case([1], [3000], nq, nkv, hd, page, torch.bfloat16, seed=3,
+                              kernel="decode")              # one request: as many splits as fit
+    assert (got - want).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("nq,nkv,hd,page", SHAPES_FAST)
+def test_prefill_attention_kernel(nq, nkv, hd, page):
+    # whole prompts, portions appended to cached keys, single tokens, sizes around 64 rows
+    lens_q = [1, 7, 40, 2, 65, 130, 33]
+    lens_kv = [33, 7, 75, 130, 65, 300, 33]
+    got, want, _ = paged_case(lens_q, lens_kv, nq, nkv, hd, page, torch.bfloat16, seed=nq * 7 + hd,
+                              kernel="prefill")
+    assert (got - want).abs().max() < 2e-2
+
+
+@pytest.mark.parametrize("kernel", ["decode", "prefill"])
+def test_fast_attention_far_key_and_window(kernel):
+    act = torch.bfloat16
+    got, want, vs = paged_case([1, 1], [700, 650], 6, 2, 32, 8, act, seed=11, spike=(0, 3),
+                               kernel=kernel)
+    assert (got - want).abs().max() < 2e-2
+    for h in range(6):
+        assert (got[0, h] - vs[0][3, h // 3].double()).abs().max() < 3e-2
+    for spike_key, inside in ((80, True), (79, False)):
+        got, want, vs = paged_case([1], [100], 4, 2, 32, 8, act, seed=13, window=20,
+                                   spike=(0, spike_key), kernel=kernel)
+        assert (got - want).abs().max() < 2e-2
+        hit = (got[0, 0] - vs[0][spike_key, 0].double()).abs().max() < 3e-2
+        assert bool(hit) == inside
+    if kernel == "prefill":
+        # a portion of 50 tokens with a window of 20 over 300 keys: every row has its own edge
+        got, want, _ = paged_case([50, 9], [300, 9], 4, 2, 64, 16, act, seed=17, window=20,
+                                  kernel="prefill")
+        assert (got - want).abs().max() < 2e-2
+    else:
+        got, want, _ = paged_case([1, 1, 1], [300, 9, 150], 4, 2, 64, 16, act, seed=17,
+                                  window=100, kernel="decode")
+        assert (got - want).abs().max() < 2e-2
+
+
+def test_fast_attention_refuses_other_head_sizes():
+    from mstar_b200 import ops
+
+    assert not ops.fast_attention_supported(torch.bfloat16, 4, 2, 48)
+    assert not ops.fast_attention_supported(torch.float32, 4, 2, 64)
+    assert not ops.fast_attention_supported(torch.bfloat16, 34, 2, 64)
+    assert ops.fast_attention_supported(torch.bfloat16, 24, 8, 128)
+    q = torch.zeros(1, 4 * 48, dtype=torch.bfloat16, device=DEV)
+    z = torch.zeros(1, dtype=torch.int32, device=DEV)
+    with pytest.raises(ops.KernelError, match="refuses"):
+        ops.paged_decode_attention(q, 4 * 48, q.clone(),
+                                   torch.zeros(1, 2, 2, 4, 48, dtype=torch.bfloat16, device=DEV),
+                                   z.view(1, 1), z, z, 1, 4, 2, 48, 4, 0, 1.0, 1)
 
 
 def test_paged_attention_refuses_what_it_cannot_do():
