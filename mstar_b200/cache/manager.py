@@ -244,21 +244,37 @@ class CacheManager:
         return int(self._lib.cm_check(self._h))
 
     # -- per-step index arrays ---------------------------------------------
+    def batch_widths(self, requests: Sequence[Hashable]) -> list:
+        """Logical pages of the longest block table of the batch, per group."""
+        rids = _i64([self._rid(r) for r in requests])
+        widths_c = _i32([0] * max(1, len(self.groups)))
+        rc = self._lib.cm_batch_widths(self._h, len(requests), rids, widths_c)
+        if rc != _OK:
+            raise RuntimeError(f"cm_batch_widths failed with {rc}")
+        return [int(widths_c[g]) for g in range(len(self.groups))]
+
     def fill_batch(self, requests: Sequence[Hashable], n_new: Sequence[int],
-                   extra: Sequence[tuple] = (), alloc=None) -> BatchIndex:
+                   extra: Sequence[tuple] = (), alloc=None, *, widths=None,
+                   pad_entries: int = 0, pad_page: int = 0, pad_slot: int = 0) -> BatchIndex:
         """Index arrays for a batch whose pages are reserved, packed in one int32
         buffer so that one copy brings them to the device.  ``extra``: further
         (name, length) sections the caller fills itself (token ids, wanted rows);
-        ``alloc(n)`` returns the int32 array to pack into (pinned memory)."""
+        ``alloc(n)`` returns the int32 array to pack into (pinned memory).
+
+        For batches of a fixed shape (CUDA graphs): ``widths`` fixes the row length
+        of each group's block table, and ``pad_entries`` appends entries of one token
+        each at position 0 whose only page is ``pad_page`` and whose slot is
+        ``pad_slot`` (a page and a slot that no request ever owns)."""
         n = len(requests)
         rids = _i64([self._rid(r) for r in requests])
         counts = [int(c) for c in n_new]
-        widths_c = _i32([0] * max(1, len(self.groups)))
-        rc = self._lib.cm_batch_widths(self._h, n, rids, widths_c)
-        if rc != _OK:
-            raise RuntimeError(f"cm_batch_widths failed with {rc}")
-        widths = [max(1, int(widths_c[g])) for g in range(len(self.groups))]
-        total = sum(counts)
+        if widths is None:
+            widths = [max(1, w) for w in self.batch_widths(requests)]
+        else:
+            widths = [int(w) for w in widths]
+        real_total = sum(counts)
+        n_all = n + int(pad_entries)
+        total = real_total + int(pad_entries)
         offsets: dict = {}
         cursor = 0
 
@@ -270,11 +286,11 @@ class CacheManager:
         take("token_req", total)
         take("positions", total)
         take("cache_pos", total)
-        take("qo_indptr", n + 1)
-        take("kv_len", n)
-        take("slots", n)
+        take("qo_indptr", n_all + 1)
+        take("kv_len", n_all)
+        take("slots", n_all)
         for g, w in enumerate(widths):
-            take(f"table{g}", n * w)
+            take(f"table{g}", n_all * w)
         for name, length in extra:
             take(name, int(length))
         size = max(cursor, 4)
@@ -295,17 +311,28 @@ class CacheManager:
         def ptr(arr: np.ndarray):
             return arr.ctypes.data_as(pi32)
 
-        tables = [view(f"table{g}").reshape(n, w) for g, w in enumerate(widths)]
+        tables = [view(f"table{g}").reshape(n_all, w) for g, w in enumerate(widths)]
         table_ptrs = (pi32 * max(1, len(tables)))(*[ptr(t) for t in tables])
         rc = self._lib.cm_fill_batch(
             self._h, n, rids, _i32(counts), ptr(view("token_req")), ptr(view("positions")),
             ptr(view("cache_pos")), ptr(view("qo_indptr")), ptr(view("kv_len")),
             ptr(view("slots")), table_ptrs, _i32(widths))
         if rc == _BAD_ARG:
-            raise ValueError("fill_batch before reserve: a request lacks pages for its tokens")
+            raise ValueError("fill_batch before reserve (a request lacks pages for its "
+                             "tokens), or a block table wider than the fixed width")
         if rc != _OK:
             raise RuntimeError(f"cm_fill_batch failed with {rc}")
-        return BatchIndex(packed=packed, num_tokens=total, num_entries=n,
+        if pad_entries:
+            view("token_req")[real_total:] = np.arange(n, n_all, dtype=np.int32)
+            view("positions")[real_total:] = 0
+            view("cache_pos")[real_total:] = 0
+            view("qo_indptr")[n + 1:] = real_total + np.arange(1, pad_entries + 1, dtype=np.int32)
+            view("kv_len")[n:] = 1
+            view("slots")[n:] = pad_slot
+            for g, t in enumerate(tables):
+                t[n:, :] = -1
+                t[n:, 0] = pad_page[g] if isinstance(pad_page, (list, tuple)) else pad_page
+        return BatchIndex(packed=packed, num_tokens=total, num_entries=n_all,
                           token_req=view("token_req"), positions=view("positions"),
                           cache_pos=view("cache_pos"), qo_indptr=view("qo_indptr"),
                           kv_len=view("kv_len"), slots=view("slots"), tables=tables,

@@ -73,16 +73,26 @@ class CacheStorage:
             if g is None:
                 self.kv.append(None)
             else:
-                n = self.group_configs[g].num_pages
+                # one page more than the manager hands out: padding entries of
+                # fixed-shape (CUDA graph) batches write their keys there
+                n = self.group_configs[g].num_pages + 1
                 self.kv.append(torch.zeros(
                     (n, 2, need.kv.num_kv_heads, self.page_size, need.kv.head_dim),
                     dtype=dtype, device=device))
             if need is not None and need.state is not None:
-                self.state.append(torch.zeros((self.num_slots,) + tuple(need.state.shape),
+                self.state.append(torch.zeros((self.num_slots + 1,) + tuple(need.state.shape),
                                               dtype=_STATE_DTYPES[need.state.dtype],
                                               device=device))
             else:
                 self.state.append(None)
+
+    def pad_page(self, group: int) -> int:
+        """The page of ``group`` that padding entries may scribble on."""
+        return self.group_configs[group].num_pages
+
+    @property
+    def pad_slot(self) -> int:
+        return self.num_slots
 
     def state_bytes_per_request(self) -> int:
         return sum(0 if s is None else s[0].numel() * s.element_size() for s in self.state)

@@ -244,10 +244,12 @@ template <int HD> static int launch_decode(const DecodeArgs& a, int tokens, cuda
     static_assert((size_t)(4 * 16 * HD + 4 * 16 * 2) * sizeof(float) <=
                       (size_t)(2 * 2 * DEC_TILE * HD) * sizeof(bf16),
                   "merge buffer must fit in the stage buffers");
-    if (smem > 48 * 1024) {
+    static bool configured = false;  // once per head size: not repeated inside graph captures
+    if (smem > 48 * 1024 && !configured) {
         cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<HD>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
+        configured = true;
     }
     dim3 grid(a.splits, a.nkv, tokens);
     decode_attention_kernel<HD><<<grid, DEC_THREADS, smem, s>>>(a);

@@ -160,16 +160,21 @@ MSTAR_API int mstar_paged_attention_generic(const void* q, int q_stride, void* o
     const size_t smem = sizeof(float) * ((size_t)G * hd + (size_t)ATT_TILE * (hd + 1) +
                                          (size_t)G * ATT_TILE + 3 * (size_t)G);
     dim3 grid(num_tokens, nkv);
+    static size_t configured_f32 = 0, configured_bf16 = 0;  // largest size set so far
     if (act_dtype == MSTAR_F32) {
-        if (smem > 48 * 1024)
+        if (smem > 48 * 1024 && smem > configured_f32) {
             cudaFuncSetAttribute(paged_attention_generic_kernel<float>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            configured_f32 = smem;
+        }
         paged_attention_generic_kernel<float><<<grid, ATT_THREADS, smem, s>>>(
             (const float*)q, (float*)out, (const float*)kv_cache, block_table, token_req, cache_pos, a);
     } else {
-        if (smem > 48 * 1024)
+        if (smem > 48 * 1024 && smem > configured_bf16) {
             cudaFuncSetAttribute(paged_attention_generic_kernel<bf16>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            configured_bf16 = smem;
+        }
         paged_attention_generic_kernel<bf16><<<grid, ATT_THREADS, smem, s>>>(
             (const bf16*)q, (bf16*)out, (const bf16*)kv_cache, block_table, token_req, cache_pos, a);
     }

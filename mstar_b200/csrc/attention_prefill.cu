@@ -221,10 +221,12 @@ __global__ void __launch_bounds__(PRE_THREADS) prefill_attention_kernel(PrefillA
 template <int HD>
 static int launch_prefill(const PrefillArgs& a, int entries, int max_q_len, cudaStream_t s) {
     const size_t smem = (size_t)(PRE_ROWS * HD + 2 * 2 * PRE_TILE * HD) * sizeof(bf16);
-    if (smem > 48 * 1024) {
+    static bool configured = false;
+    if (smem > 48 * 1024 && !configured) {
         cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<HD>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
+        configured = true;
     }
     const int G = a.nq / a.nkv;
     const long long tiles = ((long long)max_q_len * G + PRE_ROWS - 1) / PRE_ROWS;

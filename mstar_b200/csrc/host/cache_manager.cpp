@@ -318,6 +318,7 @@ MSTAR_API int cm_fill_batch(void* h, int n, const int64_t* rids, const int* n_ne
             const auto& tab = r.table[gi];
             const int64_t need = ceil_div(r.len + n_new[i], m.groups[gi].page_size);
             if ((int64_t)tab.size() < need) return kBadArg;  // not reserved
+            if ((int)tab.size() > widths[gi]) return kBadArg;  // row too narrow for the table
             int* row = tables[gi] + (size_t)i * widths[gi];
             for (int w = 0; w < widths[gi]; ++w) row[w] = w < (int)tab.size() ? tab[w] : -1;
         }

@@ -70,6 +70,10 @@ class Model:
         self.final_norm = build_part("norm", layout.final_norm, _sub(params, "final_norm"),
                                      runtime)
         self.cache_needs = cache_needs(layout)
+        # a decode step may be captured as a CUDA graph only if every mixer says its
+        # forward pass reads nothing per-step from the host
+        self.graph_safe = all(getattr(b.mixer, "graph_safe", False) for b in self.blocks
+                              if hasattr(b, "mixer"))
 
     @property
     def vocab_size(self) -> int:

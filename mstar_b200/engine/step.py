@@ -36,14 +36,121 @@ class StepEntry:
     want: Sequence[int] = field(default_factory=tuple)
 
 
+DECODE_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+
+def _bucket(n: int, buckets=DECODE_BUCKETS):
+    for b in buckets:
+        if n <= b:
+            return b
+    return None
+
+
+def _pow2_at_least(n: int, floor: int = 8) -> int:
+    w = floor
+    while w < n:
+        w *= 2
+    return w
+
+
+class DecodeGraph:
+    """One captured decode step: ``bucket`` single-token entries, block tables of fixed
+    widths.  A real batch of up to ``bucket`` requests is padded with entries that read
+    and write only the cache's padding page and slot.
+
+    CUDA streams and graphs stand where the reference uses a tracing compiler plus its
+    own graph runner (mstar/engine/cuda_graph_runner.py:45, 807-836: decode batches
+    padded to the next captured size); what is replayed here are this package's own
+    kernel launches."""
+
+    RING = 3
+
+    def __init__(self, stepper: "Stepper", bucket: int, widths: list):
+        self.stepper = stepper
+        self.bucket = bucket
+        self.widths = list(widths)
+        mgr, storage = stepper.manager, stepper.storage
+        self.pad_pages = [storage.pad_page(g) for g in range(len(mgr.groups))]
+        self.extra = (("token_ids", bucket), ("want_rows", bucket))
+        probe = mgr.fill_batch([], [], extra=self.extra, widths=self.widths, pad_entries=bucket,
+                               pad_page=self.pad_pages, pad_slot=storage.pad_slot)
+        self.offsets = probe.offsets
+        self.size = probe.packed.size
+        self.dev = torch.zeros(self.size, dtype=torch.int32, device=stepper.device)
+        self.pinned = [torch.empty(self.size, dtype=torch.int32, pin_memory=True)
+                       for _ in range(self.RING)]
+        self.events = [None] * self.RING
+        self.turn = 0
+        bound = max([w * g.page_size for w, g in zip(self.widths, mgr.groups)] or [1])
+
+        def view(name: str) -> torch.Tensor:
+            off, length = self.offsets[name]
+            return self.dev[off:off + length]
+
+        self.ctx = StepContext(
+            num_tokens=bucket, num_entries=bucket, token_req=view("token_req"),
+            positions=view("positions"), cache_pos=view("cache_pos"),
+            qo_indptr=view("qo_indptr"), kv_len=view("kv_len"), slots=view("slots"),
+            q_lens=[1] * bucket, kv_lens=[bound] * bucket,
+            host_slots=[storage.pad_slot] * bucket, max_q_len=1, max_kv_len=bound,
+            num_decode=bucket)
+        self.tables = [view(f"table{g}").view(bucket, -1) for g in range(len(mgr.groups))]
+        self.token_ids = view("token_ids")
+        self.want_rows = view("want_rows")
+        self._stage([], [])
+        model = stepper.model
+        side = torch.cuda.Stream(device=stepper.device)
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):                     # warm-up outside the capture
+            model.forward(self.token_ids, self.ctx, storage, self.tables, self.want_rows)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize(stepper.device)
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.logits = model.forward(self.token_ids, self.ctx, storage, self.tables,
+                                        self.want_rows)
+
+    def _stage(self, requests: list, tokens: list) -> int:
+        """Fill the next pinned buffer for this batch and start its copy to the device."""
+        turn = self.turn
+        self.turn = (turn + 1) % self.RING
+        if self.events[turn] is not None:
+            self.events[turn].synchronize()               # its last copy has been read
+        pinned = self.pinned[turn]
+        n = len(requests)
+        index = self.stepper.manager.fill_batch(
+            requests, [1] * n, extra=self.extra, alloc=lambda size: pinned.numpy(),
+            widths=self.widths, pad_entries=self.bucket - n, pad_page=self.pad_pages,
+            pad_slot=self.stepper.storage.pad_slot)
+        off, length = index.offsets["token_ids"]
+        index.packed[off:off + n] = tokens
+        index.packed[off + n:off + length] = 0
+        off, length = index.offsets["want_rows"]
+        index.packed[off:off + length] = np.arange(length, dtype=np.int32)
+        self.dev.copy_(pinned, non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[turn] = ev
+        return self.size * 4
+
+    def run(self, requests: list, tokens: list) -> torch.Tensor:
+        nbytes = self._stage(requests, tokens)
+        self.stepper.last_h2d_bytes = nbytes
+        self.graph.replay()
+        return self.logits[:len(requests)]
+
+
 class Stepper:
-    def __init__(self, model: Model, storage: CacheStorage):
+    def __init__(self, model: Model, storage: CacheStorage, *, cuda_graphs: bool = True):
         self.model = model
         self.storage = storage
         self.manager = storage.manager
         self.device = model.runtime.device
         self.steps = 0
         self.last_h2d_bytes = 0
+        self.cuda_graphs = bool(cuda_graphs) and getattr(model, "graph_safe", False)
+        self._graphs: dict = {}
+        self.graph_replays = 0
 
     # -- requests ---------------------------------------------------------
     def add_request(self, request: Hashable) -> int:
@@ -83,6 +190,10 @@ class Stepper:
                                      f"{len(e.tokens)} tokens")
         # single tokens first: kernels specialised for one query per request take
         # tokens [0, num_decode), the others the rest
+        if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries):
+            logits = self._step_decode_graph(entries)
+            if logits is not None:
+                return logits
         order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
         ordered = [entries[i] for i in order]
         requests = [e.request for e in ordered]
@@ -127,8 +238,35 @@ class Stepper:
         return logits
 
 
+    def _step_decode_graph(self, entries: list):
+        """A batch of single tokens as the replay of a captured graph; None when the
+        batch is larger than the largest captured shape."""
+        bucket = _bucket(len(entries))
+        if bucket is None:
+            return None
+        requests = [e.request for e in entries]
+        self.manager.reserve(requests, [1] * len(entries))
+        widths = tuple(_pow2_at_least(w) for w in self.manager.batch_widths(requests))
+        key = (bucket, widths)
+        graph = self._graphs.get(key)
+        if graph is None:
+            graph = self._graphs[key] = DecodeGraph(self, bucket, list(widths))
+        logits = graph.run(requests, [e.tokens[0] for e in entries])
+        for request in requests:
+            self.manager.commit(request, 1)
+        self.steps += 1
+        self.graph_replays += 1
+        wanted = [i for i, e in enumerate(entries) for _ in e.want]
+        if wanted == list(range(len(entries))):
+            return logits
+        if not wanted:
+            return logits[:0]
+        return logits[torch.tensor(wanted, dtype=torch.long, device=self.device)]
+
+
 def make_stepper(model: Model, *, page_size: int = 16, num_pages: Optional[int] = None,
-                 max_tokens: Optional[int] = None, num_slots: int = 64) -> Stepper:
+                 max_tokens: Optional[int] = None, num_slots: int = 64,
+                 cuda_graphs: bool = True) -> Stepper:
     """A stepper with a cache pool of ``num_pages`` pages per group, or enough pages
     for ``max_tokens`` cached tokens."""
     if num_pages is None:
@@ -137,4 +275,4 @@ def make_stepper(model: Model, *, page_size: int = 16, num_pages: Optional[int] 
         num_pages = -(-int(max_tokens) // page_size)
     storage = CacheStorage(model.cache_needs, model.runtime.dtype, model.runtime.device,
                            page_size, int(num_pages), num_slots)
-    return Stepper(model, storage)
+    return Stepper(model, storage, cuda_graphs=cuda_graphs)

@@ -19,6 +19,11 @@ from .registry import build_part, register_part
 
 
 class Attention:
+    # everything the forward pass does depends on the step's device arrays and on host
+    # values that are fixed for a batch shape, so a decode step can be replayed as a
+    # CUDA graph
+    graph_safe = True
+
     @classmethod
     def param_specs(cls, spec) -> dict:
         q_rows = spec.num_heads * spec.head_dim

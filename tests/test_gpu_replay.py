@@ -141,3 +141,38 @@ def test_cache_exhaustion_leaves_state_unchanged(model_folders):
     assert stepper.manager.free_pages(0) == 1 and stepper.manager.check() == 0
     stepper.step([StepEntry("a", [6], [0]), StepEntry("b", [1, 2], [])])   # this fits
     assert stepper.manager.length("a") == 6 and stepper.manager.length("b") == 2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_decode_steps_replay_cuda_graphs_with_the_same_logits(model_folders, dtype):
+    """Single-token batches run as replays of captured graphs (padded to a captured
+    batch size, block tables padded to a fixed width); the logits must be the ones the
+    eager path gives, for every batch size from 1 to 5 and across a width change."""
+    from mstar_b200.engine.step import make_stepper
+
+    name = "tiny_b"
+    model = get_model(model_folders, name, dtype)
+    reqs, want = get_requests(model_folders, name)
+    reqs = {k: v for k, v in reqs.items() if len(v) > 1}
+    steps = H.prefill_then_decode(reqs, 32)                 # one request at a time
+    # and all requests decoding together: lengths differ, requests drop out one by one
+    together = [{"entries": [{"id": r, "tokens": t[:1], "want": [0]} for r, t in reqs.items()],
+                 "end": []}]
+    longest = max(len(t) for t in reqs.values())
+    for pos in range(1, longest):
+        entries = [{"id": r, "tokens": [t[pos]], "want": [0]} for r, t in reqs.items()
+                   if pos < len(t)]
+        end = [r for r, t in reqs.items() if pos == len(t) - 1]
+        together.append({"entries": entries, "end": end})
+    for trace, what in ((steps, "graphs, one request"), (together, "graphs, batch")):
+        outs = {}
+        for graphs in (True, False):
+            stepper = make_stepper(model, page_size=8, num_pages=200, num_slots=8,
+                                   cuda_graphs=graphs)
+            outs[graphs] = H.run_steps_in_process(stepper, trace)
+            assert (stepper.graph_replays > 0) == graphs
+            assert stepper.manager.check() == 0 and stepper.manager.free_pages(0) == 200
+        H.compare(outs[True], want, dtype, what)
+        tol = 1e-6 if dtype == "float32" else H.TOL["bfloat16"]
+        for key, row in outs[False].items():
+            assert (row - outs[True][key]).abs().max().item() <= tol, key
