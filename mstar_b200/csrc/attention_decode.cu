@@ -219,23 +219,38 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_attention_kernel(DecodeArg
     }
 }
 
-// Merge the partial results of the splits of one (token, head).
+// Merge the partial results of the splits of one (token, head): the first warp finds
+// the overall maximum and each split's weight, then every thread sums its features.
+#define MERGE_MAX_SPLITS 256
 template <int HD>
 __global__ void decode_merge_kernel(DecodeArgs a) {
+    __shared__ float wgt[MERGE_MAX_SPLITS];
     const int head = blockIdx.x, t = blockIdx.y;
     const int hi = a.cache_pos[t] + 1;
     const int lo = (a.window > 0 && hi > a.window) ? hi - a.window : 0;
     const int n = min(a.splits, (hi - lo + a.chunk - 1) / a.chunk);
     const size_t base = ((size_t)t * a.nq + head) * a.splits;
-    float m = -INFINITY;
-    for (int s = 0; s < n; ++s) m = fmaxf(m, a.part_ml[(base + s) * 2]);
-    float L = 0.f;
-    for (int s = 0; s < n; ++s) L += a.part_ml[(base + s) * 2 + 1] * exp2f(a.part_ml[(base + s) * 2] - m);
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float m = -INFINITY;
+        for (int s = lane; s < n; s += 32) m = fmaxf(m, a.part_ml[(base + s) * 2]);
+        m = warp_max(m);
+        float L = 0.f;
+        for (int s = lane; s < n; s += 32) {
+            const float w = exp2f(a.part_ml[(base + s) * 2] - m);
+            wgt[s] = w;
+            L += a.part_ml[(base + s) * 2 + 1] * w;
+        }
+        L = warp_sum(L);
+        const float inv = 1.f / L;
+        __syncwarp();
+        for (int s = lane; s < n; s += 32) wgt[s] *= inv;
+    }
+    __syncthreads();
     for (int d = threadIdx.x; d < HD; d += blockDim.x) {
         float acc = 0.f;
-        for (int s = 0; s < n; ++s)
-            acc += a.part_o[(base + s) * HD + d] * exp2f(a.part_ml[(base + s) * 2] - m);
-        a.out[(size_t)t * a.nq * HD + (size_t)head * HD + d] = __float2bfloat16_rn(acc / L);
+        for (int s = 0; s < n; ++s) acc = fmaf(a.part_o[(base + s) * HD + d], wgt[s], acc);
+        a.out[(size_t)t * a.nq * HD + (size_t)head * HD + d] = __float2bfloat16_rn(acc);
     }
 }
 
@@ -255,7 +270,7 @@ template <int HD> static int launch_decode(const DecodeArgs& a, int tokens, cuda
     decode_attention_kernel<HD><<<grid, DEC_THREADS, smem, s>>>(a);
     if (a.splits > 1) {
         dim3 mgrid(a.nq, tokens);
-        decode_merge_kernel<HD><<<mgrid, HD < 128 ? HD : 128, 0, s>>>(a);
+        decode_merge_kernel<HD><<<mgrid, HD < 32 ? 32 : (HD < 128 ? HD : 128), 0, s>>>(a);
     }
     return launch_status();
 }
@@ -273,7 +288,7 @@ MSTAR_API int mstar_paged_decode_attention_bf16(
     int page_size, int window, float scale, int chunk, int splits, float* scratch, void* stream) {
     if (tokens <= 0) return 0;
     if (nkv <= 0 || nq % nkv != 0 || nq / nkv > 16) return -1;
-    if (chunk <= 0 || chunk % DEC_TILE != 0 || splits < 1) return -1;
+    if (chunk <= 0 || chunk % DEC_TILE != 0 || splits < 1 || splits > MERGE_MAX_SPLITS) return -1;
     if (splits > 1 && scratch == nullptr) return -1;
     if (tokens > 65535 || nkv > 65535) return -1;
     DecodeArgs a;

@@ -196,15 +196,26 @@ __global__ void rope_kv_write_kernel(A* __restrict__ qkv, const int* __restrict_
                                      const int* __restrict__ block_table,
                                      const float* __restrict__ inv_freq, A* __restrict__ kv_cache,
                                      RopeArgs a) {
+    // grid (token, slice): the items of a token (rotated pairs of q and k, unrotated tail
+    // of k, values) are spread over all threads of its slices, one or a few each, so that
+    // the dependent loads of different items overlap instead of queueing in one thread
     const int t = blockIdx.x;
     const int hd = a.hd, half = a.rotary_dim / 2;
     const int row_elems = (a.nq + 2 * a.nkv) * hd;
     A* row = qkv + (size_t)t * row_elems;
-    const float pos = (float)positions[t];
+    const bool write = kv_cache != nullptr;
+    const int rot_items = (write ? a.nq + a.nkv : a.nq) * half;
+    const int tail = hd - a.rotary_dim;
+    const int tail_items = write ? a.nkv * tail : 0;
+    const int v_items = write ? a.nkv * hd : 0;
+    const int total = rot_items + tail_items + v_items;
+    const int first = blockIdx.y * blockDim.x + threadIdx.x;
+    const int stride = gridDim.y * blockDim.x;
+    if (first >= total) return;
 
     A* kdst = nullptr;
     A* vdst = nullptr;
-    if (kv_cache != nullptr) {
+    if (write) {
         const int cp = cache_pos[t];
         const int page = block_table[(size_t)token_req[t] * a.bt_stride + cp / a.page_size];
         const int slot = cp % a.page_size;
@@ -212,39 +223,31 @@ __global__ void rope_kv_write_kernel(A* __restrict__ qkv, const int* __restrict_
         kdst = kv_cache + (size_t)page * page_elems + (size_t)slot * hd;
         vdst = kdst + (size_t)a.nkv * a.page_size * hd;
     }
-    const int rot_heads = (kv_cache != nullptr) ? a.nq + a.nkv : a.nq;
-
-    // rotated pairs of q (in place) and k (to the cache)
-    for (int item = threadIdx.x; item < rot_heads * half; item += blockDim.x) {
-        const int h = item / half, j = item - h * half;
-        const int i0 = a.interleaved ? 2 * j : j;
-        const int i1 = a.interleaved ? 2 * j + 1 : j + half;
-        float sn, cs;
-        sincosf(pos * inv_freq[j], &sn, &cs);
-        A* src = row + (size_t)h * hd;
-        const float x0 = to_float(src[i0]), x1 = to_float(src[i1]);
-        const float y0 = x0 * cs - x1 * sn;
-        const float y1 = x1 * cs + x0 * sn;
-        if (h < a.nq) {
-            src[i0] = from_float<A>(y0);
-            src[i1] = from_float<A>(y1);
-        } else {
-            A* dst = kdst + (size_t)(h - a.nq) * a.page_size * hd;
+    const float pos = (float)positions[t];
+    for (int item = first; item < total; item += stride) {
+        if (item < rot_items) {
+            const int h = item / half, j = item - h * half;
+            const int i0 = a.interleaved ? 2 * j : j;
+            const int i1 = a.interleaved ? 2 * j + 1 : j + half;
+            float sn, cs;
+            sincosf(pos * inv_freq[j], &sn, &cs);
+            A* src = row + (size_t)h * hd;
+            const float x0 = to_float(src[i0]), x1 = to_float(src[i1]);
+            const float y0 = x0 * cs - x1 * sn;
+            const float y1 = x1 * cs + x0 * sn;
+            A* dst = h < a.nq ? src : kdst + (size_t)(h - a.nq) * a.page_size * hd;
             dst[i0] = from_float<A>(y0);
             dst[i1] = from_float<A>(y1);
+        } else if (item < rot_items + tail_items) {
+            // features of k beyond rotary_dim are copied unrotated
+            const int it = item - rot_items;
+            const int h = it / tail, d = a.rotary_dim + (it - h * tail);
+            kdst[(size_t)h * a.page_size * hd + d] = row[(size_t)(a.nq + h) * hd + d];
+        } else {
+            const int it = item - rot_items - tail_items;
+            const int h = it / hd, d = it - h * hd;
+            vdst[(size_t)h * a.page_size * hd + d] = row[(size_t)(a.nq + a.nkv + h) * hd + d];
         }
-    }
-    if (kv_cache == nullptr) return;
-    // features of k beyond rotary_dim are copied unrotated
-    const int tail = hd - a.rotary_dim;
-    for (int item = threadIdx.x; item < a.nkv * tail; item += blockDim.x) {
-        const int h = item / tail, d = a.rotary_dim + (item - h * tail);
-        kdst[(size_t)h * a.page_size * hd + d] = row[(size_t)(a.nq + h) * hd + d];
-    }
-    // values
-    for (int item = threadIdx.x; item < a.nkv * hd; item += blockDim.x) {
-        const int h = item / hd, d = item - h * hd;
-        vdst[(size_t)h * a.page_size * hd + d] = row[(size_t)(a.nq + a.nkv + h) * hd + d];
     }
 }
 
@@ -256,12 +259,18 @@ MSTAR_API int mstar_rope_kv_write(void* qkv, int act_dtype, const int* positions
     if (num_tokens <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     RopeArgs a{nq, nkv, hd, rotary_dim, interleaved, page_size, bt_stride};
-    const int threads = 128;
+    const int threads = 256;
+    const int items = (nq + nkv) * (rotary_dim / 2) + nkv * (hd - rotary_dim) + nkv * hd;
+    // few tokens: one item per thread; many tokens: fewer, longer-running slices
+    int slices = (items + threads - 1) / threads;
+    if (num_tokens >= 256 && slices > 2) slices = 2;
+    if (slices < 1) slices = 1;
+    dim3 grid(num_tokens, slices);
     if (act_dtype == MSTAR_F32)
-        rope_kv_write_kernel<float><<<num_tokens, threads, 0, s>>>(
+        rope_kv_write_kernel<float><<<grid, threads, 0, s>>>(
             (float*)qkv, positions, cache_pos, token_req, block_table, inv_freq, (float*)kv_cache, a);
     else
-        rope_kv_write_kernel<bf16><<<num_tokens, threads, 0, s>>>(
+        rope_kv_write_kernel<bf16><<<grid, threads, 0, s>>>(
             (bf16*)qkv, positions, cache_pos, token_req, block_table, inv_freq, (bf16*)kv_cache, a);
     return launch_status();
 }

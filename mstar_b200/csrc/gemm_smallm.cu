@@ -1,0 +1,182 @@
+// y[M,N] = x[M,K] W[N,K]^T for few rows (M <= 64), bfloat16 in, float accumulation:
+// the matrix product of decode steps, where every weight is read once and the time is
+// the time to stream W from HBM.
+//
+// A CTA owns 16 output features (16 rows of W); its eight warps split K among them and
+// are summed in shared memory.  Each warp streams its part of the 16 rows straight from
+// global memory into MMA fragments: the rows of W are the A operand of m16n8k16 (the
+// "M" of the instruction), the tokens are the 8-wide N.  Within a block of 32 k-values a
+// thread takes 8 consecutive ones (one 16-byte load per row) instead of the canonical
+// interleaved ones; the sum over k does not care, and x is read with the same
+// assignment, so the products pair up correctly.  Loads are issued eight blocks ahead to
+// keep enough bytes in flight.
+//
+// Variants: GATED computes two strips at once, rows n and inter + n of a fused
+// [gate; up] matrix, and writes silu(gate) * up (mstar/model/components/distributed/
+// mlp.py:78-81), which saves the [M, 2*inter] round trip and one launch.  The output
+// type is bfloat16 or float (logits).  The reference uses the library GEMM for all of
+// these (mstar/model/components/distributed/linear.py:101).
+#include "common.cuh"
+#include "mma_util.cuh"
+
+#define SM_WARPS 8
+#define SM_THREADS (SM_WARPS * 32)
+
+__device__ __forceinline__ uint4 ld_stream(const bf16* p) {
+    return __ldcs(reinterpret_cast<const uint4*>(p));
+}
+__device__ __forceinline__ uint4 ld_cached(const bf16* p) {
+    return __ldg(reinterpret_cast<const uint4*>(p));
+}
+
+template <typename T> __device__ __forceinline__ void store_out(T* p, float v);
+template <> __device__ __forceinline__ void store_out<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+template <int NT, bool GATED, typename OutT>
+__global__ void __launch_bounds__(SM_THREADS)
+smallm_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* __restrict__ out,
+                   int M, int n_out, int K, int ldx, int ldw, int ldo, int inter) {
+    extern __shared__ float red[];  // [strips][SM_WARPS][16][8*NT]
+    constexpr int COLS = 8 * NT;
+    constexpr int STRIPS = GATED ? 2 : 1;
+    constexpr int UNROLL = GATED ? 4 : 8;  // k-blocks of W in flight per thread
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * 16;
+    const int kblocks = K / 32;
+    const int kb0 = (int)((long long)warp * kblocks / SM_WARPS);
+    const int kb1 = (int)((long long)(warp + 1) * kblocks / SM_WARPS);
+
+    const int ra = min(n0 + g, n_out - 1), rb = min(n0 + g + 8, n_out - 1);
+    const bf16* wa[STRIPS];
+    const bf16* wb[STRIPS];
+#pragma unroll
+    for (int s = 0; s < STRIPS; ++s) {
+        wa[s] = W + ((size_t)ra + (size_t)s * inter) * ldw + 8 * t;
+        wb[s] = W + ((size_t)rb + (size_t)s * inter) * ldw + 8 * t;
+    }
+    const bf16* xr[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) xr[j] = x + (size_t)min(8 * j + g, M - 1) * ldx + 8 * t;
+
+    float acc[STRIPS][NT][4];
+#pragma unroll
+    for (int s = 0; s < STRIPS; ++s)
+#pragma unroll
+        for (int j = 0; j < NT; ++j) acc[s][j][0] = acc[s][j][1] = acc[s][j][2] = acc[s][j][3] = 0.f;
+
+    for (int kb = kb0; kb < kb1; kb += UNROLL) {
+        uint4 va[STRIPS][UNROLL], vb[STRIPS][UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            if (kb + u < kb1) {
+                const int k = (kb + u) * 32;
+#pragma unroll
+                for (int s = 0; s < STRIPS; ++s) {
+                    va[s][u] = ld_stream(wa[s] + k);
+                    vb[s][u] = ld_stream(wb[s] + k);
+                }
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            if (kb + u < kb1) {
+                const int k = (kb + u) * 32;
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    const uint4 xv = ld_cached(xr[j] + k);
+#pragma unroll
+                    for (int s = 0; s < STRIPS; ++s) {
+                        const uint32_t a1[4] = {va[s][u].x, vb[s][u].x, va[s][u].y, vb[s][u].y};
+                        const uint32_t a2[4] = {va[s][u].z, vb[s][u].z, va[s][u].w, vb[s][u].w};
+                        mma_bf16_16816(acc[s][j], a1, xv.x, xv.y);
+                        mma_bf16_16816(acc[s][j], a2, xv.z, xv.w);
+                    }
+                }
+            }
+        }
+    }
+
+    // ---- sum the warps' parts of K in shared memory
+#pragma unroll
+    for (int s = 0; s < STRIPS; ++s) {
+        float* mine = red + ((size_t)(s * SM_WARPS + warp) * 16) * COLS;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            const int col = 8 * j + 2 * t;
+            mine[g * COLS + col] = acc[s][j][0];
+            mine[g * COLS + col + 1] = acc[s][j][1];
+            mine[(g + 8) * COLS + col] = acc[s][j][2];
+            mine[(g + 8) * COLS + col + 1] = acc[s][j][3];
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < 16 * COLS; idx += SM_THREADS) {
+        const int r = idx & 15, m = idx >> 4;  // r fastest: consecutive threads, consecutive n
+        if (m >= M || n0 + r >= n_out) continue;
+        float v[STRIPS];
+#pragma unroll
+        for (int s = 0; s < STRIPS; ++s) {
+            float sum = 0.f;
+#pragma unroll
+            for (int w = 0; w < SM_WARPS; ++w)
+                sum += red[((size_t)(s * SM_WARPS + w) * 16 + r) * COLS + m];
+            v[s] = sum;
+        }
+        float y = v[0];
+        if (GATED) {
+            // the gate is rounded to bfloat16 first, as the unfused path stores it
+            const float gate = __bfloat162float(__float2bfloat16_rn(v[0]));
+            const float up = __bfloat162float(__float2bfloat16_rn(v[STRIPS - 1]));
+            y = gate / (1.f + expf(-gate)) * up;
+        }
+        store_out<OutT>(out + (size_t)m * ldo + n0 + r, y);
+    }
+}
+
+template <int NT, bool GATED, typename OutT>
+static int launch_smallm(const bf16* x, const bf16* W, OutT* out, int M, int n_out, int K, int ldx,
+                         int ldw, int ldo, int inter, cudaStream_t s) {
+    const size_t smem = (size_t)(GATED ? 2 : 1) * SM_WARPS * 16 * 8 * NT * sizeof(float);
+    static bool configured = false;
+    if (smem > 48 * 1024 && !configured) {
+        cudaError_t e = cudaFuncSetAttribute(smallm_gemm_kernel<NT, GATED, OutT>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int grid = (n_out + 15) / 16;
+    smallm_gemm_kernel<NT, GATED, OutT><<<grid, SM_THREADS, smem, s>>>(x, W, out, M, n_out, K, ldx,
+                                                                        ldw, ldo, inter);
+    return launch_status();
+}
+
+template <bool GATED, typename OutT>
+static int dispatch_rows(const bf16* x, const bf16* W, OutT* out, int M, int n_out, int K, int ldx,
+                         int ldw, int ldo, int inter, cudaStream_t s) {
+    if (M <= 8) return launch_smallm<1, GATED, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, s);
+    if (M <= 16) return launch_smallm<2, GATED, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, s);
+    if (M <= 32) return launch_smallm<4, GATED, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, s);
+    return launch_smallm<8, GATED, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, s);
+}
+
+// out[M, N] = x W^T (gated == 0), or out[M, N/2] = silu(x Wg^T) * (x Wu^T) for W = [Wg; Wu]
+// (gated == 1).  out_dtype: MSTAR_BF16 or MSTAR_F32.  Returns 0, a CUDA error code, or -1
+// when the shape is refused: M outside 1..64, K no multiple of 32, leading dimensions not
+// multiples of 8 elements (16-byte loads), N odd for the gated form.
+MSTAR_API int mstar_gemm_smallm_bf16(const void* x, const void* W, void* out, int M, int N, int K,
+                                     int ldx, int ldw, int ldo, int gated, int out_dtype,
+                                     void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 64 || K <= 0 || K % 32 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return -1;
+    if (gated && (N % 2 != 0 || out_dtype != MSTAR_BF16)) return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bf16* xp = (const bf16*)x;
+    const bf16* wp = (const bf16*)W;
+    if (gated)
+        return dispatch_rows<true, bf16>(xp, wp, (bf16*)out, M, N / 2, K, ldx, ldw, ldo, N / 2, s);
+    if (out_dtype == MSTAR_F32)
+        return dispatch_rows<false, float>(xp, wp, (float*)out, M, N, K, ldx, ldw, ldo, 0, s);
+    return dispatch_rows<false, bf16>(xp, wp, (bf16*)out, M, N, K, ldx, ldw, ldo, 0, s);
+}

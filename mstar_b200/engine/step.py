@@ -22,6 +22,7 @@ import torch
 
 from ..cache.manager import BatchIndex
 from ..cache.storage import CacheStorage
+from ..ops import lib as ops_lib
 from ..parts.base import StepContext
 from .model import Model
 
@@ -106,9 +107,11 @@ class DecodeGraph:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize(stepper.device)
         self.graph = torch.cuda.CUDAGraph()
+        before = ops_lib.launch_count()
         with torch.cuda.graph(self.graph):
             self.logits = model.forward(self.token_ids, self.ctx, storage, self.tables,
                                         self.want_rows)
+        self.launches = ops_lib.launch_count() - before   # own kernels in one replay
 
     def _stage(self, requests: list, tokens: list) -> int:
         """Fill the next pinned buffer for this batch and start its copy to the device."""
@@ -137,6 +140,7 @@ class DecodeGraph:
         nbytes = self._stage(requests, tokens)
         self.stepper.last_h2d_bytes = nbytes
         self.graph.replay()
+        ops_lib.add_launches(self.launches)
         return self.logits[:len(requests)]
 
 

@@ -169,6 +169,7 @@ def decode_split(tokens: int, num_kv_heads: int, max_len: int) -> tuple:
     the GPU a few times over, chunks in whole tiles of 64 keys."""
     pairs = max(tokens * num_kv_heads, 1)
     want = max(1, -(-NUM_SMS * 6 // pairs))
+    want = min(want, 256)                       # the merge kernel takes up to 256 splits
     chunk = max(64, -(-(-(-max_len // want)) // 64) * 64)
     splits = max(1, -(-max_len // chunk))
     return chunk, splits
@@ -238,11 +239,39 @@ def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out=None):
     return out
 
 
+# The weight-streaming kernel takes up to 64 rows, but above 8 rows every CTA re-reads
+# so much of x per byte of W that the library GEMM is faster; it is used up to here.
+SMALL_M = 8
+
+
+def _smallm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and 0 < x.shape[0] <= SMALL_M
+            and x.shape[1] % 32 == 0 and x.stride(1) == 1 and w.stride(1) == 1
+            and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def _gemm_smallm(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, gated: bool):
+    m, k = x.shape
+    n = w.shape[0]
+    out = torch.empty((m, n // 2 if gated else n), dtype=out_dtype, device=x.device)
+    code = lib.get("gemm_smallm").mstar_gemm_smallm_bf16(
+        x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), w.stride(0),
+        out.stride(0), int(gated), _dt(out), _stream())
+    if code == -1:
+        raise KernelError(f"small-M GEMM refuses M={m}, N={n}, K={k}")
+    check(code, "gemm_smallm")
+    return out
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None):
-    """x[M,K] @ w[N,K]^T.  bfloat16 x bfloat16 -> library GEMM with float
-    accumulation; anything involving a float32 operand runs in true float32."""
+    """x[M,K] @ w[N,K]^T.  bfloat16 with at most ``SMALL_M`` rows: this package's
+    weight-streaming kernel; more rows: library GEMM with float accumulation;
+    anything involving a float32 operand runs in true float32."""
     _need_cuda(x, w)
     out_dtype = out_dtype or x.dtype
+    if out_dtype in (torch.bfloat16, torch.float32) and _smallm_ok(x, w):
+        return _gemm_smallm(x, w, out_dtype, gated=False)
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         if out_dtype == torch.float32:
             try:
@@ -254,6 +283,15 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     wf = convert(w, torch.float32)
     y = sgemm_nt(xf, wf)
     return convert(y, out_dtype)
+
+
+def gated_up(x: torch.Tensor, w_gate_up: torch.Tensor):
+    """silu(x Wg^T) * (x Wu^T) for the fused matrix [Wg; Wu]: one kernel for few
+    bfloat16 rows, else the product followed by the SiLU-multiply kernel."""
+    _need_cuda(x, w_gate_up)
+    if _smallm_ok(x, w_gate_up) and w_gate_up.shape[0] % 2 == 0:
+        return _gemm_smallm(x, w_gate_up, torch.bfloat16, gated=True)
+    return silu_mul(linear(x, w_gate_up))
 
 
 def argmax(logits: torch.Tensor):

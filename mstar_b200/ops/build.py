@@ -35,6 +35,7 @@ LIBRARIES = {
     "attention_decode": ("cuda", ["attention_decode.cu"], []),
     "attention_prefill": ("cuda", ["attention_prefill.cu"], []),
     "gemm_f32": ("cuda", ["gemm_f32.cu"], []),
+    "gemm_smallm": ("cuda", ["gemm_smallm.cu"], []),
     "sampling": ("cuda", ["sampling.cu"], []),
     "host": ("host", ["host/cache_manager.cpp"], []),
 }

@@ -42,6 +42,9 @@ _SIGNATURES = {
     "gemm_f32": {
         "mstar_sgemm_nt": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     },
+    "gemm_smallm": {
+        "mstar_gemm_smallm_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+    },
     "sampling": {
         "mstar_sample": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
         "mstar_argmax": [_vp, _i, _i, _i, _vp, _vp],
@@ -90,6 +93,12 @@ _launches = 0
 def launch_count() -> int:
     """Kernel launches of this package's own libraries since the process began."""
     return _launches
+
+
+def add_launches(n: int) -> None:
+    """Account for kernels launched by replaying a captured CUDA graph."""
+    global _launches
+    _launches += n
 
 
 def check(code: int, what: str) -> None:

@@ -25,9 +25,7 @@ class GatedMLP:
         self.down = params["down.weight"]
 
     def forward(self, x, ctx):
-        gu = ops.linear(x, self.gate_up)
-        m = ops.silu_mul(gu)
-        return ops.linear(m, self.down)
+        return ops.linear(ops.gated_up(x, self.gate_up), self.down)
 
 
 register_part("ffn", "gated_mlp", GatedMLP)

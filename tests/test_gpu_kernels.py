@@ -421,3 +421,46 @@ def test_repetition_penalty_and_seen_mask():
     got = ops.sample(logits, temp, penalty=pen, seen_mask=seen, seen_rows=rows)
     assert got.tolist() == [9, 5]                   # 4.0 / 2 < 3.0 where 5 was seen
     assert seen[2, 9] == 1 and seen.sum() == 2      # the sampled token is marked
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 33, 64])
+@pytest.mark.parametrize("n,k", [(16, 32), (100, 96), (3000, 1024), (157, 3072)])
+def test_small_m_gemm(m, n, k):
+    """The weight-streaming product of decode steps: every M up to 64, N that is no
+    multiple of the 16-row strip, K from one block of 32 up, both output types."""
+    from mstar_b200 import ops
+
+    x = rnd(m, k, dtype=torch.bfloat16, seed=m)
+    w = rnd(n, k, dtype=torch.bfloat16, seed=n, scale=0.1)
+    want = x.double() @ w.double().T
+    y = ops._gemm_smallm(x, w, torch.bfloat16, gated=False)     # the kernel itself, any M <= 64
+    assert torch.equal(ops.linear(x, w), y) or m > ops.SMALL_M
+    assert y.dtype == torch.bfloat16 and y.shape == (m, n)
+    assert (y.double() - want).abs().max() < 0.01 * want.abs().max() + 1e-3
+    y32 = ops._gemm_smallm(x, w, torch.float32, gated=False)
+    assert (y32.double() - want).abs().max() < 2e-4 * math.sqrt(k)
+    # a row's result does not depend on how many other rows the batch has
+    if m > 1:
+        assert torch.equal(ops._gemm_smallm(x[:1].contiguous(), w, torch.bfloat16, False), y[:1])
+    # rows that are views into a wider buffer (stride larger than K)
+    wide = torch.zeros(m, k + 64, dtype=torch.bfloat16, device=DEV)
+    wide[:, :k] = x
+    assert torch.equal(ops._gemm_smallm(wide[:, :k], w, torch.bfloat16, False), y)
+
+
+@pytest.mark.parametrize("m", [1, 8, 40, 64, 100])
+def test_gated_up_fused_and_unfused(m):
+    from mstar_b200 import ops
+
+    inter, k = 200, 96
+    x = rnd(m, k, dtype=torch.bfloat16, seed=1)
+    w = rnd(2 * inter, k, dtype=torch.bfloat16, seed=2, scale=0.2)
+    got = ops.gated_up(x, w) if m > 64 else ops._gemm_smallm(x, w, torch.bfloat16, gated=True)
+    g = (x.double() @ w[:inter].double().T)
+    u = (x.double() @ w[inter:].double().T)
+    want = g * torch.sigmoid(g) * u
+    assert got.shape == (m, inter)
+    assert (got.double() - want).abs().max() < 0.02 * want.abs().max() + 2e-3
+    # the fused kernel (m <= 64) and product + SiLU-multiply agree to bfloat16 rounding
+    ref = ops.silu_mul(torch.mm(x, w.t()))
+    assert (got.double() - ref.double()).abs().max() < 0.02 * want.abs().max() + 2e-3
