@@ -34,6 +34,7 @@ LIBRARIES = {
     "attention_generic": ("cuda", ["attention_generic.cu"], []),
     "attention_decode": ("cuda", ["attention_decode.cu"], []),
     "attention_prefill": ("cuda", ["attention_prefill.cu"], []),
+    "attention_decode_noalloc": ("cuda", ["attention_decode_noalloc.cu"], []),
     "gemm_f32": ("cuda", ["gemm_f32.cu"], []),
     "gemm_smallm": ("cuda", ["gemm_smallm.cu"], []),
     "sampling": ("cuda", ["sampling.cu"], []),
@@ -91,8 +92,26 @@ def build_dir() -> Path:
                      + ", ".join(str(c) for c in candidates) + ")")
 
 
-def _headers() -> list[Path]:
-    return sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")) + sorted((CSRC / "host").glob("*.h"))
+def _with_includes(sources: list) -> list:
+    """The sources and, recursively, every file of this tree they #include "..."."""
+    import re
+
+    seen: dict = {}
+    todo = [CSRC / s for s in sources]
+    while todo:
+        f = todo.pop()
+        if f in seen:
+            continue
+        if not f.is_file():
+            raise BuildError(f"source file {f} is missing")
+        text = f.read_text()
+        seen[f] = text
+        for inc in re.findall(r'^\s*#\s*include\s+"([^"]+)"', text, flags=re.M):
+            for base in (f.parent, CSRC):
+                if (base / inc).is_file():
+                    todo.append((base / inc).resolve())
+                    break
+    return sorted(seen.items())
 
 
 def library_hash(name: str) -> str:
@@ -100,11 +119,9 @@ def library_hash(name: str) -> str:
     h = hashlib.sha256()
     h.update(_compiler_id(kind).encode())
     h.update(" ".join((NVCC_FLAGS if kind == "cuda" else HOST_FLAGS) + extra).encode())
-    for src in [CSRC / s for s in sources] + _headers():
-        if not src.is_file():
-            raise BuildError(f"source file {src} is missing")
+    for src, text in _with_includes(sources):
         h.update(src.name.encode())
-        h.update(src.read_bytes())
+        h.update(text.encode())
     return h.hexdigest()[:16]
 
 
