@@ -235,6 +235,131 @@ def time_e2e(model, batch: int, cfg: dict, steps: int, warmup: int, num_pages: i
             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch}
 
 
+# --------------------------------------------------------------- single kernels
+def _time_graph(fn, reps: int = 20, rounds: int = 5) -> float:
+    """Median milliseconds of one call of ``fn`` when ``reps`` calls are replayed as one
+    CUDA graph (so that launch gaps are what they are inside a captured step)."""
+    import torch
+
+    fn()
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        fn()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(reps):
+            fn()
+    times = []
+    for _ in range(rounds):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end) / reps)
+    return statistics.median(times)
+
+
+def kernel_bench(name: str, batch: int, ctx: int, small: bool) -> int:
+    """Time one kernel alone at the benchmark model's shapes: ``--kernel NAME``.  Inputs
+    rotate over copies larger than L2 where the kernel is memory-bound.  ``--small``
+    shrinks the case for profiler captures (still larger than L2 where it matters)."""
+    import torch
+
+    from mstar_b200 import ops
+
+    cfg = ORPHEUS_3B
+    nq, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    dev = "cuda:0"
+    pk = peaks()
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def rnd(*shape, scale=1.0):
+        return (scale * torch.randn(*shape, generator=g, device=dev)).to(torch.bfloat16)
+
+    out = {"kernel": name, "batch": batch, "ctx": ctx}
+    if name in ("decode_attention", "prefill_attention"):
+        page = PAGE_SIZE
+        reqs = batch
+        pages_per = -(-ctx // page)
+        kv = rnd(reqs * pages_per + 1, 2, nkv, page, hd)
+        table = torch.randperm(reqs * pages_per, device=dev).to(torch.int32).view(reqs, pages_per)
+        if name == "decode_attention":
+            q = rnd(reqs, (nq + 2 * nkv) * hd)
+            o = torch.empty(reqs, nq * hd, dtype=torch.bfloat16, device=dev)
+            token_req = torch.arange(reqs, dtype=torch.int32, device=dev)
+            cache_pos = torch.full((reqs,), ctx - 1, dtype=torch.int32, device=dev)
+            fn = lambda: ops.paged_decode_attention(q, q.stride(0), o, kv, table, token_req,
+                                                    cache_pos, reqs, nq, nkv, hd, page, 0,
+                                                    hd ** -0.5, ctx)
+            ms = _time_graph(fn)
+            nbytes = reqs * ctx * 2 * nkv * hd * 2
+            out.update(ms=ms, gbs=nbytes / ms / 1e6, frac_hbm=nbytes / ms / 1e6 / pk["hbm_gbs"],
+                       split=ops.decode_split(reqs, nkv, ctx))
+        else:
+            q = rnd(reqs * ctx, (nq + 2 * nkv) * hd)
+            o = torch.empty(reqs * ctx, nq * hd, dtype=torch.bfloat16, device=dev)
+            indptr = torch.arange(0, (reqs + 1) * ctx, ctx, dtype=torch.int32, device=dev)
+            kvl = torch.full((reqs,), ctx, dtype=torch.int32, device=dev)
+            fn = lambda: ops.paged_prefill_attention(q, q.stride(0), o, kv, table, indptr, kvl, 0,
+                                                     reqs, ctx, nq, nkv, hd, page, 0, hd ** -0.5)
+            ms = _time_graph(fn, reps=5)
+            flops = reqs * 4.0 * nq * hd * ctx * (ctx + 1) / 2
+            out.update(ms=ms, tflops=flops / ms / 1e9,
+                       frac_bf16=flops / ms / 1e9 / pk["bf16_tflops"])
+    elif name in ("gemm_qkv", "gemm_o", "gemm_gate_up", "gemm_down", "gemm_lm_head"):
+        n, k = {"gemm_qkv": ((nq + 2 * nkv) * hd, H), "gemm_o": (H, nq * hd),
+                "gemm_gate_up": (2 * I, H), "gemm_down": (H, I), "gemm_lm_head": (V, H)}[name]
+        if small and name == "gemm_lm_head":
+            n = 65536
+        copies = max(1, -(-(160 << 20) // (n * k * 2)))          # rotate over > L2 bytes
+        ws = [rnd(n, k, scale=0.02) for _ in range(copies)]
+        x = rnd(batch, k)
+        state = {"i": 0}
+
+        def fn():
+            w = ws[state["i"] % copies]
+            state["i"] += 1
+            if name == "gemm_gate_up":
+                return ops.gated_up(x, w)
+            return ops.linear(x, w, out_dtype=torch.float32 if name == "gemm_lm_head" else None)
+
+        ms = _time_graph(fn, reps=max(copies * 2, 8))
+        nbytes = n * k * 2
+        flops = 2.0 * batch * n * k
+        out.update(ms=ms, n=n, k=k, gbs=nbytes / ms / 1e6,
+                   frac_hbm=nbytes / ms / 1e6 / pk["hbm_gbs"], tflops=flops / ms / 1e9)
+    elif name in ("add_rmsnorm", "rope_kv_write"):
+        rows = batch
+        if name == "add_rmsnorm":
+            resid = torch.randn(rows, H, device=dev)
+            delta = rnd(rows, H)
+            w = rnd(H)
+            fn = lambda: ops.add_rmsnorm(resid, delta, w, 1e-5, torch.bfloat16)
+        else:
+            qkv = rnd(rows, (nq + 2 * nkv) * hd)
+            pos = torch.full((rows,), ctx - 1, dtype=torch.int32, device=dev)
+            req = torch.arange(rows, dtype=torch.int32, device=dev)
+            kv = rnd(rows * (-(-ctx // PAGE_SIZE)) + 1, 2, nkv, PAGE_SIZE, hd)
+            table = torch.arange(rows * (-(-ctx // PAGE_SIZE)), dtype=torch.int32,
+                                 device=dev).view(rows, -1)
+            inv = torch.rand(hd // 2, device=dev)
+            fn = lambda: ops.rope_kv_write(qkv, pos, pos, req, table, inv, kv, nq, nkv, hd, hd,
+                                           False, PAGE_SIZE)
+        out.update(ms=_time_graph(fn, reps=50))
+    else:
+        print(f"unknown kernel {name!r}")
+        return 2
+    out["peaks"] = pk["source"]
+    print(json.dumps(out))
+    return 0
+
+
 def reference_arm() -> int:
     print(json.dumps({
         "impl": "reference",
@@ -254,7 +379,15 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the model has (named in the record)")
+    ap.add_argument("--kernel", default=None,
+                    help="time one kernel alone (decode_attention, prefill_attention, gemm_qkv, "
+                         "gemm_o, gemm_gate_up, gemm_down, gemm_lm_head, add_rmsnorm, "
+                         "rope_kv_write) at --batch rows / requests and --ctx keys")
+    ap.add_argument("--ctx", type=int, default=PROMPT_LEN)
+    ap.add_argument("--small", action="store_true", help="a smaller case, for profiler captures")
     args = ap.parse_args()
+    if args.kernel:
+        return kernel_bench(args.kernel, args.batch, args.ctx, args.small)
     if args.impl == "reference":
         return reference_arm()
     if args.gpus != 1:

@@ -239,9 +239,9 @@ def sgemm_nt(a: torch.Tensor, w: torch.Tensor, out=None):
     return out
 
 
-# The weight-streaming kernel takes up to 64 rows, but above 8 rows every CTA re-reads
-# so much of x per byte of W that the library GEMM is faster; it is used up to here.
-SMALL_M = 8
+# Rows up to which the weight-streaming kernel is used (it takes up to 16); beyond, the
+# library GEMM.
+SMALL_M = 16
 
 
 def _smallm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:

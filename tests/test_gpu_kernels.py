@@ -423,17 +423,17 @@ def test_repetition_penalty_and_seen_mask():
     assert seen[2, 9] == 1 and seen.sum() == 2      # the sampled token is marked
 
 
-@pytest.mark.parametrize("m", [1, 3, 8, 9, 16, 17, 33, 64])
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("n,k", [(16, 32), (100, 96), (3000, 1024), (157, 3072)])
 def test_small_m_gemm(m, n, k):
-    """The weight-streaming product of decode steps: every M up to 64, N that is no
-    multiple of the 16-row strip, K from one block of 32 up, both output types."""
+    """The weight-streaming product of decode steps: every M up to 16, N that is no
+    multiple of the 8-row strip, K from one block of 32 up, both output types."""
     from mstar_b200 import ops
 
     x = rnd(m, k, dtype=torch.bfloat16, seed=m)
     w = rnd(n, k, dtype=torch.bfloat16, seed=n, scale=0.1)
     want = x.double() @ w.double().T
-    y = ops._gemm_smallm(x, w, torch.bfloat16, gated=False)     # the kernel itself, any M <= 64
+    y = ops._gemm_smallm(x, w, torch.bfloat16, gated=False)     # the kernel itself
     assert torch.equal(ops.linear(x, w), y) or m > ops.SMALL_M
     assert y.dtype == torch.bfloat16 and y.shape == (m, n)
     assert (y.double() - want).abs().max() < 0.01 * want.abs().max() + 1e-3
@@ -448,19 +448,28 @@ def test_small_m_gemm(m, n, k):
     assert torch.equal(ops._gemm_smallm(wide[:, :k], w, torch.bfloat16, False), y)
 
 
-@pytest.mark.parametrize("m", [1, 8, 40, 64, 100])
+def test_small_m_gemm_refuses_more_rows():
+    from mstar_b200 import ops
+
+    x, w = rnd(17, 64, dtype=torch.bfloat16), rnd(32, 64, dtype=torch.bfloat16)
+    with pytest.raises(ops.KernelError, match="refuses"):
+        ops._gemm_smallm(x, w, torch.bfloat16, gated=False)
+    assert ops.linear(x, w).shape == (17, 32)             # the library product takes over
+
+
+@pytest.mark.parametrize("m", [1, 8, 13, 16, 100])
 def test_gated_up_fused_and_unfused(m):
     from mstar_b200 import ops
 
     inter, k = 200, 96
     x = rnd(m, k, dtype=torch.bfloat16, seed=1)
     w = rnd(2 * inter, k, dtype=torch.bfloat16, seed=2, scale=0.2)
-    got = ops.gated_up(x, w) if m > 64 else ops._gemm_smallm(x, w, torch.bfloat16, gated=True)
+    got = ops.gated_up(x, w) if m > 16 else ops._gemm_smallm(x, w, torch.bfloat16, gated=True)
     g = (x.double() @ w[:inter].double().T)
     u = (x.double() @ w[inter:].double().T)
     want = g * torch.sigmoid(g) * u
     assert got.shape == (m, inter)
     assert (got.double() - want).abs().max() < 0.02 * want.abs().max() + 2e-3
-    # the fused kernel (m <= 64) and product + SiLU-multiply agree to bfloat16 rounding
+    # the fused kernel (m <= 16) and product + SiLU-multiply agree to bfloat16 rounding
     ref = ops.silu_mul(torch.mm(x, w.t()))
     assert (got.double() - ref.double()).abs().max() < 0.02 * want.abs().max() + 2e-3
