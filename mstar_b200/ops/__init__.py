@@ -264,14 +264,101 @@ def _gemm_smallm(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, gated
     return out
 
 
+_tc_error_words: dict = {}
+
+
+def tcgen05_error_word(device) -> torch.Tensor:
+    """Device int32 that a tcgen05 GEMM kernel sets when one of its bounded waits ran
+    out (1 producer, 2 MMA issuer, 3 epilogue); zero otherwise."""
+    key = torch.device(device).index or 0
+    if key not in _tc_error_words:
+        _tc_error_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _tc_error_words[key]
+
+
+def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
+                 bn: int = 256):
+    """x[M,K] @ w[N,K]^T on the tcgen05 tensor cores (TMA operand tiles, TMEM
+    accumulator).  bfloat16 operands, K and the row strides multiples of 8."""
+    _need_cuda(x, w)
+    out_dtype = out_dtype or torch.bfloat16
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    assert x.dim() == 2 and w.dim() == 2 and x.shape[1] == w.shape[1]
+    assert x.stride(1) == 1 and w.stride(1) == 1
+    m, k = x.shape
+    n = w.shape[0]
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    code = lib.get("gemm_tcgen05").mstar_gemm_tcgen05_bf16(
+        x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), w.stride(0),
+        out.stride(0), _dt(out), bn, tcgen05_error_word(x.device).data_ptr(), _stream())
+    if code == -1:
+        raise KernelError(f"tcgen05 GEMM refuses M={m}, N={n}, K={k} (K and row strides must be "
+                          "multiples of 8, operands 16-byte aligned)")
+    if code in (-3, -4):
+        raise KernelError(f"tcgen05 GEMM could not make its TMA tensor map (code {code})")
+    check(code, "gemm_tcgen05")
+    return out
+
+
+def gemm_tcgen05_gated(x: torch.Tensor, w_gate_up: torch.Tensor):
+    """silu(x Wg^T) * (x Wu^T) for the fused [Wg; Wu] on pairs of CTAs (cta_group::2),
+    the activation applied in the epilogue straight from tensor memory."""
+    _need_cuda(x, w_gate_up)
+    assert x.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16
+    assert x.stride(1) == 1 and w_gate_up.stride(1) == 1 and x.shape[1] == w_gate_up.shape[1]
+    m, k = x.shape
+    n = w_gate_up.shape[0]
+    out = torch.empty((m, n // 2), dtype=torch.bfloat16, device=x.device)
+    code = lib.get("gemm_tcgen05").mstar_gemm_tcgen05_gated_bf16(
+        x.data_ptr(), w_gate_up.data_ptr(), out.data_ptr(), m, n, k, x.stride(0),
+        w_gate_up.stride(0), out.stride(0), tcgen05_error_word(x.device).data_ptr(), _stream())
+    if code == -1:
+        raise KernelError(f"gated tcgen05 GEMM refuses M={m}, N={n}, K={k}")
+    if code in (-3, -4):
+        raise KernelError(f"tcgen05 GEMM could not make its TMA tensor map (code {code})")
+    check(code, "gemm_tcgen05_gated")
+    return out
+
+
+def _tc_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0
+            and x.stride(1) == 1 and w.stride(1) == 1 and x.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
+
+
+def tcgen05_tile(m: int, n: int) -> int | None:
+    """Which tcgen05 kernel takes an [m, K] x [n, K]^T product, or None for the library
+    GEMM: 256 = lone CTAs with 128 x 256 tiles, 512 = CTA pairs with 256 x 256 tiles.
+    The hand-written kernels are used where their grid fills the GPU: very wide
+    matrices (the LM head) at any row count, and wide ones (gate/up) at prompt size.
+    ``MSTAR_GEMM=tcgen05`` forces them everywhere, ``MSTAR_GEMM=library`` nowhere."""
+    import os
+
+    forced = os.environ.get("MSTAR_GEMM", "")
+    if forced == "library":
+        return None
+    if n >= 32768:
+        return 256 if m <= 256 else 512
+    if m >= 1024 and n >= 8192:
+        return 512
+    if forced == "tcgen05":
+        return 512 if m > 128 else 256
+    return None
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None):
     """x[M,K] @ w[N,K]^T.  bfloat16 with at most ``SMALL_M`` rows: this package's
-    weight-streaming kernel; more rows: library GEMM with float accumulation;
-    anything involving a float32 operand runs in true float32."""
+    weight-streaming kernel; more rows: this package's tcgen05 kernels where
+    ``tcgen05_tile`` says so, else the library GEMM; anything involving a float32
+    operand runs in true float32."""
     _need_cuda(x, w)
     out_dtype = out_dtype or x.dtype
     if out_dtype in (torch.bfloat16, torch.float32) and _smallm_ok(x, w):
         return _gemm_smallm(x, w, out_dtype, gated=False)
+    if out_dtype in (torch.bfloat16, torch.float32) and _tc_ok(x, w):
+        tile = tcgen05_tile(x.shape[0], w.shape[0])
+        if tile is not None:
+            return gemm_tcgen05(x, w, out_dtype, tile)
     if x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16:
         if out_dtype == torch.float32:
             try:
@@ -291,6 +378,9 @@ def gated_up(x: torch.Tensor, w_gate_up: torch.Tensor):
     _need_cuda(x, w_gate_up)
     if _smallm_ok(x, w_gate_up) and w_gate_up.shape[0] % 2 == 0:
         return _gemm_smallm(x, w_gate_up, torch.bfloat16, gated=True)
+    if (_tc_ok(x, w_gate_up) and w_gate_up.shape[0] % 16 == 0
+            and tcgen05_tile(x.shape[0], w_gate_up.shape[0]) is not None):
+        return gemm_tcgen05_gated(x, w_gate_up)
     return silu_mul(linear(x, w_gate_up))
 
 

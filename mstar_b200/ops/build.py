@@ -37,6 +37,7 @@ LIBRARIES = {
     "attention_decode_noalloc": ("cuda", ["attention_decode_noalloc.cu"], []),
     "gemm_f32": ("cuda", ["gemm_f32.cu"], []),
     "gemm_smallm": ("cuda", ["gemm_smallm.cu"], []),
+    "gemm_tcgen05": ("cuda", ["gemm_tcgen05.cu"], []),
     "sampling": ("cuda", ["sampling.cu"], []),
     "host": ("host", ["host/cache_manager.cpp"], []),
 }

@@ -473,3 +473,70 @@ def test_gated_up_fused_and_unfused(m):
     # the fused kernel (m <= 16) and product + SiLU-multiply agree to bfloat16 rounding
     ref = ops.silu_mul(torch.mm(x, w.t()))
     assert (got.double() - ref.double()).abs().max() < 0.02 * want.abs().max() + 2e-3
+
+
+# ------------------------------------------------------------------- tcgen05 GEMM
+def tc_clean():
+    from mstar_b200 import ops
+
+    torch.cuda.synchronize()
+    word = ops.tcgen05_error_word(DEV)
+    code = int(word.item())
+    word.zero_()
+    return code
+
+
+@pytest.mark.parametrize("bn", [128, 256, 512])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (1, 8, 8), (200, 300, 136), (513, 1000, 776),
+                                   (64, 2048, 3072), (300, 130, 4096)])
+def test_tcgen05_gemm(bn, m, n, k):
+    """TMA + tcgen05.mma + TMEM product: lone CTAs (bn 128, 256) and CTA pairs (512); sizes
+    that are no multiples of the tiles, K that is no multiple of the 64-wide block."""
+    from mstar_b200 import ops
+
+    x = rnd(m, k, dtype=torch.bfloat16, seed=m + k)
+    w = rnd(n, k, dtype=torch.bfloat16, seed=n, scale=0.1)
+    want = x.double() @ w.double().T
+    y = ops.gemm_tcgen05(x, w, torch.bfloat16, bn)
+    y32 = ops.gemm_tcgen05(x, w, torch.float32, bn)
+    assert tc_clean() == 0
+    assert (y32.double() - want).abs().max() < 2e-4 * math.sqrt(k) * max(1.0, want.abs().max().item() / 8)
+    assert (y.double() - want).abs().max() < 0.01 * want.abs().max() + 1e-3
+    # a view into a wider buffer: the row stride goes into the tensor map
+    wide = torch.zeros(m, k + 64, dtype=torch.bfloat16, device=DEV)
+    wide[:, :k] = x
+    assert torch.equal(ops.gemm_tcgen05(wide[:, :k], w, torch.bfloat16, bn), y)
+    assert tc_clean() == 0
+
+
+@pytest.mark.parametrize("m,inter,k", [(256, 128, 64), (77, 200, 96), (2048, 1000, 512)])
+def test_tcgen05_gated_gemm(m, inter, k):
+    from mstar_b200 import ops
+
+    x = rnd(m, k, dtype=torch.bfloat16, seed=1)
+    w = rnd(2 * inter, k, dtype=torch.bfloat16, seed=2, scale=0.2)
+    got = ops.gemm_tcgen05_gated(x, w)
+    assert tc_clean() == 0
+    g = x.double() @ w[:inter].double().T
+    u = x.double() @ w[inter:].double().T
+    want = g * torch.sigmoid(g) * u
+    assert got.shape == (m, inter)
+    assert (got.double() - want).abs().max() < 0.02 * want.abs().max() + 2e-3
+    ref = ops.silu_mul(torch.mm(x, w.t()))
+    assert (got.double() - ref.double()).abs().max() < 0.02 * want.abs().max() + 2e-3
+
+
+def test_tcgen05_refusals_and_dispatch(monkeypatch):
+    from mstar_b200 import ops
+
+    x = rnd(32, 20, dtype=torch.bfloat16)          # K = 20 is no multiple of 8
+    w = rnd(64, 20, dtype=torch.bfloat16)
+    with pytest.raises(ops.KernelError, match="refuses"):
+        ops.gemm_tcgen05(x, w)
+    assert ops.linear(x, w).shape == (32, 64)       # the library product takes it
+    assert ops.tcgen05_tile(2048, 16384) == 512 and ops.tcgen05_tile(64, 156940) == 256
+    assert ops.tcgen05_tile(2048, 3072) is None
+    monkeypatch.setenv("MSTAR_GEMM", "tcgen05")
+    assert ops.tcgen05_tile(2048, 3072) == 512
+    monkeypatch.setenv("MSTAR_GEMM", "library")
+    assert ops.tcgen05_tile(2048, 16384) is None
