@@ -1,0 +1,87 @@
+"""The benchmark model's layer sizes (Orpheus 3B / Llama 3.2 3B: width 3072, 24 query and
+8 key/value heads of 128, feed-forward 8192, vocabulary 156,940, tied head, llama3 rotary
+scaling x32) with two layers, against the plain model: whole prompt, portions, and a
+mixed batch.  At these sizes the product path runs the kernels serving runs: the
+tcgen05 gate/up and LM-head products, the small-M products, the tensor-core attention."""
+import pytest
+import torch
+
+import helpers as H
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+
+CFG = dict(
+    architectures=["LlamaForCausalLM"], num_hidden_layers=2, hidden_size=3072,
+    num_attention_heads=24, num_key_value_heads=8, head_dim=128, intermediate_size=8192,
+    vocab_size=156940, tie_word_embeddings=True, rope_theta=500000.0,
+    rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                  "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    rms_norm_eps=1e-5, max_position_embeddings=131072, hidden_act="silu",
+)
+LENGTHS = [150, 37]
+# Tolerances at this size, derived as for the tiny models (tests/helpers.py): the plain
+# model evaluated in float32 instead of float64 differs from itself by 2.9e-5 (max) and
+# 2.8e-6 (mean) here, against 4.4e-6 on the tiny models whose float32 tolerance is 2e-5:
+# the same factor gives 1.3e-4 / 1.3e-5.  bfloat16: the plain model with its activations
+# rounded to bfloat16 at the places where the engine stores bfloat16 (normed rows, q, k,
+# v, attention output, projections, gate, up, their product) differs from float64 by
+# 0.18 (max) and 0.018 (mean) on these requests, logits being as large as 5.5; the
+# tolerance is 1.5 times that rounding noise.
+TOLS = {"float32": (1.3e-4, 1.3e-5), "bfloat16": (0.27, 0.027)}
+
+
+@pytest.fixture(scope="module")
+def big(tmp_path_factory):
+    from mstar_b200.config.registry import config_from_dict
+    from mstar_b200.weights.random_init import random_checkpoint
+
+    cfg = config_from_dict(CFG)
+    tensors = random_checkpoint(cfg, seed=3, std=0.02, device="cuda:0")
+    for key in tensors:                       # sharper attention, as in the tiny models
+        if key.endswith("q_proj.weight") or key.endswith("k_proj.weight"):
+            tensors[key] = (tensors[key].float() * 2.0).to(torch.bfloat16)
+    reqs = {f"o{i}": H.request_tokens(CFG["vocab_size"], n, seed=70 + i)
+            for i, n in enumerate(LENGTHS)}
+    cpu = {k: v.cpu() for k, v in tensors.items()}
+    want = {}
+    head = cpu["model.embed_tokens.weight"].double()
+    for rid, toks in reqs.items():
+        hidden = P.plain_hidden_states(cpu, CFG, toks)
+        rows = sorted({0, 1, 15, 16, 17, len(toks) // 2, len(toks) - 2, len(toks) - 1})
+        logits = hidden[rows] @ head.T
+        want.update({(rid, r): logits[i] for i, r in enumerate(rows)})
+    del head
+    return cfg, tensors, reqs, want
+
+
+def only_wanted(steps, want):
+    """Keep `want` only at the positions the plain logits were computed for."""
+    pos = {}
+    for st in steps:
+        for e in st["entries"]:
+            base = pos.get(e["id"], 0)
+            e["want"] = [w for w in e["want"] if (e["id"], base + w) in want]
+            pos[e["id"]] = base + len(e["tokens"])
+    return steps
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_orpheus_sized_layers_match_the_plain_model(big, dtype):
+    from mstar_b200.engine.model import load_model
+    from mstar_b200.engine.step import make_stepper
+
+    cfg, tensors, reqs, want = big
+    model = load_model(None, dtype=dtype, device="cuda:0", config=cfg, tensors=tensors)
+    for steps, what in ((H.whole(reqs), "3B-sized layers, whole"),
+                        (H.portions(reqs, sizes=(64, 2, 30, 17)), "3B-sized layers, portions"),
+                        (H.mixed(reqs, seed=1, prompt_frac=0.8), "3B-sized layers, mixed")):
+        steps = only_wanted(steps, want)
+        pages = H.max_tokens_of(steps, 16) // 16
+        stepper = make_stepper(model, page_size=16, num_pages=pages, num_slots=4)
+        got = H.run_steps_in_process(stepper, steps)
+        assert set(got) == set(want)
+        worst = H.compare(got, want, dtype, what, tol=TOLS[dtype][0], mean_tol=TOLS[dtype][1])
+        print(f"{what} [{dtype}]: worst abs error {worst:.3e}")
+    del model
+    torch.cuda.empty_cache()
