@@ -15,6 +15,8 @@
 // (mstar/utils/flashinfer_utils.py:348-366, 452-465).
 #include "common.cuh"
 #include "mma_util.cuh"
+#include "tma_util.cuh"
+#include <string.h>
 
 #define DEC_THREADS 128
 #define DEC_TILE 64
@@ -273,6 +275,303 @@ template <int HD> static int launch_decode(const DecodeArgs& a, int tokens, cuda
         decode_merge_kernel<HD><<<mgrid, HD < 32 ? 32 : (HD < 128 ? HD : 128), 0, s>>>(a);
     }
     return launch_status();
+}
+
+// ------------------------------------------------------------- TMA variant of the kernel
+// Same arithmetic, other way of getting keys and values into shared memory: instead of
+// every thread computing page addresses for its 16-byte pieces, one thread issues bulk
+// tensor copies (TMA), one box of [page_size rows x 64 features] per page and 64-feature
+// half, which land with the hardware's 128-byte swizzle and signal an mbarrier.  The
+// cache is described as a matrix [(page, k/v, head, slot), head_dim] by a tensor map made
+// on the host.  That takes the address arithmetic out of the instruction stream, which is
+// what bounded the cp.async kernel.  Used when head_dim is 64, 128 or 256, the page size
+// divides 64 and is at least 8, and there is no window (tiles then start on page
+// boundaries); everything else takes the kernel above.
+template <int HD> __device__ __forceinline__ int tma_off(int row, int c) {
+    // element offset of 16-byte chunk c of key `row` in a tile stored as HD/64 halves of
+    // [64 keys x 64 features], chunks XOR-swizzled by the row as TMA's SWIZZLE_128B does
+    return (c >> 3) * (64 * 64) + row * 64 + ((((c & 7) ^ (row & 7))) << 3);
+}
+
+template <int HD>
+__global__ void __launch_bounds__(DEC_THREADS)
+decode_attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs a,
+                            int* __restrict__ error_word) {
+    constexpr int CPR = HD / 8;
+    constexpr int HALVES = HD / 64;
+    constexpr uint32_t TILE_BYTES = DEC_TILE * HD * 2;  // keys (or values) of one tile
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* aligned = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+    bf16* stages = reinterpret_cast<bf16*>(aligned);              // [2]{K, V}, 1024-aligned
+    bf16* Qs = stages + 2 * 2 * DEC_TILE * HD;                    // [16][HD]
+    __shared__ __align__(8) uint64_t full_bar[2];
+
+    const int split = blockIdx.x, kvh = blockIdx.y, t = blockIdx.z;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = a.nq / a.nkv;
+    const int hi = a.cache_pos[t] + 1;
+    const int ks = split * a.chunk;
+    const int ke = min(hi, ks + a.chunk);
+    if (ks >= ke) return;
+    const int* bt = a.block_table + (size_t)a.token_req[t] * a.bt_stride;
+    const int ps = a.page_size;
+
+    if (tid == 0) {
+        mbar_init(tc_smem(&full_bar[0]), 1);
+        mbar_init(tc_smem(&full_bar[1]), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    // rows that no copy fills (beyond the request's last page) must hold finite numbers:
+    // their probabilities are zero, but 0 * NaN is not
+    for (int i = tid; i < 2 * 2 * DEC_TILE * HD / 8; i += DEC_THREADS)
+        reinterpret_cast<uint4*>(stages)[i] = make_uint4(0u, 0u, 0u, 0u);
+    const bf16* qrow = a.q + (size_t)t * a.q_stride + (size_t)kvh * G * HD;
+    for (int i = tid; i < 16 * CPR; i += DEC_THREADS) {
+        const int r = i / CPR, c = i - r * CPR;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < G) v = *reinterpret_cast<const uint4*>(qrow + (size_t)r * HD + c * 8);
+        *reinterpret_cast<uint4*>(Qs + tile_off<CPR>(r, c)) = v;
+    }
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    __syncthreads();
+
+    auto issue_tile = [&](int stage, int base) {  // one thread
+        const int pages = (min(ke, base + DEC_TILE) - base + ps - 1) / ps;
+        const uint32_t bar = tc_smem(&full_bar[stage]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_expect_tx(bar, (uint32_t)pages * ps * HD * 2 * 2);
+        unsigned char* kdst = reinterpret_cast<unsigned char*>(stages) + (size_t)stage * 2 * TILE_BYTES;
+        unsigned char* vdst = kdst + TILE_BYTES;
+        for (int p = 0; p < pages; ++p) {
+            const int page = bt[base / ps + p];
+            const int krow = ((page * 2) * a.nkv + kvh) * ps;
+            const int vrow = ((page * 2 + 1) * a.nkv + kvh) * ps;
+#pragma unroll
+            for (int h = 0; h < HALVES; ++h) {
+                const uint32_t off = (uint32_t)h * (64 * 128) + (uint32_t)p * ps * 128;
+                tma_load_2d(tc_smem(kdst + off), &kv_map, bar, h * 64, krow);
+                tma_load_2d(tc_smem(vdst + off), &kv_map, bar, h * 64, vrow);
+            }
+        }
+    };
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+
+    const int ntiles = (ke - ks + DEC_TILE - 1) / DEC_TILE;
+    if (tid == 0) issue_tile(0, ks);
+    bool alive = true;
+    for (int it = 0; it < ntiles; ++it) {
+        if (tid == 0 && it + 1 < ntiles) issue_tile((it + 1) & 1, ks + (it + 1) * DEC_TILE);
+        const bool arrived = mbar_wait(tc_smem(&full_bar[it & 1]), (uint32_t)(it >> 1) & 1u);
+        if (!__syncthreads_and(arrived ? 1 : 0)) {  // a copy never completed: give up together
+            if (tid == 0) atomicExch(error_word, 4);
+            alive = false;
+            break;
+        }
+        const bf16* Ks = stages + (size_t)(it & 1) * 2 * DEC_TILE * HD;
+        const bf16* Vs = Ks + DEC_TILE * HD;
+        const int key0 = ks + it * DEC_TILE + warp * 16;
+        if (key0 < ke) {
+            float s[2][4];
+#pragma unroll
+            for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+            for (int kk = 0; kk < HD / 16; ++kk) {
+                uint32_t qa[4], kb[4];
+                const int arow = (lane & 7) + ((lane >> 3) & 1) * 8;
+                ldmatrix_x4(qa, smem_u32(Qs + tile_off<CPR>(arow, 2 * kk + (lane >> 4))));
+                const int brow = warp * 16 + (lane & 7) + (lane >> 4) * 8;
+                ldmatrix_x4(kb, smem_u32(Ks + tma_off<HD>(brow, 2 * kk + ((lane >> 3) & 1))));
+                mma_bf16_16816(s[0], qa, kb[0], kb[1]);
+                mma_bf16_16816(s[1], qa, kb[2], kb[3]);
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 2; ++j)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
+                    const float v = key < ke ? s[j][e] * a.scale_log2e : -INFINITY;
+                    s[j][e] = v;
+                    if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+                }
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+            mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+            mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+            const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+            const float al0 = exp2f(m0 - mn0), al1 = exp2f(m1 - mn1);
+            m0 = mn0;
+            m1 = mn1;
+            float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                s[j][0] = exp2f(s[j][0] - mn0);
+                s[j][1] = exp2f(s[j][1] - mn0);
+                s[j][2] = exp2f(s[j][2] - mn1);
+                s[j][3] = exp2f(s[j][3] - mn1);
+                ps0 += s[j][0] + s[j][1];
+                ps1 += s[j][2] + s[j][3];
+            }
+            l0 = l0 * al0 + ps0;
+            l1 = l1 * al1 + ps1;
+#pragma unroll
+            for (int n = 0; n < HD / 8; ++n) {
+                o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1;
+            }
+            uint32_t pa[4];
+            pa[0] = pack_bf16(s[0][0], s[0][1]);
+            pa[1] = pack_bf16(s[0][2], s[0][3]);
+            pa[2] = pack_bf16(s[1][0], s[1][1]);
+            pa[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+            for (int n2 = 0; n2 < HD / 16; ++n2) {
+                uint32_t vb[4];
+                const int vrow = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                ldmatrix_x4_trans(vb, smem_u32(Vs + tma_off<HD>(vrow, 2 * n2 + (lane >> 4))));
+                mma_bf16_16816(o[2 * n2], pa, vb[0], vb[1]);
+                mma_bf16_16816(o[2 * n2 + 1], pa, vb[2], vb[3]);
+            }
+        }
+        __syncthreads();  // everyone is done with this stage before it is filled again
+    }
+    if (!alive) return;
+
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    float* Om = reinterpret_cast<float*>(stages);
+    float* MLm = Om + 4 * 16 * HD;
+    const int r0 = lane >> 2;
+#pragma unroll
+    for (int n = 0; n < HD / 8; ++n) {
+        const int col = n * 8 + (lane & 3) * 2;
+        float* p0 = Om + ((size_t)warp * 16 + r0) * HD + col;
+        p0[0] = o[n][0];
+        p0[1] = o[n][1];
+        float* p1 = p0 + 8 * HD;
+        p1[0] = o[n][2];
+        p1[1] = o[n][3];
+    }
+    if ((lane & 3) == 0) {
+        MLm[(warp * 16 + r0) * 2 + 0] = m0;
+        MLm[(warp * 16 + r0) * 2 + 1] = l0;
+        MLm[(warp * 16 + r0 + 8) * 2 + 0] = m1;
+        MLm[(warp * 16 + r0 + 8) * 2 + 1] = l1;
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * HD; idx += DEC_THREADS) {
+        const int g = idx / HD, d = idx - g * HD;
+        float m = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) m = fmaxf(m, MLm[(w * 16 + g) * 2]);
+        float acc = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = MLm[(w * 16 + g) * 2];
+            const float wgt = mw == -INFINITY ? 0.f : exp2f(mw - m);
+            acc += wgt * Om[((size_t)w * 16 + g) * HD + d];
+            L += wgt * MLm[(w * 16 + g) * 2 + 1];
+        }
+        const int head = kvh * G + g;
+        if (a.splits == 1) {
+            a.out[(size_t)t * a.nq * HD + (size_t)head * HD + d] = __float2bfloat16_rn(acc / L);
+        } else {
+            const size_t slot = ((size_t)t * a.nq + head) * a.splits + split;
+            a.part_o[slot * HD + d] = acc;
+            if (d == 0) {
+                a.part_ml[slot * 2] = m;
+                a.part_ml[slot * 2 + 1] = L;
+            }
+        }
+    }
+}
+
+template <int HD>
+static int launch_decode_tma(const CUtensorMap& map, const DecodeArgs& a, int tokens, int* error_word,
+                             cudaStream_t s) {
+    const size_t smem = (size_t)(16 * HD + 2 * 2 * DEC_TILE * HD) * sizeof(bf16) + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(decode_attention_tma_kernel<HD>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(a.splits, a.nkv, tokens);
+    decode_attention_tma_kernel<HD><<<grid, DEC_THREADS, smem, s>>>(map, a, error_word);
+    if (a.splits > 1) {
+        dim3 mgrid(a.nq, tokens);
+        decode_merge_kernel<HD><<<mgrid, HD < 128 ? HD : 128, 0, s>>>(a);
+    }
+    return launch_status();
+}
+
+// Tensor map of a cache [pages, 2, nkv, page_size, hd] (bfloat16) seen as the matrix
+// [pages * 2 * nkv * page_size, hd] with boxes of page_size rows x 64 features, 128-byte
+// swizzle.  `out_map` receives the 128-byte map.  Returns 0, -1 (shape not taken), -3 / -4.
+MSTAR_API int mstar_make_kv_tensor_map(void* out_map, const void* kv_cache, long long pages, int nkv,
+                                       int page_size, int hd) {
+    if (hd % 64 != 0 || hd > 256 || page_size < 8 || page_size > 64 || DEC_TILE % page_size != 0)
+        return -1;
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return -3;
+    const cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)pages * 2 * nkv * page_size};
+    const cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
+    const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(reinterpret_cast<CUtensorMap*>(out_map), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                          const_cast<void*>(kv_cache), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -4;
+}
+
+// The TMA variant: `kv_map` from mstar_make_kv_tensor_map for this cache; no window.
+// `error_word`: device int, set to 4 if a copy's barrier never completed.
+MSTAR_API int mstar_paged_decode_attention_bf16_tma(
+    const void* kv_map, const void* q, int q_stride, void* out, const void* kv_cache,
+    const int* block_table, int bt_stride, const int* token_req, const int* cache_pos, int tokens,
+    int nq, int nkv, int hd, int page_size, float scale, int chunk, int splits, float* scratch,
+    int* error_word, void* stream) {
+    if (tokens <= 0) return 0;
+    if (nkv <= 0 || nq % nkv != 0 || nq / nkv > 16) return -1;
+    if (chunk <= 0 || chunk % DEC_TILE != 0 || splits < 1 || splits > MERGE_MAX_SPLITS) return -1;
+    if (splits > 1 && scratch == nullptr) return -1;
+    if (tokens > 65535 || nkv > 65535) return -1;
+    if (page_size < 8 || page_size > 64 || DEC_TILE % page_size != 0) return -1;
+    DecodeArgs a;
+    a.q = (const bf16*)q;
+    a.kv = (const bf16*)kv_cache;
+    a.block_table = block_table;
+    a.token_req = token_req;
+    a.cache_pos = cache_pos;
+    a.part_o = scratch;
+    a.part_ml = scratch ? scratch + (size_t)tokens * nq * splits * hd : nullptr;
+    a.out = (bf16*)out;
+    a.q_stride = q_stride;
+    a.bt_stride = bt_stride;
+    a.nq = nq;
+    a.nkv = nkv;
+    a.page_size = page_size;
+    a.window = 0;
+    a.chunk = chunk;
+    a.splits = splits;
+    a.scale_log2e = scale * 1.4426950408889634f;
+    CUtensorMap map;
+    memcpy(&map, kv_map, sizeof(map));
+    cudaStream_t s = (cudaStream_t)stream;
+    switch (hd) {
+        case 64: return launch_decode_tma<64>(map, a, tokens, error_word, s);
+        case 128: return launch_decode_tma<128>(map, a, tokens, error_word, s);
+        case 256: return launch_decode_tma<256>(map, a, tokens, error_word, s);
+        default: return -1;
+    }
 }
 
 // Scratch floats needed for `tokens` query tokens cut into `splits` chunks.

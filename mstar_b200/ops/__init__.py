@@ -175,6 +175,31 @@ def decode_split(tokens: int, num_kv_heads: int, max_len: int) -> tuple:
     return chunk, splits
 
 
+_kv_maps: dict = {}
+
+
+def kv_tensor_map(kv_cache: torch.Tensor):
+    """The TMA tensor map (a 128-byte host buffer) of a cache tensor [pages, 2, kv_heads,
+    page_size, head_dim], or None when the TMA kernels do not take its shape."""
+    pages, _, nkv, page_size, hd = kv_cache.shape
+    key = (kv_cache.data_ptr(), tuple(kv_cache.shape))
+    if key not in _kv_maps:
+        import ctypes
+
+        buf = ctypes.create_string_buffer(128 + 64)
+        addr = (ctypes.addressof(buf) + 63) & ~63          # the driver wants 64-byte alignment
+        code = lib.get("attention_decode").mstar_make_kv_tensor_map(
+            addr, kv_cache.data_ptr(), pages, nkv, page_size, hd)
+        if code == -1:
+            _kv_maps[key] = None
+        elif code != 0:
+            raise KernelError(f"could not make the TMA tensor map of a cache (code {code})")
+        else:
+            _kv_maps[key] = (buf, addr)
+    entry = _kv_maps[key]
+    return None if entry is None else entry[1]
+
+
 def paged_decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv_cache,
                            block_table, token_req, cache_pos, tokens: int, num_heads: int,
                            num_kv_heads: int, head_dim: int, page_size: int, window: int,
@@ -191,6 +216,18 @@ def paged_decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
     if splits > 1:
         scratch = torch.empty(tokens * num_heads * splits * (head_dim + 2), dtype=torch.float32,
                               device=q.device)
+    kv_map = kv_tensor_map(kv_cache) if not window else None
+    if kv_map is not None:
+        code = lib.get("attention_decode").mstar_paged_decode_attention_bf16_tma(
+            kv_map, q.data_ptr(), q_stride, out.data_ptr(), kv_cache.data_ptr(),
+            block_table.data_ptr(), block_table.stride(0), token_req.data_ptr(),
+            cache_pos.data_ptr(), tokens, num_heads, num_kv_heads, head_dim, page_size,
+            float(scale), chunk, splits, _ptr(scratch), tcgen05_error_word(q.device).data_ptr(),
+            _stream())
+        if code == -1:
+            raise KernelError("TMA decode attention refuses this shape")
+        check(code, "paged_decode_attention_tma")
+        return
     code = lib.get("attention_decode").mstar_paged_decode_attention_bf16(
         q.data_ptr(), q_stride, out.data_ptr(), kv_cache.data_ptr(), block_table.data_ptr(),
         block_table.stride(0), token_req.data_ptr(), cache_pos.data_ptr(), tokens, num_heads,

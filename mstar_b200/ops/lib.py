@@ -32,6 +32,9 @@ _SIGNATURES = {
                                           _i, _i, _f, _i, _vp],
     },
     "attention_decode": {
+        "mstar_make_kv_tensor_map": [_vp, _vp, _ll, _i, _i, _i],
+        "mstar_paged_decode_attention_bf16_tma": [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i,
+                                                  _i, _i, _i, _f, _i, _i, _vp, _vp, _vp],
         "mstar_paged_decode_attention_bf16": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i,
                                               _i, _i, _i, _f, _i, _i, _vp, _vp],
     },

@@ -242,8 +242,9 @@ def test_paged_attention_window_edge(act):
         assert bool(hit) == inside
 
 
+# page sizes 8..64 with head sizes 64/128/256 take the TMA path of the decode kernel
 SHAPES_FAST = [(6, 2, 64, 4), (5, 1, 32, 16), (3, 3, 16, 8), (24, 8, 128, 16), (2, 1, 256, 2),
-               (16, 1, 64, 16)]
+               (16, 1, 64, 16), (4, 2, 256, 8), (6, 3, 128, 32), (8, 8, 64, 64)]
 
 
 @pytest.mark.parametrize("nq,nkv,hd,page", SHAPES_FAST)
@@ -256,6 +257,7 @@ def test_decode_attention_kernel(nq, nkv, hd, page):
     got, want, _ = paged_case([1], [3000], nq, nkv, hd, page, torch.bfloat16, seed=3,
                               kernel="decode")              # one request: as many splits as fit
     assert (got - want).abs().max() < 2e-2
+    assert tc_clean() == 0                                  # no bounded wait of a TMA copy ran out
 
 
 @pytest.mark.parametrize("nq,nkv,hd,page", SHAPES_FAST)
