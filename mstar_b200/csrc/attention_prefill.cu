@@ -13,8 +13,11 @@
 //
 // Semantics as attention_generic.cu; the reference uses a library here
 // (mstar/utils/flashinfer_utils.py:136-156, 259-269).
+#include <string.h>
+
 #include "common.cuh"
 #include "mma_util.cuh"
+#include "tma_util.cuh"
 
 #define PRE_THREADS 128
 #define PRE_ROWS 64
@@ -31,12 +34,29 @@ struct PrefillArgs {
     float scale_log2e;
 };
 
-template <int HD>
-__global__ void __launch_bounds__(PRE_THREADS) prefill_attention_kernel(PrefillArgs a) {
+// Position (in elements) of 16-byte chunk c of key `row` in a key/value tile.  With TMA a
+// tile is HD/64 halves of [64 keys x 64 features] with the hardware's 128-byte swizzle;
+// with cp.async it is [64 keys x HD] with this file's own XOR swizzle.
+template <int HD, bool TMA> __device__ __forceinline__ int kv_off(int row, int c) {
+    if (TMA) return (c >> 3) * (64 * 64) + row * 64 + (((c & 7) ^ (row & 7)) << 3);
+    return tile_off<HD / 8>(row, c);
+}
+
+// TMA = true: keys and values come by bulk tensor copies, one box of [page_size x 64] per
+// page and 64-feature half, issued by one thread and awaited on an mbarrier (head_dim 64,
+// 128 or 256, page size 8..64 dividing 64, no window).  TMA = false: every thread copies
+// its 16-byte pieces with cp.async (any page size, windows).
+template <int HD, bool TMA>
+__global__ void __launch_bounds__(PRE_THREADS)
+prefill_attention_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillArgs a,
+                         int* __restrict__ error_word) {
     constexpr int CPR = HD / 8;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    bf16* Qs = reinterpret_cast<bf16*>(smem_raw);  // [64][HD]
-    bf16* stages = Qs + PRE_ROWS * HD;             // [2]{K [64][HD], V [64][HD]}
+    unsigned char* aligned = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    bf16* stages = reinterpret_cast<bf16*>(aligned);   // [2]{K [64][HD], V [64][HD]}, 1024-aligned
+    bf16* Qs = stages + 2 * 2 * PRE_TILE * HD;         // [64][HD]
+    __shared__ __align__(8) uint64_t full_bar[2];
 
     const int tile = blockIdx.x, kvh = blockIdx.y, e = a.first_entry + blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -68,6 +88,39 @@ __global__ void __launch_bounds__(PRE_THREADS) prefill_attention_kernel(PrefillA
         *reinterpret_cast<uint4*>(Qs + tile_off<CPR>(r, c)) = v;
     }
 
+    if (TMA) {
+        if (tid == 0) {
+            mbar_init(tc_smem(&full_bar[0]), 1);
+            mbar_init(tc_smem(&full_bar[1]), 1);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        }
+        // rows no copy fills must hold finite numbers (their probabilities are zero)
+        for (int i = tid; i < 2 * 2 * PRE_TILE * HD / 8; i += PRE_THREADS)
+            reinterpret_cast<uint4*>(stages)[i] = make_uint4(0u, 0u, 0u, 0u);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();
+    }
+    auto issue_tile = [&](int stage, int base) {  // TMA: one thread
+        const int ps = a.page_size;
+        const int pages = (min(hi, base + PRE_TILE) - base + ps - 1) / ps;
+        const uint32_t bar = tc_smem(&full_bar[stage]);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        mbar_expect_tx(bar, (uint32_t)pages * ps * HD * 2 * 2);
+        unsigned char* kdst = reinterpret_cast<unsigned char*>(stages) +
+                              (size_t)stage * 2 * PRE_TILE * HD * 2;
+        unsigned char* vdst = kdst + (size_t)PRE_TILE * HD * 2;
+        for (int p = 0; p < pages; ++p) {
+            const int page = bt[base / ps + p];
+            const int krow = ((page * 2) * a.nkv + kvh) * ps;
+            const int vrow = ((page * 2 + 1) * a.nkv + kvh) * ps;
+#pragma unroll
+            for (int h = 0; h < HD / 64; ++h) {
+                const uint32_t off = (uint32_t)h * (64 * 128) + (uint32_t)p * ps * 128;
+                tma_load_2d(tc_smem(kdst + off), &kv_map, bar, h * 64, krow);
+                tma_load_2d(tc_smem(vdst + off), &kv_map, bar, h * 64, vrow);
+            }
+        }
+    };
     auto load_tile = [&](int stage, int base) {
         bf16* Ks = stages + (size_t)stage * 2 * PRE_TILE * HD;
         bf16* Vs = Ks + PRE_TILE * HD;
@@ -105,13 +158,26 @@ __global__ void __launch_bounds__(PRE_THREADS) prefill_attention_kernel(PrefillA
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
     const int ntiles = (hi - lo + PRE_TILE - 1) / PRE_TILE;
-    load_tile(0, lo);
-    cp_async_commit();
-    for (int it = 0; it < ntiles; ++it) {
-        if (it + 1 < ntiles) load_tile((it + 1) & 1, lo + (it + 1) * PRE_TILE);
+    if (TMA) {
+        if (tid == 0) issue_tile(0, lo);
+    } else {
+        load_tile(0, lo);
         cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
+    }
+    for (int it = 0; it < ntiles; ++it) {
+        if (TMA) {
+            if (tid == 0 && it + 1 < ntiles) issue_tile((it + 1) & 1, lo + (it + 1) * PRE_TILE);
+            const bool arrived = mbar_wait(tc_smem(&full_bar[it & 1]), (uint32_t)(it >> 1) & 1u);
+            if (!__syncthreads_and(arrived ? 1 : 0)) {  // a copy never completed
+                if (tid == 0) atomicExch(error_word, 5);
+                return;
+            }
+        } else {
+            if (it + 1 < ntiles) load_tile((it + 1) & 1, lo + (it + 1) * PRE_TILE);
+            cp_async_commit();
+            cp_async_wait<1>();
+            __syncthreads();
+        }
         const bf16* Ks = stages + (size_t)(it & 1) * 2 * PRE_TILE * HD;
         const bf16* Vs = Ks + PRE_TILE * HD;
         const int base = lo + it * PRE_TILE;
@@ -129,7 +195,7 @@ __global__ void __launch_bounds__(PRE_THREADS) prefill_attention_kernel(PrefillA
                 for (int jp = 0; jp < 4; ++jp) {
                     uint32_t kb[4];
                     const int brow = jp * 16 + (lane & 7) + (lane >> 4) * 8;
-                    ldmatrix_x4(kb, smem_u32(Ks + tile_off<CPR>(brow, 2 * kk + ((lane >> 3) & 1))));
+                    ldmatrix_x4(kb, smem_u32(Ks + kv_off<HD, TMA>(brow, 2 * kk + ((lane >> 3) & 1))));
                     mma_bf16_16816(s[2 * jp], qa, kb[0], kb[1]);
                     mma_bf16_16816(s[2 * jp + 1], qa, kb[2], kb[3]);
                 }
@@ -185,7 +251,7 @@ __global__ void __launch_bounds__(PRE_THREADS) prefill_attention_kernel(PrefillA
                 for (int n2 = 0; n2 < HD / 16; ++n2) {
                     uint32_t vb[4];
                     const int vrow = kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
-                    ldmatrix_x4_trans(vb, smem_u32(Vs + tile_off<CPR>(vrow, 2 * n2 + (lane >> 4))));
+                    ldmatrix_x4_trans(vb, smem_u32(Vs + kv_off<HD, TMA>(vrow, 2 * n2 + (lane >> 4))));
                     mma_bf16_16816(o[2 * n2], pa, vb[0], vb[1]);
                     mma_bf16_16816(o[2 * n2 + 1], pa, vb[2], vb[3]);
                 }
@@ -193,7 +259,7 @@ __global__ void __launch_bounds__(PRE_THREADS) prefill_attention_kernel(PrefillA
         }
         __syncthreads();
     }
-    cp_async_wait<0>();
+    if (!TMA) cp_async_wait<0>();
 
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
     l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -218,12 +284,13 @@ __global__ void __launch_bounds__(PRE_THREADS) prefill_attention_kernel(PrefillA
     }
 }
 
-template <int HD>
-static int launch_prefill(const PrefillArgs& a, int entries, int max_q_len, cudaStream_t s) {
-    const size_t smem = (size_t)(PRE_ROWS * HD + 2 * 2 * PRE_TILE * HD) * sizeof(bf16);
+template <int HD, bool TMA>
+static int launch_prefill(const CUtensorMap& map, const PrefillArgs& a, int entries, int max_q_len,
+                          int* error_word, cudaStream_t s) {
+    const size_t smem = (size_t)(PRE_ROWS * HD + 2 * 2 * PRE_TILE * HD) * sizeof(bf16) + 1024;
     static bool configured = false;
-    if (smem > 48 * 1024 && !configured) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<HD>,
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_attention_kernel<HD, TMA>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
@@ -232,17 +299,21 @@ static int launch_prefill(const PrefillArgs& a, int entries, int max_q_len, cuda
     const long long tiles = ((long long)max_q_len * G + PRE_ROWS - 1) / PRE_ROWS;
     if (tiles > 2147483647LL) return -1;
     dim3 grid((unsigned)tiles, a.nkv, entries);
-    prefill_attention_kernel<HD><<<grid, PRE_THREADS, smem, s>>>(a);
+    prefill_attention_kernel<HD, TMA><<<grid, PRE_THREADS, smem, s>>>(map, a, error_word);
     return launch_status();
 }
 
 // Entries [first_entry, first_entry + entries) of the batch; qo_indptr and kv_len are
 // indexed by entry, block_table rows too.  Returns 0, a CUDA error code, or -1 when
 // the shape is refused (head_dim not one of 16/32/64/128/256).
+// `kv_map`: the cache's tensor map (mstar_make_kv_tensor_map of the decode library) or
+// null; with a map, no window and a page size of 8..64 that divides 64, keys and values
+// are fetched by TMA.  `error_word`: device int, set to 5 if a TMA copy never completed.
 MSTAR_API int mstar_paged_prefill_attention_bf16(
-    const void* q, int q_stride, void* out, const void* kv_cache, const int* block_table,
-    int bt_stride, const int* qo_indptr, const int* kv_len, int first_entry, int entries,
-    int max_q_len, int nq, int nkv, int hd, int page_size, int window, float scale, void* stream) {
+    const void* kv_map, const void* q, int q_stride, void* out, const void* kv_cache,
+    const int* block_table, int bt_stride, const int* qo_indptr, const int* kv_len, int first_entry,
+    int entries, int max_q_len, int nq, int nkv, int hd, int page_size, int window, float scale,
+    int* error_word, void* stream) {
     if (entries <= 0 || max_q_len <= 0) return 0;
     if (nkv <= 0 || nq % nkv != 0 || entries > 65535 || nkv > 65535) return -1;
     PrefillArgs a;
@@ -261,12 +332,25 @@ MSTAR_API int mstar_paged_prefill_attention_bf16(
     a.first_entry = first_entry;
     a.scale_log2e = scale * 1.4426950408889634f;
     cudaStream_t s = (cudaStream_t)stream;
+    CUtensorMap map;
+    memset(&map, 0, sizeof(map));
+    const bool tma = kv_map != nullptr && window == 0 && hd % 64 == 0 && page_size >= 8 &&
+                     page_size <= 64 && PRE_TILE % page_size == 0 && error_word != nullptr;
+    if (tma) {
+        memcpy(&map, kv_map, sizeof(map));
+        switch (hd) {
+            case 64: return launch_prefill<64, true>(map, a, entries, max_q_len, error_word, s);
+            case 128: return launch_prefill<128, true>(map, a, entries, max_q_len, error_word, s);
+            case 256: return launch_prefill<256, true>(map, a, entries, max_q_len, error_word, s);
+            default: return -1;
+        }
+    }
     switch (hd) {
-        case 16: return launch_prefill<16>(a, entries, max_q_len, s);
-        case 32: return launch_prefill<32>(a, entries, max_q_len, s);
-        case 64: return launch_prefill<64>(a, entries, max_q_len, s);
-        case 128: return launch_prefill<128>(a, entries, max_q_len, s);
-        case 256: return launch_prefill<256>(a, entries, max_q_len, s);
+        case 16: return launch_prefill<16, false>(map, a, entries, max_q_len, error_word, s);
+        case 32: return launch_prefill<32, false>(map, a, entries, max_q_len, error_word, s);
+        case 64: return launch_prefill<64, false>(map, a, entries, max_q_len, error_word, s);
+        case 128: return launch_prefill<128, false>(map, a, entries, max_q_len, error_word, s);
+        case 256: return launch_prefill<256, false>(map, a, entries, max_q_len, error_word, s);
         default: return -1;
     }
 }

@@ -249,10 +249,12 @@ def paged_prefill_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, k
     _need_cuda(q, out, kv_cache, block_table, qo_indptr, kv_len)
     assert q.dtype == torch.bfloat16 and kv_cache.dtype == torch.bfloat16
     assert (q_stride * 2) % 16 == 0 and q.data_ptr() % 16 == 0 and out.is_contiguous()
+    kv_map = kv_tensor_map(kv_cache) if not window else None
     code = lib.get("attention_prefill").mstar_paged_prefill_attention_bf16(
-        q.data_ptr(), q_stride, out.data_ptr(), kv_cache.data_ptr(), block_table.data_ptr(),
-        block_table.stride(0), qo_indptr.data_ptr(), kv_len.data_ptr(), first_entry, entries,
-        max_q_len, num_heads, num_kv_heads, head_dim, page_size, window, float(scale), _stream())
+        kv_map or 0, q.data_ptr(), q_stride, out.data_ptr(), kv_cache.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), qo_indptr.data_ptr(), kv_len.data_ptr(),
+        first_entry, entries, max_q_len, num_heads, num_kv_heads, head_dim, page_size, window,
+        float(scale), tcgen05_error_word(q.device).data_ptr(), _stream())
     if code == -1:
         raise KernelError(f"prefill attention refuses heads={num_heads}, kv_heads={num_kv_heads}, "
                           f"head_dim={head_dim} (head_dim in {FAST_ATTENTION_HEAD_DIMS})")
