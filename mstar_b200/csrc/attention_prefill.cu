@@ -58,7 +58,9 @@ prefill_attention_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillArgs
     bf16* Qs = stages + 2 * 2 * PRE_TILE * HD;         // [64][HD]
     __shared__ __align__(8) uint64_t full_bar[2];
 
-    const int tile = blockIdx.x, kvh = blockIdx.y, e = a.first_entry + blockIdx.z;
+    // the last row tiles see the most keys: schedule them first, so that the short tiles of
+    // the prompt's start fill the tail of the grid
+    const int tile = gridDim.x - 1 - blockIdx.x, kvh = blockIdx.y, e = a.first_entry + blockIdx.z;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int G = a.nq / a.nkv;
     const int q_start = a.qo_indptr[e];

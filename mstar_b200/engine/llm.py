@@ -76,6 +76,9 @@ class LLM:
         self.log_stats = log_stats
         self.stats = EngineStats()
         self._auto_id = 0
+        # a decode step that has been launched but whose tokens have not been read back
+        self._inflight = None
+        self.pipelined_steps = 0
 
     def _pages_from_memory(self, page_size: int, fraction: float) -> list:
         free, _ = torch.cuda.mem_get_info(self.device)
@@ -110,31 +113,109 @@ class LLM:
         return request_id
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None
+
+    # -- one step ---------------------------------------------------------
+    # Steady decoding is pipelined one step deep, as the reference's worker does
+    # (mstar/worker/worker.py:2118-2211, 1328-1550: step N+1 is built and submitted
+    # while step N runs, and a stop takes effect one step late, worker.py:1612-1629):
+    # after launching step N the engine does not wait for its tokens; the next call
+    # launches step N+1 for the same requests with the tokens taken on the device, and
+    # only then reads step N's tokens back.  A request that turns out to have stopped at
+    # step N has one token computed in vain; a request that reaches max_output_tokens is
+    # foreseen and left out.
+
+    def _launch(self, plan) -> tuple:
+        """Run the plan's forward pass and sampling; tokens stay on the device."""
+        entries = [StepEntry(e.request.request_id, e.tokens,
+                             (len(e.tokens) - 1,) if e.samples else ())
+                   for e in plan.entries]
+        logits = self.stepper.step(entries)
+        sampling = [e.request.request_id for e in plan.entries if e.samples]
+        tokens = self.sampler.sample(sampling, logits) if sampling else None
+        return sampling, tokens
+
+    def _account(self, plan, sampled: dict) -> list:
+        finished = self.scheduler.update(plan, sampled)
+        self.stats.steps += 1
+        self.stats.prompt_tokens += sum(len(e.tokens) for e in plan.entries if not (
+            e.samples and len(e.tokens) == 1))
+        self.stats.generated_tokens += len(sampled)
+        return finished
+
+    def _try_pipeline(self, prev) -> Optional[tuple]:
+        """Launch the decode step that follows the in-flight one, if it can be foreseen:
+        nothing waits to be admitted, and every request of the in-flight step was
+        decoding.  Returns the new in-flight record, or None."""
+        plan, sampling, tokens = prev
+        if self.scheduler.waiting or tokens is None or len(sampling) != len(plan.entries):
+            return None
+        if any(len(e.tokens) != 1 for e in plan.entries):
+            return None
+        if len(plan.entries) != len(self.scheduler.running):
+            return None
+        keep = [i for i, e in enumerate(plan.entries)
+                if len(e.request.output) + 1 < e.request.params.max_output_tokens]
+        if not keep:
+            return None
+        requests = [plan.entries[i].request for i in keep]
+        ids = [r.request_id for r in requests]
+        from ..cache.manager import CacheExhausted
+        from .scheduler import ScheduledEntry, StepPlan
+
+        source = tokens if len(keep) == len(plan.entries) else tokens[
+            torch.tensor(keep, dtype=torch.long, device=self.device)]
+        try:
+            logits = self.stepper.step_decode_from_device(ids, source)
+        except CacheExhausted:
+            return None                      # the scheduler decides who gives up pages
+        if logits is None:
+            return None
+        next_tokens = self.sampler.sample(ids, logits)
+        next_plan = StepPlan(entries=[ScheduledEntry(r, [None], True) for r in requests])
+        self.pipelined_steps += 1
+        return next_plan, ids, next_tokens
 
     def step(self) -> list:
         """Schedule and run one batch; returns the requests that finished."""
         t0 = time.perf_counter()
+        finished: list = []
+        if self._inflight is not None:
+            prev = self._inflight
+            nxt = self._try_pipeline(prev)                    # launch N+1 first ...
+            plan, sampling, tokens = prev
+            sampled = dict(zip(sampling, tokens.tolist()))    # ... then read N back
+            finished += self._account(plan, sampled)
+            if nxt is not None:
+                # requests that stopped at step N ran step N+1 in vain: drop them
+                nplan, nids, ntokens = nxt
+                alive = [i for i, e in enumerate(nplan.entries) if e.request.status == "running"]
+                if len(alive) != len(nplan.entries):
+                    nplan.entries = [nplan.entries[i] for i in alive]
+                    nids = [nids[i] for i in alive]
+                    ntokens = ntokens[torch.tensor(alive, dtype=torch.long, device=self.device)] \
+                        if alive else None
+                for e in nplan.entries:                       # the token fed was step N's
+                    e.tokens = [e.request.output[-1]]
+                nxt = (nplan, nids, ntokens) if nplan.entries else None
+            self._inflight = nxt
+            if self.log_stats:
+                self.stats.step_seconds.append(time.perf_counter() - t0)
+            return finished
         plan = self.scheduler.schedule()
-        finished = list(plan.finished)
+        finished += list(plan.finished)
         self.stats.preemptions += len(plan.preempted)
         for r in plan.admitted:
             self.sampler.add_request(r.request_id, r.params, r.slot, generated=r.output)
         if plan.entries:
-            entries = [StepEntry(e.request.request_id, e.tokens,
-                                 (len(e.tokens) - 1,) if e.samples else ())
-                       for e in plan.entries]
-            logits = self.stepper.step(entries)
-            sampling = [e.request.request_id for e in plan.entries if e.samples]
-            sampled = {}
-            if sampling:
-                tokens = self.sampler.sample(sampling, logits).tolist()
-                sampled = dict(zip(sampling, tokens))
-            finished += self.scheduler.update(plan, sampled)
-            self.stats.steps += 1
-            self.stats.prompt_tokens += sum(len(e.tokens) for e in plan.entries if not (
-                e.samples and len(e.tokens) == 1))
-            self.stats.generated_tokens += len(sampled)
+            sampling, tokens = self._launch(plan)
+            decode_only = (tokens is not None and len(sampling) == len(plan.entries)
+                           and all(len(e.tokens) == 1 for e in plan.entries))
+            if decode_only and self.stepper.cuda_graphs:
+                self._inflight = (plan, sampling, tokens)     # read back at the next call
+            else:
+                sampled = dict(zip(sampling, tokens.tolist())) if sampling else {}
+                finished += self._account(plan, sampled)
         elif not plan.preempted and not plan.finished and self.scheduler.has_work():
             raise RuntimeError("the scheduler can make no progress: no request fits the cache")
         if self.log_stats:

@@ -136,9 +136,14 @@ class DecodeGraph:
         self.events[turn] = ev
         return self.size * 4
 
-    def run(self, requests: list, tokens: list) -> torch.Tensor:
+    def run(self, requests: list, tokens: list, device_tokens=None) -> torch.Tensor:
+        """``device_tokens``: int32 tensor on the device holding the requests' tokens (the
+        sampler's output of the previous step); it replaces ``tokens`` without the host
+        ever seeing the values."""
         nbytes = self._stage(requests, tokens)
         self.stepper.last_h2d_bytes = nbytes
+        if device_tokens is not None:
+            self.token_ids[:len(requests)].copy_(device_tokens)
         self.graph.replay()
         ops_lib.add_launches(self.launches)
         return self.logits[:len(requests)]
@@ -242,7 +247,17 @@ class Stepper:
         return logits
 
 
-    def _step_decode_graph(self, entries: list):
+    def step_decode_from_device(self, requests: list, device_tokens: torch.Tensor):
+        """One decode step for ``requests`` whose next tokens are still on the device
+        (``device_tokens``, int32, one per request, in order): the step is launched
+        without waiting for them.  Logits for every request; None if this batch cannot
+        run as a captured graph (the caller then takes the ordinary path)."""
+        if not self.cuda_graphs or _bucket(len(requests)) is None:
+            return None
+        entries = [StepEntry(r, (0,), (0,)) for r in requests]
+        return self._step_decode_graph(entries, device_tokens=device_tokens)
+
+    def _step_decode_graph(self, entries: list, device_tokens=None):
         """A batch of single tokens as the replay of a captured graph; None when the
         batch is larger than the largest captured shape."""
         bucket = _bucket(len(entries))
@@ -255,7 +270,7 @@ class Stepper:
         graph = self._graphs.get(key)
         if graph is None:
             graph = self._graphs[key] = DecodeGraph(self, bucket, list(widths))
-        logits = graph.run(requests, [e.tokens[0] for e in entries])
+        logits = graph.run(requests, [e.tokens[0] for e in entries], device_tokens)
         for request in requests:
             self.manager.commit(request, 1)
         self.steps += 1
