@@ -429,6 +429,255 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
     }
 }
 
+// [rows, K] bf16 row-major with leading dimension ld (elements); box = box_rows x 64
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return -3;
+    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    const cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                          box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : -4;
+}
+
+static int pairs_on_gpu() {
+    static int pairs = 0;
+    if (pairs == 0) {
+        int dev = 0, sms = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        pairs = sms > 1 ? sms / 2 : 1;
+    }
+    return pairs;
+}
+
+// ------------------------------------------------- persistent pairs, overlapped epilogue
+// As many CTA pairs as the GPU holds at once walk over the tiles (row tiles fastest, so
+// that pairs working at the same time share W tiles in L2).  Each CTA's tensor memory
+// holds two accumulators of 256 columns: while the epilogue warps read and store tile j,
+// the MMAs of tile j+1 already run into the other one.  Two more barrier pairs do the
+// hand-over: "accumulator full" (the leader's commit, arriving in both CTAs) and
+// "accumulator empty" (one arrival per epilogue warp of both CTAs on the leader's barrier).
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr)
+                 : "memory");
+}
+
+template <int BN, int STAGES, bool GATED, typename OutT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS)
+gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+                               const __grid_constant__ CUtensorMap map_b, OutT* __restrict__ out, int M,
+                               int N, int K, int ldo, int tiles_m, int tiles_total,
+                               int* __restrict__ error_word) {
+    static_assert(BN == 256 || BN == 192 || BN == 128, "pair tile width");
+    static_assert(!GATED || BN == 256, "the gated form keeps gate and up in 128 columns each");
+    constexpr int OUT_COLS = GATED ? BN / 2 : BN;
+    constexpr uint32_t A_BYTES = TC_BM * TC_BK * 2;
+    constexpr uint32_t B_BYTES = (BN / 2) * TC_BK * 2;
+    constexpr uint32_t STAGE_BYTES = A_BYTES + B_BYTES;
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* tiles = reinterpret_cast<unsigned char*>(
+        (reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+    __shared__ __align__(8) uint64_t full_bar[STAGES];
+    __shared__ __align__(8) uint64_t empty_bar[STAGES];
+    __shared__ __align__(8) uint64_t acc_full[2];
+    __shared__ __align__(8) uint64_t acc_empty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(tc_smem(&full_bar[s]), 1);
+            mbar_init(tc_smem(&empty_bar[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(tc_smem(&acc_full[b]), 1);
+            mbar_init(tc_smem(&acc_empty[b]), 8);  // four epilogue warps in each of two CTAs
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         tc_smem(&tmem_base_slot)),
+                     "r"(512u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;  // k-blocks loaded so far, over all tiles
+            for (int t = pair; t < tiles_total; t += num_pairs) {
+                const int m0 = (t % tiles_m) * 2 * TC_BM + (int)rank * TC_BM;
+                const int n0 = (t / tiles_m) * OUT_COLS;
+                const int w_row0 = GATED ? (int)rank * N + n0 : n0 + (int)rank * (BN / 2);
+                bool ok = true;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t phase = (it / STAGES) & 1u;
+                    if (!mbar_wait(tc_smem(&empty_bar[s]), phase ^ 1u)) {
+                        atomicExch(error_word, 1);
+                        abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t leader_bar = map_to_rank(tc_smem(&full_bar[s]), 0);
+                    if (rank == 0) mbar_expect_tx(tc_smem(&full_bar[s]), 2 * STAGE_BYTES);
+                    unsigned char* stage = tiles + (size_t)s * STAGE_BYTES;
+                    tma_load_2d_pair(tc_smem(stage), &map_a, leader_bar, kb * TC_BK, m0);
+                    tma_load_2d_pair(tc_smem(stage + A_BYTES), &map_b, leader_bar, kb * TC_BK, w_row0);
+                }
+                if (!ok || *(volatile int*)&abort_flag) break;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = instr_desc_bf16(2 * TC_BM, BN);
+            uint32_t it = 0;
+            int j = 0;  // tiles done by this pair
+            bool ok = true;
+            for (int t = pair; t < tiles_total && ok; t += num_pairs, ++j) {
+                const int b = j & 1;
+                if (!mbar_wait(tc_smem(&acc_empty[b]), (((uint32_t)j >> 1) & 1u) ^ 1u)) {
+                    atomicExch(error_word, 6);
+                    abort_flag = 1;
+                    break;
+                }
+                tc_fence_after_sync();
+                const uint32_t tmem_d = tmem_base + (uint32_t)b * 256;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t phase = (it / STAGES) & 1u;
+                    if (!mbar_wait(tc_smem(&full_bar[s]), phase)) {
+                        atomicExch(error_word, 2);
+                        abort_flag = 1;
+                        ok = false;
+                        break;
+                    }
+                    tc_fence_after_sync();
+                    const uint32_t a_addr = tc_smem(tiles + (size_t)s * STAGE_BYTES);
+                    const uint32_t b_addr = a_addr + A_BYTES;
+#pragma unroll
+                    for (int k4 = 0; k4 < TC_BK / 16; ++k4)
+                        tc_mma_pair(tmem_d, smem_desc_sw128(a_addr + k4 * 32),
+                                    smem_desc_sw128(b_addr + k4 * 32), idesc, (kb | k4) != 0 ? 1u : 0u);
+                    tc_commit_pair(tc_smem(&empty_bar[s]));
+                }
+                if (ok) tc_commit_pair(tc_smem(&acc_full[b]));
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        const bool vec_ok = (ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
+        int j = 0;
+        for (int t = pair; t < tiles_total; t += num_pairs, ++j) {
+            const int b = j & 1;
+            const bool ready = mbar_wait(tc_smem(&acc_full[b]), ((uint32_t)j >> 1) & 1u);
+            if (!ready || *(volatile int*)&abort_flag) {
+                if (!ready && lane == 0) {
+                    atomicExch(error_word, 3);
+                    abort_flag = 1;
+                }
+                break;
+            }
+            tc_fence_after_sync();
+            const int m0 = (t % tiles_m) * 2 * TC_BM + (int)rank * TC_BM;
+            const int n0 = (t / tiles_m) * OUT_COLS;
+            const int row = m0 + quarter * 32 + lane;
+            const uint32_t tbase = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)b * 256;
+            if (!GATED) {
+                // read 64 columns at a time; after the last read the accumulator is free
+                // for the MMAs of the tile after next, the stores follow
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 64) {
+                    uint32_t r[2][32];
+                    tc_ld32(tbase + (uint32_t)c0, r[0]);
+                    tc_ld32(tbase + (uint32_t)(c0 + 32), r[1]);
+                    tc_wait_ld();
+                    if (c0 + 64 == BN) {
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_remote(map_to_rank(tc_smem(&acc_empty[b]), 0));
+                    }
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        const int col = n0 + c0 + c * 32;
+                        if (row < M && col < N)
+                            store32<OutT>(out + (size_t)row * ldo + col, r[c], min(32, N - col), vec_ok);
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c0 = 0; c0 < OUT_COLS; c0 += 32) {
+                    uint32_t r[32], u[32];
+                    tc_ld32(tbase + (uint32_t)c0, r);
+                    tc_ld32(tbase + (uint32_t)(c0 + BN / 2), u);
+                    tc_wait_ld();
+                    if (c0 + 32 == OUT_COLS) {
+                        tc_fence_before_sync();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_remote(map_to_rank(tc_smem(&acc_empty[b]), 0));
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const float g = __bfloat162float(__float2bfloat16_rn(__uint_as_float(r[i])));
+                        const float v = __bfloat162float(__float2bfloat16_rn(__uint_as_float(u[i])));
+                        r[i] = __float_as_uint(g / (1.f + expf(-g)) * v);
+                    }
+                    const int col = n0 + c0;
+                    if (row < M && col < N)
+                        store32<OutT>(out + (size_t)row * ldo + col, r, min(32, N - col), vec_ok);
+                }
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    cluster_sync_all();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u)
+                     : "memory");
+    }
+}
+
+template <int BN, int STAGES, bool GATED, typename OutT>
+static int launch_tc_persistent(const CUtensorMap& ma, const CUtensorMap& mb, OutT* out, int M, int N,
+                                int K, int ldo, int* error_word, cudaStream_t s) {
+    const size_t smem = (size_t)STAGES * (TC_BM + BN / 2) * TC_BK * 2 + 1024;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_persistent_kernel<BN, STAGES, GATED, OutT>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int out_cols = GATED ? BN / 2 : BN;
+    const int tiles_m = (M + 2 * TC_BM - 1) / (2 * TC_BM);
+    const int tiles_n = (N + out_cols - 1) / out_cols;
+    const int total = tiles_m * tiles_n;
+    const int on_gpu = pairs_on_gpu();
+    const int pairs = total < on_gpu ? total : on_gpu;
+    gemm_tcgen05_persistent_kernel<BN, STAGES, GATED, OutT><<<2 * pairs, TC_THREADS, smem, s>>>(
+        ma, mb, out, M, N, K, ldo, tiles_m, total, error_word);
+    return launch_status();
+}
+
 template <int STAGES, bool GATED, typename OutT>
 static int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, OutT* out, int M, int N, int K,
                           int ldo, int* error_word, cudaStream_t s) {
@@ -448,20 +697,6 @@ static int launch_tc_pair(const CUtensorMap& ma, const CUtensorMap& mb, OutT* ou
 }
 
 // ------------------------------------------------------------------------------- host
-// [rows, K] bf16 row-major with leading dimension ld (elements); box = box_rows x 64
-static int make_map(CUtensorMap* map, const void* base, int rows, int K, int ld, int box_rows) {
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (fn == nullptr) return -3;
-    const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    const cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
-                          box, elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : -4;
-}
-
 template <int BN, int STAGES, typename OutT>
 static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, OutT* out, int M, int N, int K, int ldo,
                      int* error_word, cudaStream_t s) {
@@ -480,7 +715,9 @@ static int launch_tc(const CUtensorMap& ma, const CUtensorMap& mb, OutT* out, in
 }
 
 // out[M,N] = x[M,K] W[N,K]^T.  out_dtype MSTAR_BF16 or MSTAR_F32; bn 128 or 256: lone CTAs
-// with 128 x bn tiles; bn 512: pairs of CTAs with 256 x 256 tiles.
+// with 128 x bn tiles; bn 512: pairs of CTAs with 256 x 256 tiles, one tile per pair; bn
+// 1024: persistent pairs that walk over the tiles and overlap each tile's epilogue with
+// the next tile's MMAs.
 // `error_word`: device int, zero before the call; a kernel that gave up on a wait writes
 // 1 (producer), 2 (MMA issuer) or 3 (epilogue) there.  Returns 0, a CUDA error code, -1
 // when the shape is refused (K or a leading dimension not a multiple of 8 elements,
@@ -500,8 +737,8 @@ MSTAR_API int mstar_gemm_tcgen05_gated_bf16(const void* x, const void* W, void* 
     if (rc != 0) return rc;
     rc = make_map(&mb, W, N, K, ldw, 128);
     if (rc != 0) return rc;
-    return launch_tc_pair<6, true, bf16>(ma, mb, (bf16*)out, M, N / 2, K, ldo, error_word,
-                                         (cudaStream_t)stream);
+    return launch_tc_persistent<256, 6, true, bf16>(ma, mb, (bf16*)out, M, N / 2, K, ldo, error_word,
+                                                    (cudaStream_t)stream);
 }
 
 MSTAR_API int mstar_gemm_tcgen05_bf16(const void* x, const void* W, void* out, int M, int N, int K,
@@ -510,13 +747,22 @@ MSTAR_API int mstar_gemm_tcgen05_bf16(const void* x, const void* W, void* out, i
     if (M <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return -1;
     if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(W) & 15)) return -1;
-    if (bn != 128 && bn != 256 && bn != 512) return -1;
+    if (bn != 128 && bn != 256 && bn != 512 && bn != 1024) return -1;
     CUtensorMap ma, mb;
     int rc = make_map(&ma, x, M, K, ldx, TC_BM);
     if (rc != 0) return rc;
-    rc = make_map(&mb, W, N, K, ldw, bn == 512 ? 128 : bn);
+    rc = make_map(&mb, W, N, K, ldw, bn >= 512 ? 128 : bn);
     if (rc != 0) return rc;
     cudaStream_t s = (cudaStream_t)stream;
+    if (bn == 1024) {  // persistent pairs with overlapped epilogue
+        // (narrower pair tiles, 192 or 128 columns, were measured for the shapes whose 256-wide
+        // tiles fill the pairs unevenly: no gain, the kernel is bound by operand traffic per
+        // k-block, which narrower tiles do not reduce)
+        if (out_dtype == MSTAR_F32)
+            return launch_tc_persistent<256, 6, false, float>(ma, mb, (float*)out, M, N, K, ldo,
+                                                              error_word, s);
+        return launch_tc_persistent<256, 6, false, bf16>(ma, mb, (bf16*)out, M, N, K, ldo, error_word, s);
+    }
     if (bn == 512) {  // pairs of CTAs, 256 x 256 tiles
         if (out_dtype == MSTAR_F32)
             return launch_tc_pair<6, false, float>(ma, mb, (float*)out, M, N, K, ldo, error_word, s);

@@ -367,7 +367,8 @@ def _tc_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 def tcgen05_tile(m: int, n: int) -> int | None:
     """Which tcgen05 kernel takes an [m, K] x [n, K]^T product, or None for the library
-    GEMM: 256 = lone CTAs with 128 x 256 tiles, 512 = CTA pairs with 256 x 256 tiles.
+    GEMM: 256 = lone CTAs with 128 x 256 tiles, 1024 = persistent CTA pairs with 256 x 256
+    tiles (512: the same pairs, one tile each).
     The hand-written kernels are used where their grid fills the GPU: very wide
     matrices (the LM head) at any row count, and wide ones (gate/up) at prompt size.
     ``MSTAR_GEMM=tcgen05`` forces them everywhere, ``MSTAR_GEMM=library`` nowhere."""
@@ -377,11 +378,11 @@ def tcgen05_tile(m: int, n: int) -> int | None:
     if forced == "library":
         return None
     if n >= 32768:
-        return 256 if m <= 256 else 512
+        return 256 if m <= 256 else 1024
     if m >= 1024 and n >= 8192:
-        return 512
+        return 1024
     if forced == "tcgen05":
-        return 512 if m > 128 else 256
+        return 1024 if m > 128 else 256
     return None
 
 

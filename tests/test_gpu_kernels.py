@@ -488,7 +488,7 @@ def tc_clean():
     return code
 
 
-@pytest.mark.parametrize("bn", [128, 256, 512])
+@pytest.mark.parametrize("bn", [128, 256, 512, 1024])
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (1, 8, 8), (200, 300, 136), (513, 1000, 776),
                                    (64, 2048, 3072), (300, 130, 4096)])
 def test_tcgen05_gemm(bn, m, n, k):
@@ -536,9 +536,9 @@ def test_tcgen05_refusals_and_dispatch(monkeypatch):
     with pytest.raises(ops.KernelError, match="refuses"):
         ops.gemm_tcgen05(x, w)
     assert ops.linear(x, w).shape == (32, 64)       # the library product takes it
-    assert ops.tcgen05_tile(2048, 16384) == 512 and ops.tcgen05_tile(64, 156940) == 256
+    assert ops.tcgen05_tile(2048, 16384) == 1024 and ops.tcgen05_tile(64, 156940) == 256
     assert ops.tcgen05_tile(2048, 3072) is None
     monkeypatch.setenv("MSTAR_GEMM", "tcgen05")
-    assert ops.tcgen05_tile(2048, 3072) == 512
+    assert ops.tcgen05_tile(2048, 3072) == 1024
     monkeypatch.setenv("MSTAR_GEMM", "library")
     assert ops.tcgen05_tile(2048, 16384) is None
