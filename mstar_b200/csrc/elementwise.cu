@@ -43,7 +43,7 @@ MSTAR_API int mstar_embed_rows(const void* table, int table_dtype, const int* id
 // One block per row.  The sum of squares is accumulated per thread over a fixed
 // stride and then reduced in a fixed tree, so a row's result does not depend on
 // which other rows are in the batch.
-template <typename A, typename W>
+template <typename A, typename W, bool VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const A* __restrict__ delta,
                                    const W* __restrict__ weight, A* __restrict__ out, int hidden,
                                    float eps, float w_offset) {
@@ -51,6 +51,35 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const A* __restric
     const size_t base = (size_t)blockIdx.x * hidden;
     float* r = resid + base;
     float ss = 0.f;
+    if (VEC) {
+        // eight elements per thread and step, 16-byte accesses; the order in which a row's
+        // squares are summed depends only on the row's width and the block size
+        const int chunks = hidden >> 3;
+        for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+            float v[8];
+            load8(r + 8 * c, v);
+            if (delta != nullptr) {
+                float d[8];
+                load8(delta + base + 8 * c, d);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] += d[i];
+                store8(r + 8 * c, v);
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);
+        }
+        const float total = block_sum(ss, scratch);
+        const float inv = rsqrtf(total / (float)hidden + eps);
+        for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
+            float v[8], w[8];
+            load8(r + 8 * c, v);  // what this thread wrote itself
+            load8(weight + 8 * c, w);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = v[i] * inv * (w[i] + w_offset);
+            store8(out + base + 8 * c, v);
+        }
+        return;
+    }
     if (delta != nullptr) {
         const A* d = delta + base;
         for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
@@ -78,14 +107,21 @@ MSTAR_API int mstar_add_rmsnorm(float* resid, const void* delta, const void* wei
                                 float eps, float w_offset, void* stream) {
     if (rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-#define LAUNCH(A, W)                                                                        \
-    add_rmsnorm_kernel<A, W><<<rows, threads, 0, s>>>(resid, (const A*)delta, (const W*)weight, \
-                                                      (A*)out, hidden, eps, w_offset)
+    const bool vec = hidden % 8 == 0 && ((uintptr_t)resid % 32 == 0) && ((uintptr_t)out % 16 == 0) &&
+                     ((uintptr_t)weight % 32 == 0) && (delta == nullptr || (uintptr_t)delta % 16 == 0);
+    int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    if (vec) threads = hidden >= 4096 ? 512 : (hidden >= 2048 ? 256 : 128);
+#define LAUNCH(A, W)                                                                             \
+    if (vec)                                                                                     \
+        add_rmsnorm_kernel<A, W, true><<<rows, threads, 0, s>>>(                                 \
+            resid, (const A*)delta, (const W*)weight, (A*)out, hidden, eps, w_offset);          \
+    else                                                                                         \
+        add_rmsnorm_kernel<A, W, false><<<rows, threads, 0, s>>>(                                \
+            resid, (const A*)delta, (const W*)weight, (A*)out, hidden, eps, w_offset)
     if (act_dtype == MSTAR_F32) {
-        if (weight_dtype == MSTAR_F32) LAUNCH(float, float); else LAUNCH(float, bf16);
+        if (weight_dtype == MSTAR_F32) { LAUNCH(float, float); } else { LAUNCH(float, bf16); }
     } else {
-        if (weight_dtype == MSTAR_F32) LAUNCH(bf16, float); else LAUNCH(bf16, bf16);
+        if (weight_dtype == MSTAR_F32) { LAUNCH(bf16, float); } else { LAUNCH(bf16, bf16); }
     }
 #undef LAUNCH
     return launch_status();
@@ -251,6 +287,77 @@ __global__ void rope_kv_write_kernel(A* __restrict__ qkv, const int* __restrict_
     }
 }
 
+// Vector form of the kernel above for split-half pairs whose halves are multiples of 8
+// features: a thread rotates 8 pairs (two 16-byte loads, two 16-byte stores) or copies
+// 8 values; same arithmetic per element.
+template <typename A>
+__global__ void rope_kv_write_vec_kernel(A* __restrict__ qkv, const int* __restrict__ positions,
+                                         const int* __restrict__ cache_pos,
+                                         const int* __restrict__ token_req,
+                                         const int* __restrict__ block_table,
+                                         const float* __restrict__ inv_freq,
+                                         A* __restrict__ kv_cache, RopeArgs a) {
+    const int t = blockIdx.x;
+    const int hd = a.hd, half = a.rotary_dim / 2;
+    const int row_elems = (a.nq + 2 * a.nkv) * hd;
+    A* row = qkv + (size_t)t * row_elems;
+    const bool write = kv_cache != nullptr;
+    const int hchunks = half >> 3;                         // 8-pair chunks per head
+    const int rot_items = (write ? a.nq + a.nkv : a.nq) * hchunks;
+    const int tail = hd - a.rotary_dim;                    // multiple of 8 on this path
+    const int tail_items = write ? a.nkv * (tail >> 3) : 0;
+    const int v_items = write ? a.nkv * (hd >> 3) : 0;
+    const int total = rot_items + tail_items + v_items;
+    const int first = blockIdx.y * blockDim.x + threadIdx.x;
+    const int stride = gridDim.y * blockDim.x;
+    if (first >= total) return;
+
+    A* kdst = nullptr;
+    A* vdst = nullptr;
+    if (write) {
+        const int cp = cache_pos[t];
+        const int page = block_table[(size_t)token_req[t] * a.bt_stride + cp / a.page_size];
+        const int slot = cp % a.page_size;
+        const size_t page_elems = (size_t)2 * a.nkv * a.page_size * hd;
+        kdst = kv_cache + (size_t)page * page_elems + (size_t)slot * hd;
+        vdst = kdst + (size_t)a.nkv * a.page_size * hd;
+    }
+    const float pos = (float)positions[t];
+    for (int item = first; item < total; item += stride) {
+        if (item < rot_items) {
+            const int h = item / hchunks, j0 = (item - h * hchunks) * 8;
+            A* src = row + (size_t)h * hd;
+            float x0[8], x1[8], f[8], y0[8], y1[8];
+            load8(src + j0, x0);
+            load8(src + j0 + half, x1);
+            load8(inv_freq + j0, f);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                float sn, cs;
+                sincosf(pos * f[i], &sn, &cs);
+                y0[i] = x0[i] * cs - x1[i] * sn;
+                y1[i] = x1[i] * cs + x0[i] * sn;
+            }
+            A* dst = h < a.nq ? src : kdst + (size_t)(h - a.nq) * a.page_size * hd;
+            store8(dst + j0, y0);
+            store8(dst + j0 + half, y1);
+        } else if (item < rot_items + tail_items) {
+            const int it = item - rot_items;
+            const int per = tail >> 3;
+            const int h = it / per, d = a.rotary_dim + (it - h * per) * 8;
+            *reinterpret_cast<uint4*>(kdst + (size_t)h * a.page_size * hd + d) =
+                *reinterpret_cast<const uint4*>(row + (size_t)(a.nq + h) * hd + d);
+        } else {
+            const int it = item - rot_items - tail_items;
+            const int per = hd >> 3;
+            const int h = it / per, d = (it - h * per) * 8;
+            float v[8];
+            load8(row + (size_t)(a.nq + a.nkv + h) * hd + d, v);
+            store8(vdst + (size_t)h * a.page_size * hd + d, v);
+        }
+    }
+}
+
 MSTAR_API int mstar_rope_kv_write(void* qkv, int act_dtype, const int* positions,
                                   const int* cache_pos, const int* token_req,
                                   const int* block_table, int bt_stride, const float* inv_freq,
@@ -260,6 +367,22 @@ MSTAR_API int mstar_rope_kv_write(void* qkv, int act_dtype, const int* positions
     cudaStream_t s = (cudaStream_t)stream;
     RopeArgs a{nq, nkv, hd, rotary_dim, interleaved, page_size, bt_stride};
     const int threads = 256;
+    // split-half pairs, halves and the unrotated tail in whole groups of 8, float angles
+    // table aligned: the vector kernel; else one pair per item
+    const bool vec = !interleaved && rotary_dim > 0 && (rotary_dim / 2) % 8 == 0 && hd % 8 == 0 &&
+                     (hd - rotary_dim) % 8 == 0 && ((uintptr_t)qkv % 32 == 0) &&
+                     ((uintptr_t)inv_freq % 32 == 0) && (kv_cache == nullptr || (uintptr_t)kv_cache % 32 == 0) &&
+                     act_dtype == MSTAR_BF16;
+    if (vec) {
+        const int items = (nq + nkv) * (rotary_dim / 16) + nkv * ((hd - rotary_dim) / 8) + nkv * (hd / 8);
+        int slices = (items + threads - 1) / threads;
+        if (num_tokens >= 256 && slices > 1) slices = 1;
+        if (slices < 1) slices = 1;
+        dim3 grid(num_tokens, slices);
+        rope_kv_write_vec_kernel<bf16><<<grid, threads, 0, s>>>(
+            (bf16*)qkv, positions, cache_pos, token_req, block_table, inv_freq, (bf16*)kv_cache, a);
+        return launch_status();
+    }
     const int items = (nq + nkv) * (rotary_dim / 2) + nkv * (hd - rotary_dim) + nkv * hd;
     // few tokens: one item per thread; many tokens: fewer, longer-running slices
     int slices = (items + threads - 1) / threads;
