@@ -322,10 +322,6 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeAr
         mbar_init(tc_smem(&full_bar[1]), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    // rows that no copy fills (beyond the request's last page) must hold finite numbers:
-    // their probabilities are zero, but 0 * NaN is not
-    for (int i = tid; i < 2 * 2 * DEC_TILE * HD / 8; i += DEC_THREADS)
-        reinterpret_cast<uint4*>(stages)[i] = make_uint4(0u, 0u, 0u, 0u);
     const bf16* qrow = a.q + (size_t)t * a.q_stride + (size_t)kvh * G * HD;
     for (int i = tid; i < 16 * CPR; i += DEC_THREADS) {
         const int r = i / CPR, c = i - r * CPR;
@@ -336,15 +332,19 @@ decode_attention_tma_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeAr
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     __syncthreads();
 
+    // Every tile is filled completely: pages beyond the request's last one are replaced by
+    // that last page, so that rows whose keys are masked still hold finite numbers (their
+    // probabilities are zero, but 0 * NaN is not) without clearing shared memory first.
+    const int last_page = (hi - 1) / ps;
     auto issue_tile = [&](int stage, int base) {  // one thread
-        const int pages = (min(ke, base + DEC_TILE) - base + ps - 1) / ps;
+        const int npages = DEC_TILE / ps;
         const uint32_t bar = tc_smem(&full_bar[stage]);
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        mbar_expect_tx(bar, (uint32_t)pages * ps * HD * 2 * 2);
+        mbar_expect_tx(bar, 2 * TILE_BYTES);
         unsigned char* kdst = reinterpret_cast<unsigned char*>(stages) + (size_t)stage * 2 * TILE_BYTES;
         unsigned char* vdst = kdst + TILE_BYTES;
-        for (int p = 0; p < pages; ++p) {
-            const int page = bt[base / ps + p];
+        for (int p = 0; p < npages; ++p) {
+            const int page = bt[min(base / ps + p, last_page)];
             const int krow = ((page * 2) * a.nkv + kvh) * ps;
             const int vrow = ((page * 2 + 1) * a.nkv + kvh) * ps;
 #pragma unroll

@@ -164,11 +164,18 @@ def fast_attention_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: i
             and num_heads % num_kv_heads == 0 and num_heads // num_kv_heads <= 16)
 
 
+# CTAs of the decode attention grid per SM that the split of the keys aims for
+DECODE_FILL = 6
+
+
 def decode_split(tokens: int, num_kv_heads: int, max_len: int) -> tuple:
     """(chunk, splits) of the keys for split-K decode attention: enough CTAs to fill
     the GPU a few times over, chunks in whole tiles of 64 keys."""
+    import os
+
     pairs = max(tokens * num_kv_heads, 1)
-    want = max(1, -(-NUM_SMS * 6 // pairs))
+    fill = int(os.environ.get("MSTAR_DECODE_FILL", DECODE_FILL))
+    want = max(1, -(-NUM_SMS * fill // pairs))
     want = min(want, 256)                       # the merge kernel takes up to 256 splits
     chunk = max(64, -(-(-(-max_len // want)) // 64) * 64)
     splits = max(1, -(-max_len // chunk))
