@@ -1,0 +1,502 @@
+// Paged causal prefill attention on the fifth-generation tensor cores (tcgen05), bfloat16,
+// head_dim 128.  Same semantics as attention_prefill.cu (rows are (token, query head of
+// the group) pairs, causal end-aligned mask, float softmax); what differs is where the
+// work runs.
+//
+// One CTA owns 128 rows and one kv head; the CTAs with the most keys are launched first.
+// Per tile of 64 keys:
+//   * the producer warp brings the keys and the values by TMA (one box of [page_size x 64]
+//     per page and 64-feature half, 128-byte swizzle, issued side by side from several
+//     lanes) into two rings of two stages;
+//   * a lane of the S warp issues S = Q K^T as tcgen05.mma (M 128, N 64, K 16 x 8) into
+//     tensor memory, as soon as the softmax threads hold the tile before in registers;
+//   * 128 softmax threads each own one row: they read their row of S from tensor memory
+//     (tcgen05.ld; the row maximum and sum need no shuffles), and write the probabilities
+//     as packed bfloat16 into one of two P buffers in tensor memory (tcgen05.st), so P
+//     never passes through shared memory; they rescale their row of the running output O
+//     in tensor memory only when the row maximum grew by more than 2^8;
+//   * a lane of the O warp issues O += P V (M 128, N 128, K 16 x 4) with P as the A
+//     operand from tensor memory and V as the N-major B operand straight from the
+//     cache's [key][feature] tiles.
+// At the end each thread reads its row of O, divides by the softmax sum and stores.
+// Two CTAs fit on an SM (97 KB of shared memory, 256 TMEM columns each: S 64, P 2 x 32,
+// O 128), so one CTA's softmax overlaps the other's MMAs.
+//
+// Shared-memory descriptors: Q and K are K-major with the 128-byte swizzle (8-row groups
+// 1024 bytes apart); V is MN-major (features contiguous): 8-key groups 1024 bytes apart
+// (stride byte offset), the two 64-feature halves 8192 bytes apart (leading byte offset).
+// Every mbarrier wait is bounded; a timeout is recorded in the error word.
+//
+// The reference calls a library for this (mstar/utils/flashinfer_utils.py:136-156).
+#include <string.h>
+
+#include "common.cuh"
+#include "tma_util.cuh"
+
+#define PT_ROWS 128
+#define PT_KEYS 64
+#define PT_HD 128
+#define PT_THREADS 224  // 4 softmax warps, the S-issuing warp, the TMA warp, the O-issuing warp
+
+struct PrefillTcArgs {
+    const bf16* q;
+    const int* block_table;
+    const int* qo_indptr;
+    const int* kv_len;
+    bf16* out;
+    int q_stride, bt_stride, nq, nkv, page_size, first_entry;
+    float scale_log2e;
+};
+
+__device__ __forceinline__ void pt_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void pt_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void pt_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void pt_mma(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t idesc,
+                                       uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// the same with the A operand in tensor memory (M lanes x K/2 columns of packed pairs)
+__device__ __forceinline__ void pt_mma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t db, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "r"(tmem_a), "l"(db), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void pt_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]),
+          "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]),
+          "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]),
+          "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+}
+__device__ __forceinline__ void pt_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+          "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]),
+          "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]),
+          "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]),
+          "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void pt_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void pt_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+// descriptor bits common to all operands here: version 1 [46,48), SWIZZLE_128B [61,64)
+__device__ __forceinline__ uint64_t pt_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    return (uint64_t)((addr >> 4) & 0x3FFF) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16) |
+           ((uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32) | (1ull << 46) | (2ull << 61);
+}
+// kind::f16 instruction descriptor: D float, A and B bfloat16, b_major (bit 16) = 1 for an
+// MN-major B operand
+__host__ __device__ constexpr uint32_t pt_idesc(int m, int n, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) |
+           ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+// Shared memory of one CTA: Q, two stages of keys, two of values, then the barriers.
+#define PT_Q_BYTES (PT_ROWS * PT_HD * 2)        // 32 KB: two halves [128 rows x 64]
+#define PT_KV_TILE (PT_KEYS * PT_HD * 2)        // 16 KB: two halves [64 keys x 64]
+#define PT_SMEM (PT_Q_BYTES + 4 * PT_KV_TILE + 128)
+// The running maximum of a row follows the tile maxima only when they exceed it by more
+// than this (in powers of two): probabilities then reach 2^8 at most, which float sums and
+// bfloat16's relative precision take, and the output in tensor memory is rarely rescaled.
+#define PT_MAX_SLACK 8.0f
+
+__device__ __forceinline__ float pt_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__global__ void __launch_bounds__(PT_THREADS)
+prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillTcArgs a,
+                            int* __restrict__ error_word) {
+    constexpr int HD = PT_HD;
+    extern __shared__ __align__(1024) unsigned char smem_dyn[];
+    unsigned char* q_s = smem_dyn;
+    unsigned char* k_s = q_s + PT_Q_BYTES;          // [2 stages]
+    unsigned char* v_s = k_s + 2 * PT_KV_TILE;      // [2 stages]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * PT_KV_TILE);
+    // k_full[2], v_full[2]: a stage's copies have landed.  k_empty[2]: S of the stage's tile
+    // is done.  v_empty[2]: O += P V of the stage's tile is done (the values may be refilled,
+    // the tile's P overwritten, O rescaled or read).  s_full: S of a tile is done; s_read: all
+    // softmax threads hold it in registers (the next S may overwrite it).  p_ready[2]: P of a
+    // tile is written.  The last three take one arrival per softmax thread or per commit and
+    // go through one phase per tile (per two tiles for the pairs).
+    const uint32_t k_full = tc_smem(bars + 0), v_full = tc_smem(bars + 2), k_empty = tc_smem(bars + 4),
+                   v_empty = tc_smem(bars + 6), p_ready = tc_smem(bars + 8), s_full = tc_smem(bars + 10),
+                   s_read = tc_smem(bars + 11);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
+
+    // grid: x the kv head, y the row tile with the longest first (the tiles with the most keys
+    // are launched before the short ones), z the entry
+    const int tile = gridDim.y - 1 - blockIdx.y, kvh = blockIdx.x, e = a.first_entry + blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = a.nq / a.nkv;
+    const int q_start = a.qo_indptr[e];
+    const int q_len = a.qo_indptr[e + 1] - q_start;
+    const int rows_total = q_len * G;
+    const int row0 = tile * PT_ROWS;
+    if (row0 >= rows_total) return;
+    if ((tc_smem(smem_dyn) & 1023u) != 0) {         // the swizzled tiles need this alignment
+        if (tid == 0) atomicExch(error_word, 6);
+        return;
+    }
+    const int past = a.kv_len[e] - q_len;
+    const int last_row = min(rows_total, row0 + PT_ROWS) - 1;
+    const int hi = past + last_row / G + 1;       // keys 0 .. hi-1 are visible to some row
+    const int ntiles = (hi + PT_KEYS - 1) / PT_KEYS;
+    const int* bt = a.block_table + (size_t)e * a.bt_stride;
+    const int ps = a.page_size;
+
+    const uint32_t q_ready = tc_smem(bars + 12);
+    if (tid == 0) {
+        for (int i = 0; i < 13; ++i)
+            mbar_init(tc_smem(bars + i), i == 8 || i == 9 || i == 11 || i == 12 ? 128 : 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                         tc_smem(tmem_slot)),
+                     "r"(256u)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    pt_fence_before();
+    __syncthreads();
+    pt_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_s = tmem;         // S: columns 0..63
+    const uint32_t tmem_p = tmem + 64;    // P: two buffers of 32 columns (64 packed keys each)
+    const uint32_t tmem_o = tmem + 128;   // O: columns 128..255
+
+    if (warp == 5) {
+        // ------------------------------------------------------------- TMA producer
+        // The whole warp runs the loop: its lanes fetch 32 block-table entries at a time
+        // (one dependent global load per page would cost more than the copies), lane 0
+        // waits for the stages and issues the copies.
+        const int last_page = (hi - 1) / ps;
+        const int per_tile = PT_KEYS / ps;            // pages per tile: 1, 2, 4 or 8
+        int mine = 0, have_from = -1;                 // lanes hold pages have_from .. +31
+        bool ok = true;
+        for (int j = 0; j < ntiles; ++j) {
+            const int s = j & 1;
+            const uint32_t free_parity = (((uint32_t)j >> 1) & 1u) ^ 1u;
+            const int base_page = j * per_tile;
+            if (have_from < 0 || base_page + per_tile > have_from + 32) {
+                have_from = base_page;
+                // pages beyond the last are replaced by the last: masked rows stay finite
+                mine = bt[min(base_page + lane, last_page)];
+            }
+            // keys, as soon as S of tile j-2 is done
+            if (lane == 0 && !mbar_wait(k_empty + 8 * s, free_parity)) {
+                atomicExch(error_word, 7);
+                ok = false;
+            }
+            if (!__shfl_sync(0xffffffffu, (int)ok, 0)) break;
+            // lane 2p + h copies half h of page p: the copies are issued side by side
+            const int p = lane >> 1, h = lane & 1;
+            const int page = __shfl_sync(0xffffffffu, mine, (base_page + p - have_from) & 31);
+            const uint32_t dst_off = (uint32_t)(s * PT_KV_TILE + h * (PT_KEYS * 128) + p * ps * 128);
+            if (lane == 0) mbar_expect_tx(k_full + 8 * s, PT_KV_TILE);
+            __syncwarp();
+            if (p < per_tile)
+                tma_load_2d(tc_smem(k_s + dst_off), &kv_map, k_full + 8 * s, h * 64,
+                            ((page * 2) * a.nkv + kvh) * ps);
+            // values, once O += P V of tile j-2 is done
+            if (lane == 0 && !mbar_wait(v_empty + 8 * s, free_parity)) {
+                atomicExch(error_word, 7);
+                ok = false;
+            }
+            if (!__shfl_sync(0xffffffffu, (int)ok, 0)) break;
+            if (lane == 0) mbar_expect_tx(v_full + 8 * s, PT_KV_TILE);
+            __syncwarp();
+            if (p < per_tile)
+                tma_load_2d(tc_smem(v_s + dst_off), &kv_map, v_full + 8 * s, h * 64,
+                            ((page * 2 + 1) * a.nkv + kvh) * ps);
+        }
+    } else if (warp == 4) {
+        // ------------------------------------------------ S = Q K^T, while the softmax works on
+        // the tile before
+        if (lane == 0) {
+            constexpr uint32_t idesc_s = pt_idesc(PT_ROWS, PT_KEYS, 0);
+            const uint32_t q_addr = tc_smem(q_s);
+            bool q_there = mbar_wait(q_ready, 0);
+            if (!q_there) atomicExch(error_word, 8);
+            for (int j = 0; j < ntiles && q_there; ++j) {
+                const int s = j & 1;
+                const uint32_t parity = ((uint32_t)j >> 1) & 1u;
+                if (!mbar_wait(k_full + 8 * s, parity)) {
+                    atomicExch(error_word, 8);
+                    break;
+                }
+                // 8 k-steps of 16 features; features 64.. live in the second half-tile.  The
+                // descriptors are made before the wait that the softmax threads end.
+                const uint32_t k_addr = tc_smem(k_s + s * PT_KV_TILE);
+                uint64_t dq[HD / 16], dk[HD / 16];
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    dq[kk] = pt_desc(q_addr + (uint32_t)(kk >> 2) * (PT_ROWS * 128) + (uint32_t)(kk & 3) * 32, 16, 1024);
+                    dk[kk] = pt_desc(k_addr + (uint32_t)(kk >> 2) * (PT_KEYS * 128) + (uint32_t)(kk & 3) * 32, 16, 1024);
+                }
+                // the softmax threads hold S of tile j-1 in registers
+                if (j >= 1 && !mbar_wait(s_read, (uint32_t)(j - 1) & 1u)) {
+                    atomicExch(error_word, 8);
+                    break;
+                }
+                pt_fence_after();
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) pt_mma(tmem_s, dq[kk], dk[kk], idesc_s, kk != 0);
+                pt_commit(s_full);
+                pt_commit(k_empty + 8 * s);
+            }
+        }
+    } else if (warp == 6) {
+        // ------------------------------------------------ O += P V, V the N-major operand
+        if (lane == 0) {
+            constexpr uint32_t idesc_o = pt_idesc(PT_ROWS, HD, 1);
+            for (int j = 0; j < ntiles; ++j) {
+                const int s = j & 1;
+                const uint32_t parity = ((uint32_t)j >> 1) & 1u;
+                if (!mbar_wait(v_full + 8 * s, parity)) {
+                    atomicExch(error_word, 9);
+                    break;
+                }
+                // the softmax threads have replaced S by P and rescaled O where needed
+                if (!mbar_wait(p_ready + 8 * s, parity)) {
+                    atomicExch(error_word, 9);
+                    break;
+                }
+                pt_fence_after();
+                // 4 k-steps of 16 keys (8 columns of packed P); V rows are keys, 8-key
+                // groups 1024 bytes apart, the two 64-feature halves 8192 bytes apart
+                const uint32_t v_addr = tc_smem(v_s + s * PT_KV_TILE);
+#pragma unroll
+                for (int kk = 0; kk < PT_KEYS / 16; ++kk) {
+                    const uint64_t db = pt_desc(v_addr + (uint32_t)kk * 16 * 128, PT_KEYS * 128, 1024);
+                    pt_mma_ts(tmem_o, tmem_p + (uint32_t)s * 32 + (uint32_t)kk * 8, db, idesc_o, (j | kk) != 0);
+                }
+                pt_commit(v_empty + 8 * s);   // the values are consumed, O holds tiles 0..j
+            }
+        }
+    } else if (warp < 4) {
+        // ------------------------------------------------------ softmax, one row per thread
+        // the 128 query rows -> shared, K-major with the 128-byte swizzle: 16 chunks of 16
+        // bytes per thread, all loads in flight before the first store
+        {
+            uint4 v[16];
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                const int i = tid + 128 * k, qr = i >> 4, c = i & 15;
+                const int qrow = row0 + qr;
+                v[k] = make_uint4(0u, 0u, 0u, 0u);
+                if (qrow < rows_total) {
+                    const int tok = q_start + qrow / G, head = kvh * G + qrow % G;
+                    v[k] = *reinterpret_cast<const uint4*>(a.q + (size_t)tok * a.q_stride + (size_t)head * HD + c * 8);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+                const int i = tid + 128 * k, qr = i >> 4, c = i & 15;
+                const uint32_t off = (uint32_t)(c >> 3) * (PT_ROWS * 128) + (uint32_t)qr * 128 +
+                                     (uint32_t)(((c & 7) ^ (qr & 7)) << 4);
+                *reinterpret_cast<uint4*>(q_s + off) = v[k];
+            }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_arrive(q_ready);
+        }
+        const int r = tid;                              // row of the tile = TMEM lane
+        const int row = row0 + r;
+        const int cp = past + min(row, rows_total - 1) / G;   // newest key this row sees
+        const int cp_min = past + row0 / G;                   // ... and any row of this CTA
+        const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
+        const float scale = a.scale_log2e;
+        float m = -INFINITY, l = 0.f;     // m: the reference maximum, in scaled (log2) units
+        bool ok = true;
+        for (int j = 0; j < ntiles; ++j) {
+            if (!mbar_wait(s_full, (uint32_t)j & 1u)) {
+                if (lane == 0) atomicExch(error_word, 10);
+                ok = false;
+                break;
+            }
+            pt_fence_after();
+            uint32_t s0[32], s1[32];
+            pt_ld32(tmem_s + lane_off, s0);
+            pt_ld32(tmem_s + lane_off + 32, s1);
+            pt_wait_ld();
+            pt_fence_before();
+            mbar_arrive(s_read);                          // the next S may be computed
+            const int key0 = j * PT_KEYS;
+            if (key0 + PT_KEYS - 1 > cp_min) {            // the tile touches the diagonal
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    if (key0 + i > cp) s0[i] = 0xff800000u;          // -inf
+                    if (key0 + 32 + i > cp) s1[i] = 0xff800000u;
+                }
+            }
+            float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                mx0 = fmaxf(mx0, __uint_as_float(s0[i]));
+                mx1 = fmaxf(mx1, __uint_as_float(s1[i]));
+            }
+            const float mx = fmaxf(mx0, mx1) * scale;     // scale > 0
+            // key 0 is visible to every row, so m is finite from the first tile on
+            float alpha = 1.f;
+            if (mx > m + PT_MAX_SLACK) {
+                alpha = pt_ex2(m - mx);
+                m = mx;
+            }
+            float sum0 = 0.f, sum1 = 0.f;
+            uint32_t packed[32];
+#pragma unroll
+            for (int i = 0; i < 32; i += 2) {
+                const float p0 = pt_ex2(fmaf(__uint_as_float(s0[i]), scale, -m));
+                const float p1 = pt_ex2(fmaf(__uint_as_float(s0[i + 1]), scale, -m));
+                const float p2 = pt_ex2(fmaf(__uint_as_float(s1[i]), scale, -m));
+                const float p3 = pt_ex2(fmaf(__uint_as_float(s1[i + 1]), scale, -m));
+                sum0 += p0 + p1;
+                sum1 += p2 + p3;
+                __nv_bfloat162 lo = __floats2bfloat162_rn(p0, p1), hi2 = __floats2bfloat162_rn(p2, p3);
+                packed[i >> 1] = *reinterpret_cast<uint32_t*>(&lo);
+                packed[16 + (i >> 1)] = *reinterpret_cast<uint32_t*>(&hi2);
+            }
+            l = l * alpha + (sum0 + sum1);
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                // O += P V of tile j-1 must be done before O is rescaled
+                if (!mbar_wait(v_empty + 8 * ((j - 1) & 1), ((uint32_t)(j - 1) >> 1) & 1u)) {
+                    if (lane == 0) atomicExch(error_word, 11);
+                    ok = false;
+                    break;
+                }
+                pt_fence_after();
+#pragma unroll 1
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    uint32_t o[32];
+                    pt_ld32(tmem_o + lane_off + (uint32_t)c0, o);
+                    pt_wait_ld();
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    pt_st32(tmem_o + lane_off + (uint32_t)c0, o);
+                }
+            }
+            // P of tile j-2 lies in this tile's buffer until O += P V of that tile is done
+            if (j >= 2 && !mbar_wait(v_empty + 8 * (j & 1), ((uint32_t)(j - 2) >> 1) & 1u)) {
+                if (lane == 0) atomicExch(error_word, 11);
+                ok = false;
+                break;
+            }
+            // column c of the buffer holds keys 2c, 2c+1
+            pt_st32(tmem_p + lane_off + (uint32_t)(j & 1) * 32, packed);
+            pt_wait_st();
+            pt_fence_before();
+            mbar_arrive(p_ready + 8 * (j & 1));
+        }
+        if (ok && !mbar_wait(v_empty + 8 * ((ntiles - 1) & 1), ((uint32_t)(ntiles - 1) >> 1) & 1u)) {
+            if (lane == 0) atomicExch(error_word, 12);
+            ok = false;
+        }
+        pt_fence_after();
+        if (ok) {
+            const float inv = 1.f / l;
+            const bool valid = row < rows_total;
+            bf16* dst = nullptr;
+            if (valid) {
+                const int tok = q_start + row / G, head = kvh * G + row % G;
+                dst = a.out + (size_t)tok * a.nq * HD + (size_t)head * HD;
+            }
+#pragma unroll 1
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t o[32];
+                pt_ld32(tmem_o + lane_off + (uint32_t)c0, o);
+                pt_wait_ld();
+                if (valid) {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        float f[8];
+#pragma unroll
+                        for (int t = 0; t < 8; ++t) f[t] = __uint_as_float(o[8 * i + t]) * inv;
+                        store8(dst + c0 + 8 * i, f);
+                    }
+                }
+            }
+        }
+    }
+    pt_fence_before();
+    __syncthreads();
+    if (warp == 4) {
+        pt_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u)
+                     : "memory");
+    }
+}
+
+// Entries [first_entry, first_entry + entries) of the batch.  head_dim must be 128, the
+// page size 8..64 dividing 64, no window.  `kv_map`: the cache's tensor map.  Returns 0, a
+// CUDA error code or -1 (shape refused).  `error_word` receives 6..12 if a wait ran out
+// (6: the shared memory was not aligned as the swizzle needs).
+MSTAR_API int mstar_paged_prefill_attention_tc(
+    const void* kv_map, const void* q, int q_stride, void* out, const int* block_table, int bt_stride,
+    const int* qo_indptr, const int* kv_len, int first_entry, int entries, int max_q_len, int nq,
+    int nkv, int hd, int page_size, float scale, int* error_word, void* stream) {
+    if (entries <= 0 || max_q_len <= 0) return 0;
+    if (hd != PT_HD || !(scale > 0.f) || nkv <= 0 || nq % nkv != 0 || kv_map == nullptr || error_word == nullptr) return -1;
+    if (page_size < 8 || page_size > 64 || PT_KEYS % page_size != 0) return -1;
+    if (entries > 65535) return -1;
+    PrefillTcArgs a;
+    a.q = (const bf16*)q;
+    a.block_table = block_table;
+    a.qo_indptr = qo_indptr;
+    a.kv_len = kv_len;
+    a.out = (bf16*)out;
+    a.q_stride = q_stride;
+    a.bt_stride = bt_stride;
+    a.nq = nq;
+    a.nkv = nkv;
+    a.page_size = page_size;
+    a.first_entry = first_entry;
+    a.scale_log2e = scale * 1.4426950408889634f;
+    CUtensorMap map;
+    memcpy(&map, kv_map, sizeof(map));
+    const size_t smem = PT_SMEM;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        // two CTAs per SM need nearly all of the SM's shared memory
+        e = cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 (int)cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int G = nq / nkv;
+    const long long tiles = ((long long)max_q_len * G + PT_ROWS - 1) / PT_ROWS;
+    if (tiles > 65535) return -1;
+    dim3 grid(nkv, (unsigned)tiles, entries);
+    prefill_attention_tc_kernel<<<grid, PT_THREADS, smem, (cudaStream_t)stream>>>(map, a, error_word);
+    return launch_status();
+}

@@ -247,6 +247,27 @@ def paged_decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
     check(code, "paged_decode_attention")
 
 
+# Rows ((token, head of the group) pairs) of the longest entry from which the tcgen05
+# prefill kernel, whose tiles are 128 rows, is chosen over the mma.sync one (64 rows).
+PREFILL_TC_MIN_ROWS = 96
+
+
+def prefill_attention_kernel(has_kv_map: bool, head_dim: int, page_size: int, max_q_len: int,
+                             group: int) -> str:
+    """"tcgen05" or "mma": which prefill attention kernel runs.  The tcgen05 kernel takes
+    head_dim 128, no window and page sizes 8..64 dividing 64; MSTAR_PREFILL_ATTENTION=mma|
+    tcgen05 forces one of them where both take the shape."""
+    import os
+
+    takes = has_kv_map and head_dim == 128 and 8 <= page_size <= 64 and 64 % page_size == 0
+    if not takes:
+        return "mma"
+    forced = os.environ.get("MSTAR_PREFILL_ATTENTION")
+    if forced in ("mma", "tcgen05"):
+        return forced
+    return "tcgen05" if max_q_len * group >= PREFILL_TC_MIN_ROWS else "mma"
+
+
 def paged_prefill_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv_cache,
                             block_table, qo_indptr, kv_len, first_entry: int, entries: int,
                             max_q_len: int, num_heads: int, num_kv_heads: int, head_dim: int,
@@ -257,6 +278,17 @@ def paged_prefill_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, k
     assert q.dtype == torch.bfloat16 and kv_cache.dtype == torch.bfloat16
     assert (q_stride * 2) % 16 == 0 and q.data_ptr() % 16 == 0 and out.is_contiguous()
     kv_map = kv_tensor_map(kv_cache) if not window else None
+    if prefill_attention_kernel(kv_map is not None, head_dim, page_size, max_q_len,
+                                num_heads // num_kv_heads) == "tcgen05":
+        code = lib.get("attention_prefill_tc").mstar_paged_prefill_attention_tc(
+            kv_map, q.data_ptr(), q_stride, out.data_ptr(), block_table.data_ptr(),
+            block_table.stride(0), qo_indptr.data_ptr(), kv_len.data_ptr(), first_entry, entries,
+            max_q_len, num_heads, num_kv_heads, head_dim, page_size, float(scale),
+            tcgen05_error_word(q.device).data_ptr(), _stream())
+        if code == -1:
+            raise KernelError("tcgen05 prefill attention refuses this shape")
+        check(code, "paged_prefill_attention_tc")
+        return
     code = lib.get("attention_prefill").mstar_paged_prefill_attention_bf16(
         kv_map or 0, q.data_ptr(), q_stride, out.data_ptr(), kv_cache.data_ptr(),
         block_table.data_ptr(), block_table.stride(0), qo_indptr.data_ptr(), kv_len.data_ptr(),

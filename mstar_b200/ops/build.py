@@ -34,6 +34,7 @@ LIBRARIES = {
     "attention_generic": ("cuda", ["attention_generic.cu"], []),
     "attention_decode": ("cuda", ["attention_decode.cu"], []),
     "attention_prefill": ("cuda", ["attention_prefill.cu"], []),
+    "attention_prefill_tc": ("cuda", ["attention_prefill_tc.cu"], []),
     "attention_decode_noalloc": ("cuda", ["attention_decode_noalloc.cu"], []),
     "gemm_f32": ("cuda", ["gemm_f32.cu"], []),
     "gemm_smallm": ("cuda", ["gemm_smallm.cu"], []),
