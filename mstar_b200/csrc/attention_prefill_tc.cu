@@ -1,5 +1,5 @@
 // Paged causal prefill attention on the fifth-generation tensor cores (tcgen05), bfloat16,
-// head_dim 128.  Same semantics as attention_prefill.cu (rows are (token, query head of
+// head_dim 64, 128 or 256.  Same semantics as attention_prefill.cu (rows are (token, query head of
 // the group) pairs, causal end-aligned mask, float softmax); what differs is where the
 // work runs.
 //
@@ -8,23 +8,24 @@
 //   * the producer warp brings the keys and the values by TMA (one box of [page_size x 64]
 //     per page and 64-feature half, 128-byte swizzle, issued side by side from several
 //     lanes) into two rings of two stages;
-//   * a lane of the S warp issues S = Q K^T as tcgen05.mma (M 128, N 64, K 16 x 8) into
+//   * a lane of the S warp issues S = Q K^T as tcgen05.mma (M 128, N 64, K 16 per step) into
 //     tensor memory, as soon as the softmax threads hold the tile before in registers;
 //   * 128 softmax threads each own one row: they read their row of S from tensor memory
 //     (tcgen05.ld; the row maximum and sum need no shuffles), and write the probabilities
 //     as packed bfloat16 into one of two P buffers in tensor memory (tcgen05.st), so P
 //     never passes through shared memory; they rescale their row of the running output O
 //     in tensor memory only when the row maximum grew by more than 2^8;
-//   * a lane of the O warp issues O += P V (M 128, N 128, K 16 x 4) with P as the A
+//   * a lane of the O warp issues O += P V (M 128, N head_dim, K 16 x 4) with P as the A
 //     operand from tensor memory and V as the N-major B operand straight from the
 //     cache's [key][feature] tiles.
 // At the end each thread reads its row of O, divides by the softmax sum and stores.
-// Two CTAs fit on an SM (97 KB of shared memory, 256 TMEM columns each: S 64, P 2 x 32,
-// O 128), so one CTA's softmax overlaps the other's MMAs.
+// At head_dim 128 two CTAs fit on an SM (97 KB of shared memory, 256 TMEM columns each:
+// S 64, P 2 x 32, O 128), so one CTA's softmax overlaps the other's MMAs; at 64 there is
+// room for more, at 256 (193 KB, 512 columns) for one.
 //
 // Shared-memory descriptors: Q and K are K-major with the 128-byte swizzle (8-row groups
 // 1024 bytes apart); V is MN-major (features contiguous): 8-key groups 1024 bytes apart
-// (stride byte offset), the two 64-feature halves 8192 bytes apart (leading byte offset).
+// (stride byte offset), the 64-feature blocks 8192 bytes apart (leading byte offset).
 // Every mbarrier wait is bounded; a timeout is recorded in the error word.
 //
 // The reference calls a library for this (mstar/utils/flashinfer_utils.py:136-156).
@@ -35,7 +36,6 @@
 
 #define PT_ROWS 128
 #define PT_KEYS 64
-#define PT_HD 128
 #define PT_THREADS 224  // 4 softmax warps, the S-issuing warp, the TMA warp, the O-issuing warp
 
 struct PrefillTcArgs {
@@ -116,10 +116,16 @@ __host__ __device__ constexpr uint32_t pt_idesc(int m, int n, int b_mn_major) {
            ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-// Shared memory of one CTA: Q, two stages of keys, two of values, then the barriers.
-#define PT_Q_BYTES (PT_ROWS * PT_HD * 2)        // 32 KB: two halves [128 rows x 64]
-#define PT_KV_TILE (PT_KEYS * PT_HD * 2)        // 16 KB: two halves [64 keys x 64]
-#define PT_SMEM (PT_Q_BYTES + 4 * PT_KV_TILE + 128)
+// Shared memory of one CTA: Q as blocks of [128 rows x 64 features], two stages of keys and
+// two of values as blocks of [64 keys x 64 features], then the barriers.
+__host__ __device__ constexpr int pt_q_bytes(int hd) { return PT_ROWS * hd * 2; }
+__host__ __device__ constexpr int pt_kv_tile(int hd) { return PT_KEYS * hd * 2; }
+__host__ __device__ constexpr int pt_smem(int hd) { return pt_q_bytes(hd) + 4 * pt_kv_tile(hd) + 128; }
+// What a launch asks for: at head_dim 64 more than the kernel uses, so that no more CTAs
+// land on an SM than its 512 TMEM columns serve (a further one would wait in its allocation).
+__host__ __device__ constexpr int pt_smem_launch(int hd) { return pt_smem(hd) < 77 * 1024 ? 77 * 1024 : pt_smem(hd); }
+// Tensor memory: S 64 columns, P 2 x 32, O head_dim; allocations are powers of two.
+__host__ __device__ constexpr uint32_t pt_tmem_cols(int hd) { return hd <= 128 ? 256u : 512u; }
 // The running maximum of a row follows the tile maxima only when they exceed it by more
 // than this (in powers of two): probabilities then reach 2^8 at most, which float sums and
 // bfloat16's relative precision take, and the output in tensor memory is rarely rescaled.
@@ -131,10 +137,12 @@ __device__ __forceinline__ float pt_ex2(float x) {
     return y;
 }
 
+template <int HD>
 __global__ void __launch_bounds__(PT_THREADS)
 prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillTcArgs a,
                             int* __restrict__ error_word) {
-    constexpr int HD = PT_HD;
+    constexpr int PT_Q_BYTES = pt_q_bytes(HD), PT_KV_TILE = pt_kv_tile(HD);
+    constexpr int NB = HD / 64;                     // 64-feature blocks of a row
     extern __shared__ __align__(1024) unsigned char smem_dyn[];
     unsigned char* q_s = smem_dyn;
     unsigned char* k_s = q_s + PT_Q_BYTES;          // [2 stages]
@@ -181,7 +189,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillT
     if (warp == 4) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
                          tc_smem(tmem_slot)),
-                     "r"(256u)
+                     "r"(pt_tmem_cols(HD))
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
@@ -191,7 +199,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillT
     const uint32_t tmem = *tmem_slot;
     const uint32_t tmem_s = tmem;         // S: columns 0..63
     const uint32_t tmem_p = tmem + 64;    // P: two buffers of 32 columns (64 packed keys each)
-    const uint32_t tmem_o = tmem + 128;   // O: columns 128..255
+    const uint32_t tmem_o = tmem + 128;   // O: head_dim columns from 128 on
 
     if (warp == 5) {
         // ------------------------------------------------------------- TMA producer
@@ -217,8 +225,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillT
                 ok = false;
             }
             if (!__shfl_sync(0xffffffffu, (int)ok, 0)) break;
-            // lane 2p + h copies half h of page p: the copies are issued side by side
-            const int p = lane >> 1, h = lane & 1;
+            // lane NB p + h copies block h of page p (at most 8 pages x 4 blocks): the copies
+            // are issued side by side
+            const int p = lane / NB, h = lane % NB;
             const int page = __shfl_sync(0xffffffffu, mine, (base_page + p - have_from) & 31);
             const uint32_t dst_off = (uint32_t)(s * PT_KV_TILE + h * (PT_KEYS * 128) + p * ps * 128);
             if (lane == 0) mbar_expect_tx(k_full + 8 * s, PT_KV_TILE);
@@ -304,26 +313,31 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillT
         }
     } else if (warp < 4) {
         // ------------------------------------------------------ softmax, one row per thread
-        // the 128 query rows -> shared, K-major with the 128-byte swizzle: 16 chunks of 16
-        // bytes per thread, all loads in flight before the first store
+        // the 128 query rows -> shared, K-major with the 128-byte swizzle: chunks of 16
+        // bytes, 8 loads per thread in flight before their stores
         {
-            uint4 v[16];
+            constexpr int CPR = HD / 8;                 // chunks per row
 #pragma unroll
-            for (int k = 0; k < 16; ++k) {
-                const int i = tid + 128 * k, qr = i >> 4, c = i & 15;
-                const int qrow = row0 + qr;
-                v[k] = make_uint4(0u, 0u, 0u, 0u);
-                if (qrow < rows_total) {
-                    const int tok = q_start + qrow / G, head = kvh * G + qrow % G;
-                    v[k] = *reinterpret_cast<const uint4*>(a.q + (size_t)tok * a.q_stride + (size_t)head * HD + c * 8);
+            for (int k0 = 0; k0 < CPR; k0 += 8) {
+                uint4 v[8];
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const int i = tid + 128 * (k0 + k), qr = i / CPR, c = i % CPR;
+                    const int qrow = row0 + qr;
+                    v[k] = make_uint4(0u, 0u, 0u, 0u);
+                    if (qrow < rows_total) {
+                        const int tok = q_start + qrow / G, head = kvh * G + qrow % G;
+                        v[k] = *reinterpret_cast<const uint4*>(a.q + (size_t)tok * a.q_stride +
+                                                               (size_t)head * HD + c * 8);
+                    }
                 }
-            }
 #pragma unroll
-            for (int k = 0; k < 16; ++k) {
-                const int i = tid + 128 * k, qr = i >> 4, c = i & 15;
-                const uint32_t off = (uint32_t)(c >> 3) * (PT_ROWS * 128) + (uint32_t)qr * 128 +
-                                     (uint32_t)(((c & 7) ^ (qr & 7)) << 4);
-                *reinterpret_cast<uint4*>(q_s + off) = v[k];
+                for (int k = 0; k < 8; ++k) {
+                    const int i = tid + 128 * (k0 + k), qr = i / CPR, c = i % CPR;
+                    const uint32_t off = (uint32_t)(c >> 3) * (PT_ROWS * 128) + (uint32_t)qr * 128 +
+                                         (uint32_t)(((c & 7) ^ (qr & 7)) << 4);
+                    *reinterpret_cast<uint4*>(q_s + off) = v[k];
+                }
             }
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             mbar_arrive(q_ready);
@@ -449,21 +463,41 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillT
     __syncthreads();
     if (warp == 4) {
         pt_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(pt_tmem_cols(HD))
                      : "memory");
     }
 }
 
-// Entries [first_entry, first_entry + entries) of the batch.  head_dim must be 128, the
-// page size 8..64 dividing 64, no window.  `kv_map`: the cache's tensor map.  Returns 0, a
-// CUDA error code or -1 (shape refused).  `error_word` receives 6..12 if a wait ran out
-// (6: the shared memory was not aligned as the swizzle needs).
+template <int HD>
+static int launch_prefill_tc(const CUtensorMap& map, const PrefillTcArgs& a, dim3 grid, int* error_word,
+                             cudaStream_t stream) {
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<HD>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, pt_smem_launch(HD));
+        if (e != cudaSuccess) return (int)e;
+        // several CTAs per SM need nearly all of the SM's shared memory
+        e = cudaFuncSetAttribute(prefill_attention_tc_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 (int)cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    prefill_attention_tc_kernel<HD><<<grid, PT_THREADS, pt_smem_launch(HD), stream>>>(map, a, error_word);
+    return launch_status();
+}
+
+// Entries [first_entry, first_entry + entries) of the batch.  head_dim must be 64, 128 or
+// 256, the page size 8..64 dividing 64, no window.  `kv_map`: the cache's tensor map.
+// Returns 0, a CUDA error code or -1 (shape refused).  `error_word` receives 6..12 if a wait
+// ran out (6: the shared memory was not aligned as the swizzle needs).
 MSTAR_API int mstar_paged_prefill_attention_tc(
     const void* kv_map, const void* q, int q_stride, void* out, const int* block_table, int bt_stride,
     const int* qo_indptr, const int* kv_len, int first_entry, int entries, int max_q_len, int nq,
     int nkv, int hd, int page_size, float scale, int* error_word, void* stream) {
     if (entries <= 0 || max_q_len <= 0) return 0;
-    if (hd != PT_HD || !(scale > 0.f) || nkv <= 0 || nq % nkv != 0 || kv_map == nullptr || error_word == nullptr) return -1;
+    if ((hd != 64 && hd != 128 && hd != 256) || !(scale > 0.f) || nkv <= 0 || nq % nkv != 0 ||
+        kv_map == nullptr || error_word == nullptr)
+        return -1;
     if (page_size < 8 || page_size > 64 || PT_KEYS % page_size != 0) return -1;
     if (entries > 65535) return -1;
     PrefillTcArgs a;
@@ -481,22 +515,13 @@ MSTAR_API int mstar_paged_prefill_attention_tc(
     a.scale_log2e = scale * 1.4426950408889634f;
     CUtensorMap map;
     memcpy(&map, kv_map, sizeof(map));
-    const size_t smem = PT_SMEM;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-        // two CTAs per SM need nearly all of the SM's shared memory
-        e = cudaFuncSetAttribute(prefill_attention_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                 (int)cudaSharedmemCarveoutMaxShared);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
     const int G = nq / nkv;
     const long long tiles = ((long long)max_q_len * G + PT_ROWS - 1) / PT_ROWS;
     if (tiles > 65535) return -1;
     dim3 grid(nkv, (unsigned)tiles, entries);
-    prefill_attention_tc_kernel<<<grid, PT_THREADS, smem, (cudaStream_t)stream>>>(map, a, error_word);
-    return launch_status();
+    switch (hd) {
+        case 64: return launch_prefill_tc<64>(map, a, grid, error_word, (cudaStream_t)stream);
+        case 128: return launch_prefill_tc<128>(map, a, grid, error_word, (cudaStream_t)stream);
+        default: return launch_prefill_tc<256>(map, a, grid, error_word, (cudaStream_t)stream);
+    }
 }

@@ -247,25 +247,17 @@ def paged_decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
     check(code, "paged_decode_attention")
 
 
-# Rows ((token, head of the group) pairs) of the longest entry from which the tcgen05
-# prefill kernel, whose tiles are 128 rows, is chosen over the mma.sync one (64 rows).
-PREFILL_TC_MIN_ROWS = 96
-
-
-def prefill_attention_kernel(has_kv_map: bool, head_dim: int, page_size: int, max_q_len: int,
-                             group: int) -> str:
+def prefill_attention_kernel(has_kv_map: bool, head_dim: int, page_size: int) -> str:
     """"tcgen05" or "mma": which prefill attention kernel runs.  The tcgen05 kernel takes
-    head_dim 128, no window and page sizes 8..64 dividing 64; MSTAR_PREFILL_ATTENTION=mma|
-    tcgen05 forces one of them where both take the shape."""
+    head_dim 64, 128 or 256, no window and page sizes 8..64 dividing 64, and is the faster
+    one from the shortest portions on; MSTAR_PREFILL_ATTENTION=mma selects the other one."""
     import os
 
-    takes = has_kv_map and head_dim == 128 and 8 <= page_size <= 64 and 64 % page_size == 0
-    if not takes:
+    takes = (has_kv_map and head_dim in (64, 128, 256) and 8 <= page_size <= 64
+             and 64 % page_size == 0)
+    if not takes or os.environ.get("MSTAR_PREFILL_ATTENTION") == "mma":
         return "mma"
-    forced = os.environ.get("MSTAR_PREFILL_ATTENTION")
-    if forced in ("mma", "tcgen05"):
-        return forced
-    return "tcgen05" if max_q_len * group >= PREFILL_TC_MIN_ROWS else "mma"
+    return "tcgen05"
 
 
 def paged_prefill_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv_cache,
@@ -278,8 +270,7 @@ def paged_prefill_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, k
     assert q.dtype == torch.bfloat16 and kv_cache.dtype == torch.bfloat16
     assert (q_stride * 2) % 16 == 0 and q.data_ptr() % 16 == 0 and out.is_contiguous()
     kv_map = kv_tensor_map(kv_cache) if not window else None
-    if prefill_attention_kernel(kv_map is not None, head_dim, page_size, max_q_len,
-                                num_heads // num_kv_heads) == "tcgen05":
+    if prefill_attention_kernel(kv_map is not None, head_dim, page_size) == "tcgen05":
         code = lib.get("attention_prefill_tc").mstar_paged_prefill_attention_tc(
             kv_map, q.data_ptr(), q_stride, out.data_ptr(), block_table.data_ptr(),
             block_table.stride(0), qo_indptr.data_ptr(), kv_len.data_ptr(), first_entry, entries,
