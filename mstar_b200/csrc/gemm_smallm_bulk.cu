@@ -1,0 +1,296 @@
+// y[M,N] = x[M,K] W[N,K]^T for few rows (M <= 16), bfloat16 in, float accumulation, with
+// the weights brought by bulk asynchronous copies (cp.async.bulk, global -> shared, mbarrier
+// completion) instead of register loads.
+//
+// Why: at these sizes the time of a product is the time to stream W once from HBM, and with
+// register loads a warp has at most a few kilobytes in flight, so a CTA lives through
+// several rounds of DRAM latency and the narrow projections (N = 3072 .. 5120) reach 40 %
+// of the memory bandwidth.  Here one lane asks for a CTA's rows as whole row segments of up
+// to 2 KB, three stages deep; with four CTAs on an SM about 200 KB per SM are in flight from
+// the first microsecond on, which is several times the latency-bandwidth product, and the
+// consumer warps only ever wait for data that is already on its way.
+//
+// A CTA owns strips of 8 NT output features (8 NT rows of W; twice that for the fused gate/up
+// form: rows n and inter + n) and walks over its strips (grid = what is resident at once,
+// further strips are taken in further turns without draining the ring).  NT is 1, 2 or 4:
+// the more rows share one read of x, the less traffic x causes (with 8 tokens and NT = 1 it
+// equals the traffic of W), so wide matrices, which have strips enough, take larger ones.
+// The bytes in flight per SM stay near 200 KB: 4, 2 or 1 CTAs per SM.  The K range of a strip is cut
+// into chunks of `KC` elements; a stage of the ring holds one chunk of every row, rows 64
+// bytes more than a chunk apart, which makes the 16-byte fragment reads free of bank
+// conflicts.  Eight consumer warps take the 32-element blocks of a chunk in turn, read their
+// fragments from shared memory (W rows as the 8-wide N of m16n8k16, the tokens as its M, k
+// assigned to threads as in gemm_smallm.cu) and x from global memory (it is small and stays
+// in L1/L2), and are summed through shared memory at the end of a strip.
+//
+// Every mbarrier wait is bounded; a wait that runs out sets the error word (13 producer, 14
+// consumer) and the CTA leaves (the consumer warps together, after their next barrier).
+// The reference uses the library GEMM for these products
+// (mstar/model/components/distributed/linear.py:101, mlp.py:78-81 for the gated form).
+#include <stdlib.h>
+
+#include "common.cuh"
+#include "mma_util.cuh"
+#include "tma_util.cuh"
+
+#define SB_WARPS 8                       // consumer warps
+#define SB_THREADS ((SB_WARPS + 1) * 32) // + the producer warp
+#define SB_STAGES 3
+#define SB_KC 1024                       // elements of K per chunk
+#define SB_PAD 64                        // bytes between the end of a row's chunk and the next row
+
+template <typename T> __device__ __forceinline__ void sb_store(T* p, float v);
+template <> __device__ __forceinline__ void sb_store<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void sb_store<bf16>(bf16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+        ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void sb_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__host__ __device__ constexpr int sb_rows(bool gated, int nt) { return (gated ? 16 : 8) * nt; }
+__host__ __device__ constexpr int sb_pitch() { return SB_KC * 2 + SB_PAD; }
+__host__ __device__ constexpr int sb_stage_bytes(bool gated, int nt) { return sb_rows(gated, nt) * sb_pitch(); }
+// ring, the warps' partial sums [row groups][warps][16][8], barriers
+__host__ __device__ constexpr int sb_smem(bool gated, int nt) {
+    return SB_STAGES * sb_stage_bytes(gated, nt) + (gated ? 2 : 1) * nt * SB_WARPS * 16 * 8 * 4 + 64;
+}
+
+// M16: tokens 8..15 exist (else the upper half of the MMA's rows is zero)
+template <bool GATED, bool M16, int NT, typename OutT>
+__global__ void __launch_bounds__(SB_THREADS, (GATED ? 2 : 4) / NT >= 1 ? (GATED ? 2 : 4) / NT : 1)
+smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* __restrict__ out, int M,
+                   int n_out, int K, int ldx, int ldw, int ldo, int inter, int* __restrict__ error_word) {
+    constexpr int STRIPS = GATED ? 2 : 1;
+    constexpr int GROUPS = STRIPS * NT;               // 8-row groups of a stage
+    constexpr int ROWS = 8 * GROUPS;
+    constexpr int PITCH = sb_pitch();
+    constexpr int STAGE = sb_stage_bytes(GATED, NT);
+    extern __shared__ __align__(128) unsigned char sb_smem_raw[];
+    unsigned char* ring = sb_smem_raw;
+    float* red = reinterpret_cast<float*>(ring + SB_STAGES * STAGE);           // [GROUPS][warps][16][8]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(red + GROUPS * SB_WARPS * 128);
+    const uint32_t full = tc_smem(bars), empty = tc_smem(bars + SB_STAGES);     // [SB_STAGES] each
+    volatile int* failed = reinterpret_cast<volatile int*>(bars + 2 * SB_STAGES);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nstrips = (n_out + 8 * NT - 1) / (8 * NT);
+    const int nch = (K + SB_KC - 1) / SB_KC;
+
+    if (tid == 0) {
+        *failed = 0;
+        for (int s = 0; s < SB_STAGES; ++s) {
+            mbar_init(full + 8 * s, 1);
+            mbar_init(empty + 8 * s, SB_WARPS);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == SB_WARPS) {
+        // ------------------------------------------------------------------ producer
+        // lane r asks for row r of the stage: rows n0 .. n0 + 8 NT - 1 (and inter + the same)
+        int c = 0;
+        bool ok = true;
+        for (int strip = blockIdx.x; strip < nstrips && ok; strip += gridDim.x) {
+            const int n0 = strip * 8 * NT;
+            const int row = min(n0 + lane % (8 * NT), n_out - 1) + (lane / (8 * NT)) * inter;
+            const bf16* src_row = W + (size_t)(lane < ROWS ? row : 0) * ldw;
+            for (int ch = 0; ch < nch; ++ch, ++c) {
+                const int st = c % SB_STAGES;
+                const uint32_t bytes = (uint32_t)min(SB_KC, K - ch * SB_KC) * 2;
+                if (lane == 0) {
+                    if (c >= SB_STAGES && !mbar_wait(empty + 8 * st, ((uint32_t)(c / SB_STAGES) - 1u) & 1u)) {
+                        atomicExch(error_word, 13);
+                        ok = false;
+                    } else {
+                        mbar_expect_tx(full + 8 * st, bytes * ROWS);
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+                if (!ok) break;
+                if (lane < ROWS)
+                    bulk_load(tc_smem(ring + st * STAGE + lane * PITCH), src_row + (size_t)ch * SB_KC, bytes,
+                              full + 8 * st);
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------------- consumers
+    const int g = lane >> 2, t = lane & 3;
+    const bf16* xa = x + (size_t)min(g, M - 1) * ldx + 8 * t;
+    const bf16* xb = x + (size_t)min(g + 8, M - 1) * ldx + 8 * t;
+    int c = 0;
+    for (int strip = blockIdx.x; strip < nstrips; strip += gridDim.x) {
+        const int n0 = strip * 8 * NT;
+        float acc[GROUPS][4];
+#pragma unroll
+        for (int s = 0; s < GROUPS; ++s) acc[s][0] = acc[s][1] = acc[s][2] = acc[s][3] = 0.f;
+        for (int ch = 0; ch < nch; ++ch, ++c) {
+            const int st = c % SB_STAGES;
+            const int nkb = min(SB_KC, K - ch * SB_KC) / 32;
+            // this warp's blocks of the chunk: warp, warp + 8, ...  (at most 4 of 32); x is asked
+            // for before the wait for W
+            constexpr int PER = SB_KC / 32 / SB_WARPS;
+            uint4 xv[PER], xw[PER];
+#pragma unroll
+            for (int u = 0; u < PER; ++u) {
+                const int kb = warp + u * SB_WARPS;
+                xv[u] = xw[u] = make_uint4(0u, 0u, 0u, 0u);
+                if (kb < nkb) {
+                    const int k = ch * SB_KC + kb * 32;
+                    xv[u] = __ldg(reinterpret_cast<const uint4*>(xa + k));
+                    if (M16) xw[u] = __ldg(reinterpret_cast<const uint4*>(xb + k));
+                }
+            }
+            if (!mbar_wait(full + 8 * st, (uint32_t)(c / SB_STAGES) & 1u)) {
+                // give up, but only together with the other warps (they wait at the barrier below)
+                if (lane == 0) atomicExch(error_word, 14);
+                *failed = 1;
+                break;
+            }
+            const unsigned char* stage = ring + st * STAGE;
+#pragma unroll
+            for (int u = 0; u < PER; ++u) {
+                const int kb = warp + u * SB_WARPS;
+                if (kb < nkb) {
+                    const uint32_t a1[4] = {xv[u].x, xw[u].x, xv[u].y, xw[u].y};
+                    const uint32_t a2[4] = {xv[u].z, xw[u].z, xv[u].w, xw[u].w};
+#pragma unroll
+                    for (int s = 0; s < GROUPS; ++s) {
+                        const uint4 wv = *reinterpret_cast<const uint4*>(stage + (s * 8 + g) * PITCH + kb * 64 + t * 16);
+                        mma_bf16_16816(acc[s], a1, wv.x, wv.y);
+                        mma_bf16_16816(acc[s], a2, wv.z, wv.w);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) sb_arrive(empty + 8 * st);
+        }
+        // ---- sum the warps' parts in shared memory: red[group][warp][token][W row]
+#pragma unroll
+        for (int s = 0; s < GROUPS; ++s) {
+            float* mine = red + ((s * SB_WARPS + warp) * 16) * 8;
+            mine[g * 8 + 2 * t] = acc[s][0];
+            mine[g * 8 + 2 * t + 1] = acc[s][1];
+            mine[(g + 8) * 8 + 2 * t] = acc[s][2];
+            mine[(g + 8) * 8 + 2 * t + 1] = acc[s][3];
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(SB_WARPS * 32) : "memory");
+        if (*failed) return;
+        // thread -> (token m, row r of an 8-row group, group j): r fastest, so that consecutive
+        // threads store consecutive features
+        for (int idx = tid; idx < 128 * NT; idx += SB_WARPS * 32) {
+            const int r = idx & 7, j = (idx >> 3) % NT, m = idx / (8 * NT);
+            const int n = n0 + 8 * j + r;
+            if (m < M && n < n_out) {
+                float v[STRIPS];
+#pragma unroll
+                for (int s = 0; s < STRIPS; ++s) {
+                    float sum = 0.f;
+#pragma unroll
+                    for (int w = 0; w < SB_WARPS; ++w)
+                        sum += red[(((s * NT + j) * SB_WARPS + w) * 16 + m) * 8 + r];
+                    v[s] = sum;
+                }
+                float y = v[0];
+                if (GATED) {
+                    // gate and up are rounded to bfloat16 first, as the unfused path stores them
+                    const float gate = __bfloat162float(__float2bfloat16_rn(v[0]));
+                    const float up = __bfloat162float(__float2bfloat16_rn(v[STRIPS - 1]));
+                    y = gate / (1.f + expf(-gate)) * up;
+                }
+                sb_store<OutT>(out + (size_t)m * ldo + n, y);
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(SB_WARPS * 32) : "memory");  // red is reused by the next strip
+    }
+}
+
+template <bool GATED, bool M16, int NT, typename OutT>
+static int launch_bulk_nt(const bf16* x, const bf16* W, OutT* out, int M, int n_out, int K, int ldx, int ldw,
+                          int ldo, int inter, int* error_word, cudaStream_t s) {
+    static int resident = 0;   // CTAs of this variant that fit on the GPU at once
+    auto kernel = smallm_bulk_kernel<GATED, M16, NT, OutT>;
+    constexpr int SMEM = sb_smem(GATED, NT);
+    if (resident == 0) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 (int)cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return (int)e;
+        int per_sm = 0, dev = 0, sms = 0;
+        e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, SB_THREADS, SMEM);
+        if (e != cudaSuccess) return (int)e;
+        if ((e = cudaGetDevice(&dev)) != cudaSuccess) return (int)e;
+        if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+        if (per_sm < 1) return -2;
+        resident = per_sm * sms;
+    }
+    const int nstrips = (n_out + 8 * NT - 1) / (8 * NT);
+    const int grid = nstrips < resident ? nstrips : resident;
+    kernel<<<grid, SB_THREADS, SMEM, s>>>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, error_word);
+    return launch_status();
+}
+
+// Rows of W per strip by the number of output features: 8 while the strips barely fill the
+// GPU, 16 and 32 where there are many (less traffic for x); the gated form has twice the rows
+// per strip already.  MSTAR_SMALLM_NT=1|2|4 forces one (for measurements).
+static int pick_nt(int n_out, bool gated) {
+    static int forced = -1;
+    if (forced < 0) {
+        const char* e = getenv("MSTAR_SMALLM_NT");
+        forced = e ? atoi(e) : 0;
+    }
+    int nt = n_out >= 32768 ? 4 : (n_out >= 1024 ? 2 : 1);
+    if (forced == 1 || forced == 2 || forced == 4) nt = forced;
+    if (gated && nt > 2) nt = 2;
+    return nt;
+}
+
+template <bool GATED, bool M16, typename OutT>
+static int launch_bulk(const bf16* x, const bf16* W, OutT* out, int M, int n_out, int K, int ldx, int ldw,
+                       int ldo, int inter, int* error_word, cudaStream_t s) {
+    switch (pick_nt(n_out, GATED)) {
+        case 4:
+            if constexpr (!GATED)
+                return launch_bulk_nt<GATED, M16, 4, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, error_word, s);
+        case 2: return launch_bulk_nt<GATED, M16, 2, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, error_word, s);
+        default: return launch_bulk_nt<GATED, M16, 1, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, error_word, s);
+    }
+}
+
+// out[M, N] = x W^T (gated == 0), or out[M, N/2] = silu(x Wg^T) * (x Wu^T) for W = [Wg; Wu]
+// (gated == 1, N even, bfloat16 out).  x: [M, K] bf16 with row stride ldx, W: [N, K] bf16 with
+// row stride ldw, out: bf16 or float (out_dtype) with row stride ldo.  Returns 0, a CUDA error
+// code, or -1 when the shape is refused: M outside 1..16, K no multiple of 32, leading
+// dimensions not multiples of 8 elements or pointers not 16-byte aligned (bulk copies), N odd
+// for the gated form.  `error_word`: device int, set to 13 / 14 if a bounded wait ran out.
+MSTAR_API int mstar_gemm_smallm_bulk_bf16(const void* x, const void* W, void* out, int M, int N, int K,
+                                          int ldx, int ldw, int ldo, int gated, int out_dtype,
+                                          int* error_word, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (M > 16 || K <= 0 || K % 32 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || error_word == nullptr) return -1;
+    if (((uintptr_t)x & 15) != 0 || ((uintptr_t)W & 15) != 0) return -1;
+    if (gated && (N % 2 != 0 || out_dtype != MSTAR_BF16)) return -1;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bf16* xp = (const bf16*)x;
+    const bf16* wp = (const bf16*)W;
+    if (gated) {
+        if (M > 8)
+            return launch_bulk<true, true, bf16>(xp, wp, (bf16*)out, M, N / 2, K, ldx, ldw, ldo, N / 2, error_word, s);
+        return launch_bulk<true, false, bf16>(xp, wp, (bf16*)out, M, N / 2, K, ldx, ldw, ldo, N / 2, error_word, s);
+    }
+    if (out_dtype == MSTAR_F32) {
+        if (M > 8) return launch_bulk<false, true, float>(xp, wp, (float*)out, M, N, K, ldx, ldw, ldo, 0, error_word, s);
+        return launch_bulk<false, false, float>(xp, wp, (float*)out, M, N, K, ldx, ldw, ldo, 0, error_word, s);
+    }
+    if (M > 8) return launch_bulk<false, true, bf16>(xp, wp, (bf16*)out, M, N, K, ldx, ldw, ldo, 0, error_word, s);
+    return launch_bulk<false, false, bf16>(xp, wp, (bf16*)out, M, N, K, ldx, ldw, ldo, 0, error_word, s);
+}

@@ -320,16 +320,37 @@ def _smallm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
+def smallm_kernel(m: int, gated: bool) -> str:
+    """"bulk" or "registers": which weight-streaming kernel takes a product of ``m`` rows.
+    The bulk-copy kernel (weights through a shared-memory ring filled by ``cp.async.bulk``)
+    is the faster one except for the fused gate/up form with at most 8 rows;
+    MSTAR_SMALLM=bulk|registers forces one."""
+    import os
+
+    forced = os.environ.get("MSTAR_SMALLM")
+    if forced in ("bulk", "registers"):
+        return forced
+    return "registers" if gated and m <= 8 else "bulk"
+
+
 def _gemm_smallm(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, gated: bool):
     m, k = x.shape
     n = w.shape[0]
     out = torch.empty((m, n // 2 if gated else n), dtype=out_dtype, device=x.device)
-    code = lib.get("gemm_smallm").mstar_gemm_smallm_bf16(
-        x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), w.stride(0),
-        out.stride(0), int(gated), _dt(out), _stream())
+    if smallm_kernel(m, gated) == "bulk":
+        code = lib.get("gemm_smallm_bulk").mstar_gemm_smallm_bulk_bf16(
+            x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), w.stride(0),
+            out.stride(0), int(gated), _dt(out), tcgen05_error_word(x.device).data_ptr(),
+            _stream())
+        what = "gemm_smallm_bulk"
+    else:
+        code = lib.get("gemm_smallm").mstar_gemm_smallm_bf16(
+            x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), w.stride(0),
+            out.stride(0), int(gated), _dt(out), _stream())
+        what = "gemm_smallm"
     if code == -1:
         raise KernelError(f"small-M GEMM refuses M={m}, N={n}, K={k}")
-    check(code, "gemm_smallm")
+    check(code, what)
     return out
 
 
@@ -337,8 +358,9 @@ _tc_error_words: dict = {}
 
 
 def tcgen05_error_word(device) -> torch.Tensor:
-    """Device int32 that a tcgen05 GEMM kernel sets when one of its bounded waits ran
-    out (1 producer, 2 MMA issuer, 3 epilogue); zero otherwise."""
+    """Device int32 that a kernel with bounded mbarrier waits sets when one of them ran out:
+    1-3 tcgen05 GEMM (producer, MMA issuer, epilogue), 4 decode attention copies, 6-12 tcgen05
+    prefill attention, 13-14 bulk-copy small-M GEMM; zero otherwise."""
     key = torch.device(device).index or 0
     if key not in _tc_error_words:
         _tc_error_words[key] = torch.zeros(1, dtype=torch.int32, device=device)

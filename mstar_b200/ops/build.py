@@ -38,6 +38,7 @@ LIBRARIES = {
     "attention_decode_noalloc": ("cuda", ["attention_decode_noalloc.cu"], []),
     "gemm_f32": ("cuda", ["gemm_f32.cu"], []),
     "gemm_smallm": ("cuda", ["gemm_smallm.cu"], []),
+    "gemm_smallm_bulk": ("cuda", ["gemm_smallm_bulk.cu"], []),
     "gemm_tcgen05": ("cuda", ["gemm_tcgen05.cu"], []),
     "sampling": ("cuda", ["sampling.cu"], []),
     "host": ("host", ["host/cache_manager.cpp"], []),

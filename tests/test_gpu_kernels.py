@@ -2,6 +2,7 @@
 than the engine's test models use (odd widths, head sizes in steps of 16, groups of
 1, 3 and 5, permuted pages, windows)."""
 import math
+import os
 
 import pytest
 import torch
@@ -463,13 +464,19 @@ def test_repetition_penalty_and_seen_mask():
     assert seen[2, 9] == 1 and seen.sum() == 2      # the sampled token is marked
 
 
+@pytest.mark.parametrize("variant", ["bulk", "registers"])
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
-@pytest.mark.parametrize("n,k", [(16, 32), (100, 96), (3000, 1024), (157, 3072)])
-def test_small_m_gemm(m, n, k):
-    """The weight-streaming product of decode steps: every M up to 16, N that is no
-    multiple of the 8-row strip, K from one block of 32 up, both output types."""
+@pytest.mark.parametrize("n,k", [(16, 32), (100, 96), (3000, 1024), (157, 3072), (33001, 64),
+                                 (1030, 2080)])
+def test_small_m_gemm(m, n, k, variant, monkeypatch):
+    """The weight-streaming products of decode steps, both kernels (weights through a
+    shared-memory ring of bulk copies with strips of 8, 16 and 32 rows; weights through
+    registers): every M up to 16, N that is no multiple of the strip, K from one block of 32
+    up and K that is no multiple of the ring's chunk, both output types."""
     from mstar_b200 import ops
 
+    monkeypatch.setenv("MSTAR_SMALLM", variant)
+    assert ops.smallm_kernel(m, False) == variant
     x = rnd(m, k, dtype=torch.bfloat16, seed=m)
     w = rnd(n, k, dtype=torch.bfloat16, seed=n, scale=0.1)
     want = x.double() @ w.double().T
@@ -486,22 +493,32 @@ def test_small_m_gemm(m, n, k):
     wide = torch.zeros(m, k + 64, dtype=torch.bfloat16, device=DEV)
     wide[:, :k] = x
     assert torch.equal(ops._gemm_smallm(wide[:, :k], w, torch.bfloat16, False), y)
+    assert tc_clean() == 0                                  # no bounded wait ran out
 
 
 def test_small_m_gemm_refuses_more_rows():
     from mstar_b200 import ops
 
     x, w = rnd(17, 64, dtype=torch.bfloat16), rnd(32, 64, dtype=torch.bfloat16)
-    with pytest.raises(ops.KernelError, match="refuses"):
-        ops._gemm_smallm(x, w, torch.bfloat16, gated=False)
+    for variant in ("bulk", "registers"):
+        os.environ["MSTAR_SMALLM"] = variant
+        try:
+            with pytest.raises(ops.KernelError, match="refuses"):
+                ops._gemm_smallm(x, w, torch.bfloat16, gated=False)
+        finally:
+            del os.environ["MSTAR_SMALLM"]
+    assert ops.smallm_kernel(8, True) == "registers" and ops.smallm_kernel(8, False) == "bulk"
+    assert ops.smallm_kernel(9, True) == "bulk"
     assert ops.linear(x, w).shape == (17, 32)             # the library product takes over
 
 
+@pytest.mark.parametrize("variant", ["bulk", "registers"])
+@pytest.mark.parametrize("inter,k", [(200, 96), (1500, 1120)])
 @pytest.mark.parametrize("m", [1, 8, 13, 16, 100])
-def test_gated_up_fused_and_unfused(m):
+def test_gated_up_fused_and_unfused(m, inter, k, variant, monkeypatch):
     from mstar_b200 import ops
 
-    inter, k = 200, 96
+    monkeypatch.setenv("MSTAR_SMALLM", variant)
     x = rnd(m, k, dtype=torch.bfloat16, seed=1)
     w = rnd(2 * inter, k, dtype=torch.bfloat16, seed=2, scale=0.2)
     got = ops.gated_up(x, w) if m > 16 else ops._gemm_smallm(x, w, torch.bfloat16, gated=True)
