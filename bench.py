@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import argparse
 import json
+import os
 import statistics
 import subprocess
 import sys
@@ -300,7 +301,7 @@ def kernel_bench(name: str, batch: int, ctx: int, small: bool) -> int:
             ms = _time_graph(fn)
             nbytes = reqs * ctx * 2 * nkv * hd * 2
             out.update(ms=ms, gbs=nbytes / ms / 1e6, frac_hbm=nbytes / ms / 1e6 / pk["hbm_gbs"],
-                       split=ops.decode_split(reqs, nkv, ctx))
+                       split=ops.decode_split(reqs, nkv, ctx, ring=os.environ.get("MSTAR_DECODE_ATTENTION") != "per_item"))
         else:
             q = rnd(reqs * ctx, (nq + 2 * nkv) * hd)
             o = torch.empty(reqs * ctx, nq * hd, dtype=torch.bfloat16, device=dev)

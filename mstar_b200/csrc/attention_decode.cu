@@ -16,6 +16,7 @@
 #include "common.cuh"
 #include "mma_util.cuh"
 #include "tma_util.cuh"
+#include <stdlib.h>
 #include <string.h>
 
 #define DEC_THREADS 128
@@ -32,7 +33,26 @@ struct DecodeArgs {
     bf16* out;       // [tokens, nq * HD]
     int q_stride, bt_stride, nq, nkv, page_size, window, chunk, splits;
     float scale_log2e;
+    // > 0: the chunk is made on the device from the longest of these tokens' key ranges (see
+    // live_chunk), `chunk` being its upper bound; 0: `chunk` as given
+    int live_tokens;
 };
+
+// The chunk that cuts the longest key range among the launch's tokens into `splits` equal
+// parts, in whole tiles, at least 128 keys, at most the chunk the launch was sized for.  A
+// launch replayed from a CUDA graph is sized for the longest range its block tables could
+// hold; the ranges that are there may be half as long, and chunks cut for the bound would
+// leave half of the splits empty.  Every warp of every CTA (and the merge kernel) computes
+// the same value from the same array.
+__device__ __forceinline__ int live_chunk(const DecodeArgs& a) {
+    if (a.live_tokens <= 0) return a.chunk;
+    int longest = 1;
+    for (int i = threadIdx.x & 31; i < a.live_tokens; i += 32) longest = max(longest, a.cache_pos[i] + 1);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) longest = max(longest, __shfl_xor_sync(0xffffffffu, longest, o));
+    const int c = max(128, ((longest + a.splits - 1) / a.splits + DEC_TILE - 1) / DEC_TILE * DEC_TILE);
+    return min(c, a.chunk);
+}
 
 template <int HD>
 __global__ void __launch_bounds__(DEC_THREADS) decode_attention_kernel(DecodeArgs a) {
@@ -230,7 +250,8 @@ __global__ void decode_merge_kernel(DecodeArgs a) {
     const int head = blockIdx.x, t = blockIdx.y;
     const int hi = a.cache_pos[t] + 1;
     const int lo = (a.window > 0 && hi > a.window) ? hi - a.window : 0;
-    const int n = min(a.splits, (hi - lo + a.chunk - 1) / a.chunk);
+    const int chunk = live_chunk(a);               // every warp computes it (uniform)
+    const int n = min(a.splits, (hi - lo + chunk - 1) / chunk);
     const size_t base = ((size_t)t * a.nq + head) * a.splits;
     if (threadIdx.x < 32) {
         const int lane = threadIdx.x;
@@ -512,6 +533,336 @@ static int launch_decode_tma(const CUtensorMap& map, const DecodeArgs& a, int to
     return launch_status();
 }
 
+// ------------------------------------------------------------- persistent ring variant
+// The same tiles and arithmetic once more, with the launch turned inside out: the grid is
+// what fits on the GPU at once, every CTA walks over work items (token, kv head, split),
+// and a producer warp keeps a ring of key/value tiles filled across item boundaries, so
+// that the copies of the next item are in flight while this one is computed.  With one
+// CTA per item a CTA lives for a launch plus two or three DRAM latencies, and at small
+// batches most of a decode step's attention time was that; here the latencies overlap.
+// The producer's lanes fetch 32 block-table entries at a time and issue the copies of a
+// tile side by side; the four consumer warps take 16 keys of a tile each, as above, and
+// are merged in shared memory at the end of an item.
+#define RING_THREADS (DEC_THREADS + 32)
+
+struct RingLayout {   // byte offsets into dynamic shared memory, made on the host
+    int stages, q_off, om_off, ml_off, bar_off, total;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(RING_THREADS)
+decode_attention_ring_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs a, int tokens,
+                             RingLayout lay, int* __restrict__ error_word) {
+    constexpr int CPR = HD / 8;
+    constexpr int HALVES = HD / 64;
+    constexpr uint32_t TILE_BYTES = DEC_TILE * HD * 2;  // keys (or values) of one tile
+    extern __shared__ __align__(1024) unsigned char ring_smem[];
+    unsigned char* ring = ring_smem;                                  // [stages]{K, V}
+    bf16* Qs = reinterpret_cast<bf16*>(ring_smem + lay.q_off);        // [16][HD]
+    float* Om = reinterpret_cast<float*>(ring_smem + lay.om_off);     // [4 warps][G][HD]
+    float* MLm = reinterpret_cast<float*>(ring_smem + lay.ml_off);    // [4 warps][G][2]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring_smem + lay.bar_off);
+    const int S = lay.stages;
+    const uint32_t full = tc_smem(bars), empty = tc_smem(bars + S);
+    volatile int* failed = reinterpret_cast<volatile int*>(bars + 2 * S);
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int G = a.nq / a.nkv;
+    const int ps = a.page_size;
+    const int items = tokens * a.nkv * a.splits;
+    const int chunk = live_chunk(a);
+
+    if ((tc_smem(ring_smem) & 1023u) != 0) {          // the swizzled tiles need this alignment
+        if (tid == 0) atomicExch(error_word, 5);
+        return;
+    }
+    if (tid == 0) {
+        *failed = 0;
+        for (int s = 0; s < S; ++s) {
+            mbar_init(full + 8 * s, 1);
+            mbar_init(empty + 8 * s, DEC_THREADS / 32);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == DEC_THREADS / 32) {
+        // ------------------------------------------------------------------ producer
+        int c = 0;
+        bool ok = true;
+        for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+            const int split = item % a.splits, kvh = (item / a.splits) % a.nkv, t = item / (a.splits * a.nkv);
+            const int hi = a.cache_pos[t] + 1;
+            const int ks = split * chunk;
+            const int ke = min(hi, ks + chunk);
+            if (ks >= ke) continue;
+            const int* bt = a.block_table + (size_t)a.token_req[t] * a.bt_stride;
+            // pages beyond the request's last one are replaced by it: masked keys stay finite
+            const int last_page = (hi - 1) / ps;
+            const int per_tile = DEC_TILE / ps;
+            const int ntiles = (ke - ks + DEC_TILE - 1) / DEC_TILE;
+            int mine = 0, have_from = -1;              // lanes hold pages have_from .. +31
+            for (int it = 0; it < ntiles; ++it, ++c) {
+                const int st = c % S;
+                const int base_page = (ks + it * DEC_TILE) / ps;
+                if (have_from < 0 || base_page + per_tile > have_from + 32) {
+                    have_from = base_page;
+                    mine = bt[min(base_page + lane, last_page)];
+                }
+                if (lane == 0) {
+                    if (c >= S && !mbar_wait(empty + 8 * st, ((uint32_t)(c / S) - 1u) & 1u)) {
+                        atomicExch(error_word, 4);
+                        ok = false;
+                    } else {
+                        mbar_expect_tx(full + 8 * st, 2 * TILE_BYTES);
+                    }
+                }
+                ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+                if (!ok) break;
+                // lane HALVES p + h copies 64-feature block h of page p, keys and values
+                const int p = lane / HALVES, h = lane % HALVES;
+                const int page = __shfl_sync(0xffffffffu, mine, (base_page + p - have_from) & 31);
+                if (p < per_tile) {
+                    unsigned char* kdst = ring + (size_t)st * 2 * TILE_BYTES + h * (64 * 128) + p * ps * 128;
+                    tma_load_2d(tc_smem(kdst), &kv_map, full + 8 * st, h * 64, ((page * 2) * a.nkv + kvh) * ps);
+                    tma_load_2d(tc_smem(kdst + TILE_BYTES), &kv_map, full + 8 * st, h * 64,
+                                ((page * 2 + 1) * a.nkv + kvh) * ps);
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------------- consumers
+    int c = 0;
+    for (int item = blockIdx.x; item < items; item += gridDim.x) {
+        const int split = item % a.splits, kvh = (item / a.splits) % a.nkv, t = item / (a.splits * a.nkv);
+        const int hi = a.cache_pos[t] + 1;
+        const int ks = split * chunk;
+        const int ke = min(hi, ks + chunk);
+        if (ks >= ke) continue;   // this token has fewer chunks than the launch has splits
+        // the last item's Q and merge buffers are free: every warp is past its last barrier
+        const bf16* qrow = a.q + (size_t)t * a.q_stride + (size_t)kvh * G * HD;
+        for (int i = tid; i < 16 * CPR; i += DEC_THREADS) {
+            const int r = i / CPR, cc = i - r * CPR;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (r < G) v = *reinterpret_cast<const uint4*>(qrow + (size_t)r * HD + cc * 8);
+            *reinterpret_cast<uint4*>(Qs + tile_off<CPR>(r, cc)) = v;
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(DEC_THREADS) : "memory");
+
+        float o[HD / 8][4];
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+        float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+        const int ntiles = (ke - ks + DEC_TILE - 1) / DEC_TILE;
+        for (int it = 0; it < ntiles; ++it, ++c) {
+            const int st = c % S;
+            if (!mbar_wait(full + 8 * st, (uint32_t)(c / S) & 1u)) {
+                // give up, but together with the other warps (they wait at the barrier below)
+                if (lane == 0) atomicExch(error_word, 4);
+                *failed = 1;
+                break;
+            }
+            const bf16* Ks = reinterpret_cast<const bf16*>(ring + (size_t)st * 2 * TILE_BYTES);
+            const bf16* Vs = Ks + DEC_TILE * HD;
+            const int key0 = ks + it * DEC_TILE + warp * 16;
+            if (key0 < ke) {
+                float s[2][4];
+#pragma unroll
+                for (int j = 0; j < 2; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
+#pragma unroll
+                for (int kk = 0; kk < HD / 16; ++kk) {
+                    uint32_t qa[4], kb[4];
+                    const int arow = (lane & 7) + ((lane >> 3) & 1) * 8;
+                    ldmatrix_x4(qa, smem_u32(Qs + tile_off<CPR>(arow, 2 * kk + (lane >> 4))));
+                    const int brow = warp * 16 + (lane & 7) + (lane >> 4) * 8;
+                    ldmatrix_x4(kb, smem_u32(Ks + tma_off<HD>(brow, 2 * kk + ((lane >> 3) & 1))));
+                    mma_bf16_16816(s[0], qa, kb[0], kb[1]);
+                    mma_bf16_16816(s[1], qa, kb[2], kb[3]);
+                }
+                float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+                for (int j = 0; j < 2; ++j)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
+                        const float v = key < ke ? s[j][e] * a.scale_log2e : -INFINITY;
+                        s[j][e] = v;
+                        if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
+                    }
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+                mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+                mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+                const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);  // finite: key0 is valid
+                const float al0 = exp2f(m0 - mn0), al1 = exp2f(m1 - mn1);
+                m0 = mn0;
+                m1 = mn1;
+                float ps0 = 0.f, ps1 = 0.f;
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    s[j][0] = exp2f(s[j][0] - mn0);
+                    s[j][1] = exp2f(s[j][1] - mn0);
+                    s[j][2] = exp2f(s[j][2] - mn1);
+                    s[j][3] = exp2f(s[j][3] - mn1);
+                    ps0 += s[j][0] + s[j][1];
+                    ps1 += s[j][2] + s[j][3];
+                }
+                l0 = l0 * al0 + ps0;
+                l1 = l1 * al1 + ps1;
+#pragma unroll
+                for (int n = 0; n < HD / 8; ++n) {
+                    o[n][0] *= al0; o[n][1] *= al0; o[n][2] *= al1; o[n][3] *= al1;
+                }
+                uint32_t pa[4];
+                pa[0] = pack_bf16(s[0][0], s[0][1]);
+                pa[1] = pack_bf16(s[0][2], s[0][3]);
+                pa[2] = pack_bf16(s[1][0], s[1][1]);
+                pa[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+                for (int n2 = 0; n2 < HD / 16; ++n2) {
+                    uint32_t vb[4];
+                    const int vrow = warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                    ldmatrix_x4_trans(vb, smem_u32(Vs + tma_off<HD>(vrow, 2 * n2 + (lane >> 4))));
+                    mma_bf16_16816(o[2 * n2], pa, vb[0], vb[1]);
+                    mma_bf16_16816(o[2 * n2 + 1], pa, vb[2], vb[3]);
+                }
+            }
+            __syncwarp();
+            if (lane == 0) {
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty + 8 * st) : "memory");
+            }
+        }
+
+        // ---- the warps' parts of the keys -> shared (rows of the group only), then merged
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+        l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+        l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+        const int r0 = lane >> 2;
+#pragma unroll
+        for (int n = 0; n < HD / 8; ++n) {
+            const int col = n * 8 + (lane & 3) * 2;
+            if (r0 < G) {
+                float* p0 = Om + ((size_t)warp * G + r0) * HD + col;
+                p0[0] = o[n][0];
+                p0[1] = o[n][1];
+            }
+            if (r0 + 8 < G) {
+                float* p1 = Om + ((size_t)warp * G + r0 + 8) * HD + col;
+                p1[0] = o[n][2];
+                p1[1] = o[n][3];
+            }
+        }
+        if ((lane & 3) == 0) {
+            if (r0 < G) {
+                MLm[(warp * G + r0) * 2 + 0] = m0;
+                MLm[(warp * G + r0) * 2 + 1] = l0;
+            }
+            if (r0 + 8 < G) {
+                MLm[(warp * G + r0 + 8) * 2 + 0] = m1;
+                MLm[(warp * G + r0 + 8) * 2 + 1] = l1;
+            }
+        }
+        asm volatile("bar.sync 1, %0;" ::"n"(DEC_THREADS) : "memory");
+        if (*failed) return;
+        for (int idx = tid; idx < G * HD; idx += DEC_THREADS) {
+            const int g = idx / HD, d = idx - g * HD;
+            float m = -INFINITY;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) m = fmaxf(m, MLm[(w * G + g) * 2]);
+            float acc = 0.f, L = 0.f;
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float mw = MLm[(w * G + g) * 2];
+                const float wgt = mw == -INFINITY ? 0.f : exp2f(mw - m);
+                acc += wgt * Om[((size_t)w * G + g) * HD + d];
+                L += wgt * MLm[(w * G + g) * 2 + 1];
+            }
+            const int head = kvh * G + g;
+            if (a.splits == 1) {
+                a.out[(size_t)t * a.nq * HD + (size_t)head * HD + d] = __float2bfloat16_rn(acc / L);
+            } else {
+                const size_t slot = ((size_t)t * a.nq + head) * a.splits + split;
+                a.part_o[slot * HD + d] = acc;
+                if (d == 0) {
+                    a.part_ml[slot * 2] = m;
+                    a.part_ml[slot * 2 + 1] = L;
+                }
+            }
+        }
+        // Q and the merge buffers are written again only after every warp has passed this
+        asm volatile("bar.sync 1, %0;" ::"n"(DEC_THREADS) : "memory");
+    }
+}
+
+// Shared memory of the ring kernel for a group of G query heads: as many stages (3 or 2) as
+// leave room for two CTAs per SM.
+template <int HD> static RingLayout ring_layout(int G, int stages) {
+    RingLayout l;
+    l.stages = stages;
+    l.q_off = stages * 2 * DEC_TILE * HD * 2;
+    l.om_off = l.q_off + 16 * HD * 2;
+    l.ml_off = l.om_off + 4 * G * HD * 4;
+    l.bar_off = (l.ml_off + 4 * G * 2 * 4 + 7) & ~7;
+    l.total = l.bar_off + (2 * stages + 1) * 8;
+    return l;
+}
+
+template <int HD>
+static int launch_decode_ring(const CUtensorMap& map, const DecodeArgs& a, int tokens, int* error_word,
+                              cudaStream_t s) {
+    const int G = a.nq / a.nkv;
+    static int sms = 0, max_smem = 0, configured_for = 0;
+    auto kernel = decode_attention_ring_kernel<HD>;
+    if (sms == 0) {
+        int dev = 0;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return (int)e;
+        if ((e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev)) != cudaSuccess) return (int)e;
+        if ((e = cudaDeviceGetAttribute(&max_smem, cudaDevAttrMaxSharedMemoryPerMultiprocessor, dev)) != cudaSuccess)
+            return (int)e;
+    }
+    // 3 stages if two such CTAs fit on an SM (1 KB per CTA is the system's), else 2; one CTA
+    // per SM if even that is too much (head_dim 256)
+    RingLayout lay = ring_layout<HD>(G, 3);
+    int per_sm = 2;
+    if (2 * (lay.total + 1024) > max_smem) {
+        lay = ring_layout<HD>(G, 2);
+        if (2 * (lay.total + 1024) > max_smem) per_sm = 1;
+    }
+    if (lay.total + 1024 > max_smem) return -1;
+    if (lay.total > configured_for) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, lay.total);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                 (int)cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return (int)e;
+        configured_for = lay.total;
+    }
+    const long long items = (long long)tokens * a.nkv * a.splits;
+    if (items > 2147483647LL) return -1;
+    DecodeArgs live = a;
+    live.live_tokens = tokens;
+    static int occ_for = -1, occ = 0;   // registers may allow fewer CTAs than shared memory does
+    if (occ_for != lay.total) {
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kernel, RING_THREADS, lay.total);
+        if (e != cudaSuccess) return (int)e;
+        if (occ < 1) return -1;
+        occ_for = lay.total;
+    }
+    if (occ < per_sm) per_sm = occ;
+    const int resident = per_sm * sms;
+    const int grid = items < resident ? (int)items : resident;
+    kernel<<<grid, RING_THREADS, lay.total, s>>>(map, live, tokens, lay, error_word);
+    if (a.splits > 1) {
+        dim3 mgrid(a.nq, tokens);
+        decode_merge_kernel<HD><<<mgrid, HD < 128 ? HD : 128, 0, s>>>(live);
+    }
+    return launch_status();
+}
+
 // Tensor map of a cache [pages, 2, nkv, page_size, hd] (bfloat16) seen as the matrix
 // [pages * 2 * nkv * page_size, hd] with boxes of page_size rows x 64 features, 128-byte
 // swizzle.  `out_map` receives the 128-byte map.  Returns 0, -1 (shape not taken), -3 / -4.
@@ -563,13 +914,27 @@ MSTAR_API int mstar_paged_decode_attention_bf16_tma(
     a.chunk = chunk;
     a.splits = splits;
     a.scale_log2e = scale * 1.4426950408889634f;
+    a.live_tokens = 0;
     CUtensorMap map;
     memcpy(&map, kv_map, sizeof(map));
     cudaStream_t s = (cudaStream_t)stream;
+    static int per_item = -1;   // MSTAR_DECODE_ATTENTION=per_item: one CTA per work item
+    if (per_item < 0) {
+        const char* e = getenv("MSTAR_DECODE_ATTENTION");
+        per_item = (e != nullptr && strcmp(e, "per_item") == 0) ? 1 : 0;
+    }
+    if (per_item) {
+        switch (hd) {
+            case 64: return launch_decode_tma<64>(map, a, tokens, error_word, s);
+            case 128: return launch_decode_tma<128>(map, a, tokens, error_word, s);
+            case 256: return launch_decode_tma<256>(map, a, tokens, error_word, s);
+            default: return -1;
+        }
+    }
     switch (hd) {
-        case 64: return launch_decode_tma<64>(map, a, tokens, error_word, s);
-        case 128: return launch_decode_tma<128>(map, a, tokens, error_word, s);
-        case 256: return launch_decode_tma<256>(map, a, tokens, error_word, s);
+        case 64: return launch_decode_ring<64>(map, a, tokens, error_word, s);
+        case 128: return launch_decode_ring<128>(map, a, tokens, error_word, s);
+        case 256: return launch_decode_ring<256>(map, a, tokens, error_word, s);
         default: return -1;
     }
 }
@@ -608,6 +973,7 @@ MSTAR_API int mstar_paged_decode_attention_bf16(
     a.chunk = chunk;
     a.splits = splits;
     a.scale_log2e = scale * 1.4426950408889634f;
+    a.live_tokens = 0;
     cudaStream_t s = (cudaStream_t)stream;
     switch (hd) {
         case 16: return launch_decode<16>(a, tokens, s);

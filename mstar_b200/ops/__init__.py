@@ -9,6 +9,8 @@ is this package's own true-32-bit kernel.
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import lib
@@ -164,21 +166,32 @@ def fast_attention_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: i
             and num_heads % num_kv_heads == 0 and num_heads // num_kv_heads <= 16)
 
 
-# CTAs of the decode attention grid per SM that the split of the keys aims for
+# CTAs of the decode attention grid per SM that the split of the keys aims for (the kernel
+# with one CTA per work item), and CTAs per SM of the persistent ring kernel
 DECODE_FILL = 6
+RING_CTAS_PER_SM = 2
 
 
-def decode_split(tokens: int, num_kv_heads: int, max_len: int) -> tuple:
-    """(chunk, splits) of the keys for split-K decode attention: enough CTAs to fill
-    the GPU a few times over, chunks in whole tiles of 64 keys."""
+def decode_split(tokens: int, num_kv_heads: int, max_len: int, ring: bool = False) -> tuple:
+    """(chunk, splits) of the keys for split-K decode attention, chunks in whole tiles of 64
+    keys.  One CTA per work item (token, kv head, split): enough items to fill the GPU a
+    few times over.  Persistent ring kernel: as many items as CTAs are resident or fewer
+    (each CTA then streams one item of equal size), of at least 128 keys."""
     import os
 
     pairs = max(tokens * num_kv_heads, 1)
-    fill = int(os.environ.get("MSTAR_DECODE_FILL", DECODE_FILL))
-    want = max(1, -(-NUM_SMS * fill // pairs))
-    want = min(want, 256)                       # the merge kernel takes up to 256 splits
-    chunk = max(64, -(-(-(-max_len // want)) // 64) * 64)
+    if ring:
+        want = max(1, (NUM_SMS * RING_CTAS_PER_SM) // pairs)
+        chunk = max(128, -(-(-(-max_len // want)) // 64) * 64)
+    else:
+        fill = int(os.environ.get("MSTAR_DECODE_FILL", DECODE_FILL))
+        want = max(1, -(-NUM_SMS * fill // pairs))
+        want = min(want, 256)                   # the merge kernel takes up to 256 splits
+        chunk = max(64, -(-(-(-max_len // want)) // 64) * 64)
     splits = max(1, -(-max_len // chunk))
+    while splits > 256:                         # the merge kernel takes up to 256 splits
+        chunk *= 2
+        splits = max(1, -(-max_len // chunk))
     return chunk, splits
 
 
@@ -218,12 +231,13 @@ def paged_decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
     assert (q_stride * 2) % 16 == 0 and q.data_ptr() % 16 == 0 and out.is_contiguous()
     if window:
         max_len = min(max_len, window)
-    chunk, splits = decode_split(tokens, num_kv_heads, max(max_len, 1))
+    kv_map = kv_tensor_map(kv_cache) if not window else None
+    ring = kv_map is not None and os.environ.get("MSTAR_DECODE_ATTENTION") != "per_item"
+    chunk, splits = decode_split(tokens, num_kv_heads, max(max_len, 1), ring=ring)
     scratch = None
     if splits > 1:
         scratch = torch.empty(tokens * num_heads * splits * (head_dim + 2), dtype=torch.float32,
                               device=q.device)
-    kv_map = kv_tensor_map(kv_cache) if not window else None
     if kv_map is not None:
         code = lib.get("attention_decode").mstar_paged_decode_attention_bf16_tma(
             kv_map, q.data_ptr(), q_stride, out.data_ptr(), kv_cache.data_ptr(),
