@@ -246,6 +246,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_attention_kernel(DecodeArg
 #define MERGE_MAX_SPLITS 256
 template <int HD>
 __global__ void decode_merge_kernel(DecodeArgs a) {
+    pdl_wait();
     __shared__ float wgt[MERGE_MAX_SPLITS];
     const int head = blockIdx.x, t = blockIdx.y;
     const int hi = a.cache_pos[t] + 1;
@@ -293,7 +294,7 @@ template <int HD> static int launch_decode(const DecodeArgs& a, int tokens, cuda
     decode_attention_kernel<HD><<<grid, DEC_THREADS, smem, s>>>(a);
     if (a.splits > 1) {
         dim3 mgrid(a.nq, tokens);
-        decode_merge_kernel<HD><<<mgrid, HD < 32 ? 32 : (HD < 128 ? HD : 128), 0, s>>>(a);
+        mstar_launch((decode_merge_kernel<HD>), mgrid, dim3(HD < 32 ? 32 : (HD < 128 ? HD : 128)), 0, s, a);
     }
     return launch_status();
 }
@@ -528,7 +529,7 @@ static int launch_decode_tma(const CUtensorMap& map, const DecodeArgs& a, int to
     decode_attention_tma_kernel<HD><<<grid, DEC_THREADS, smem, s>>>(map, a, error_word);
     if (a.splits > 1) {
         dim3 mgrid(a.nq, tokens);
-        decode_merge_kernel<HD><<<mgrid, HD < 128 ? HD : 128, 0, s>>>(a);
+        mstar_launch((decode_merge_kernel<HD>), mgrid, dim3(HD < 128 ? HD : 128), 0, s, a);
     }
     return launch_status();
 }
@@ -553,6 +554,7 @@ template <int HD>
 __global__ void __launch_bounds__(RING_THREADS)
 decode_attention_ring_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs a, int tokens,
                              RingLayout lay, int* __restrict__ error_word) {
+    pdl_wait();
     constexpr int CPR = HD / 8;
     constexpr int HALVES = HD / 64;
     constexpr uint32_t TILE_BYTES = DEC_TILE * HD * 2;  // keys (or values) of one tile
@@ -735,6 +737,7 @@ decode_attention_ring_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeA
             }
         }
 
+        if (item + (int)gridDim.x >= items) pdl_launch_dependents();   // the last keys are here
         // ---- the warps' parts of the keys -> shared (rows of the group only), then merged
         l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
         l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
@@ -855,10 +858,10 @@ static int launch_decode_ring(const CUtensorMap& map, const DecodeArgs& a, int t
     if (occ < per_sm) per_sm = occ;
     const int resident = per_sm * sms;
     const int grid = items < resident ? (int)items : resident;
-    kernel<<<grid, RING_THREADS, lay.total, s>>>(map, live, tokens, lay, error_word);
+    mstar_launch(kernel, dim3(grid), dim3(RING_THREADS), lay.total, s, map, live, tokens, lay, error_word);
     if (a.splits > 1) {
         dim3 mgrid(a.nq, tokens);
-        decode_merge_kernel<HD><<<mgrid, HD < 128 ? HD : 128, 0, s>>>(live);
+        mstar_launch((decode_merge_kernel<HD>), mgrid, dim3(HD < 128 ? HD : 128), 0, s, live);
     }
     return launch_status();
 }

@@ -9,6 +9,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define MSTAR_API extern "C" __attribute__((visibility("default")))
 
@@ -91,3 +92,45 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 }
 
 static inline int launch_status() { return (int)cudaGetLastError(); }
+
+// ---- programmatic dependent launch
+// A kernel launched through mstar_launch may be scheduled while the kernel before it on the
+// stream is still draining: its CTAs become resident, run up to pdl_wait() and stay there
+// until that kernel has completed and its memory is visible.  This takes launch latency and
+// the ramp of CTA scheduling out of the gaps between the many short kernels of a decode step
+// (measured: 2.35 -> 2.22 ms per step at batch 8).  A successor is scheduled once every CTA
+// of the running kernel has called pdl_launch_dependents() or has ended.  The long kernels
+// call it where their last weights or keys have arrived, before their reductions; the short
+// ones leave it to their end.  Calling it at the top of every kernel lets waiting successors
+// pile up on the SMs and was slower than no overlap at all (2.93 ms).  Every kernel calls
+// pdl_wait() before it touches global memory.  MSTAR_PDL=0 launches everything with full
+// serialization (the calls in the kernels are then no-ops).
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+static inline int pdl_enabled() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("MSTAR_PDL");
+        v = (e != nullptr && e[0] == '0') ? 0 : 1;
+    }
+    return v;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t mstar_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                       cudaStream_t stream, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = pdl_enabled();
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}

@@ -14,6 +14,7 @@
 template <typename W>
 __global__ void embed_rows_kernel(const W* __restrict__ table, const int* __restrict__ ids,
                                   float* __restrict__ out, int vocab, int hidden) {
+    pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * hidden;
@@ -31,9 +32,9 @@ MSTAR_API int mstar_embed_rows(const void* table, int table_dtype, const int* id
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == MSTAR_F32)
-        embed_rows_kernel<float><<<num_tokens, threads, 0, s>>>((const float*)table, ids, out, vocab, hidden);
+        mstar_launch((embed_rows_kernel<float>), dim3(num_tokens), dim3(threads), 0, s, (const float*)table, ids, out, vocab, hidden);
     else
-        embed_rows_kernel<bf16><<<num_tokens, threads, 0, s>>>((const bf16*)table, ids, out, vocab, hidden);
+        mstar_launch((embed_rows_kernel<bf16>), dim3(num_tokens), dim3(threads), 0, s, (const bf16*)table, ids, out, vocab, hidden);
     return launch_status();
 }
 
@@ -47,6 +48,7 @@ template <typename A, typename W, bool VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const A* __restrict__ delta,
                                    const W* __restrict__ weight, A* __restrict__ out, int hidden,
                                    float eps, float w_offset) {
+    pdl_wait();
     __shared__ float scratch[32];
     const size_t base = (size_t)blockIdx.x * hidden;
     float* r = resid + base;
@@ -113,10 +115,10 @@ MSTAR_API int mstar_add_rmsnorm(float* resid, const void* delta, const void* wei
     if (vec) threads = hidden >= 4096 ? 512 : (hidden >= 2048 ? 256 : 128);
 #define LAUNCH(A, W)                                                                             \
     if (vec)                                                                                     \
-        add_rmsnorm_kernel<A, W, true><<<rows, threads, 0, s>>>(                                 \
+        mstar_launch((add_rmsnorm_kernel<A, W, true>), dim3(rows), dim3(threads), 0, s,                                  \
             resid, (const A*)delta, (const W*)weight, (A*)out, hidden, eps, w_offset);          \
     else                                                                                         \
-        add_rmsnorm_kernel<A, W, false><<<rows, threads, 0, s>>>(                                \
+        mstar_launch((add_rmsnorm_kernel<A, W, false>), dim3(rows), dim3(threads), 0, s,                                 \
             resid, (const A*)delta, (const W*)weight, (A*)out, hidden, eps, w_offset)
     if (act_dtype == MSTAR_F32) {
         if (weight_dtype == MSTAR_F32) { LAUNCH(float, float); } else { LAUNCH(float, bf16); }
@@ -134,6 +136,7 @@ template <typename A>
 __global__ void gather_add_rows_kernel(const float* __restrict__ resid, const A* __restrict__ delta,
                                        const int* __restrict__ rows, float* __restrict__ out,
                                        int hidden) {
+    pdl_wait();
     const size_t src = (size_t)rows[blockIdx.x] * hidden;
     const size_t dst = (size_t)blockIdx.x * hidden;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
@@ -149,9 +152,9 @@ MSTAR_API int mstar_gather_add_rows(const float* resid, const void* delta, int a
     if (num_rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     if (act_dtype == MSTAR_F32)
-        gather_add_rows_kernel<float><<<num_rows, 256, 0, s>>>(resid, (const float*)delta, rows, out, hidden);
+        mstar_launch((gather_add_rows_kernel<float>), dim3(num_rows), dim3(256), 0, s, resid, (const float*)delta, rows, out, hidden);
     else
-        gather_add_rows_kernel<bf16><<<num_rows, 256, 0, s>>>(resid, (const bf16*)delta, rows, out, hidden);
+        mstar_launch((gather_add_rows_kernel<bf16>), dim3(num_rows), dim3(256), 0, s, resid, (const bf16*)delta, rows, out, hidden);
     return launch_status();
 }
 
@@ -161,6 +164,7 @@ MSTAR_API int mstar_gather_add_rows(const float* resid, const void* delta, int a
 template <typename A>
 __global__ void silu_mul_kernel(const A* __restrict__ gate_up, A* __restrict__ out, int inter,
                                 size_t total) {
+    pdl_wait();
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t row = idx / inter;
@@ -182,9 +186,9 @@ MSTAR_API int mstar_silu_mul(const void* gate_up, void* out, int act_dtype, int 
     size_t blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 32) blocks = 148 * 32;
     if (act_dtype == MSTAR_F32)
-        silu_mul_kernel<float><<<(int)blocks, threads, 0, s>>>((const float*)gate_up, (float*)out, inter, total);
+        mstar_launch((silu_mul_kernel<float>), dim3((int)blocks), dim3(threads), 0, s, (const float*)gate_up, (float*)out, inter, total);
     else
-        silu_mul_kernel<bf16><<<(int)blocks, threads, 0, s>>>((const bf16*)gate_up, (bf16*)out, inter, total);
+        mstar_launch((silu_mul_kernel<bf16>), dim3((int)blocks), dim3(threads), 0, s, (const bf16*)gate_up, (bf16*)out, inter, total);
     return launch_status();
 }
 
@@ -232,6 +236,7 @@ __global__ void rope_kv_write_kernel(A* __restrict__ qkv, const int* __restrict_
                                      const int* __restrict__ block_table,
                                      const float* __restrict__ inv_freq, A* __restrict__ kv_cache,
                                      RopeArgs a) {
+    pdl_wait();
     // grid (token, slice): the items of a token (rotated pairs of q and k, unrotated tail
     // of k, values) are spread over all threads of its slices, one or a few each, so that
     // the dependent loads of different items overlap instead of queueing in one thread
@@ -297,6 +302,7 @@ __global__ void rope_kv_write_vec_kernel(A* __restrict__ qkv, const int* __restr
                                          const int* __restrict__ block_table,
                                          const float* __restrict__ inv_freq,
                                          A* __restrict__ kv_cache, RopeArgs a) {
+    pdl_wait();
     const int t = blockIdx.x;
     const int hd = a.hd, half = a.rotary_dim / 2;
     const int row_elems = (a.nq + 2 * a.nkv) * hd;
@@ -379,7 +385,7 @@ MSTAR_API int mstar_rope_kv_write(void* qkv, int act_dtype, const int* positions
         if (num_tokens >= 256 && slices > 1) slices = 1;
         if (slices < 1) slices = 1;
         dim3 grid(num_tokens, slices);
-        rope_kv_write_vec_kernel<bf16><<<grid, threads, 0, s>>>(
+        mstar_launch((rope_kv_write_vec_kernel<bf16>), dim3(grid), dim3(threads), 0, s, 
             (bf16*)qkv, positions, cache_pos, token_req, block_table, inv_freq, (bf16*)kv_cache, a);
         return launch_status();
     }
@@ -390,10 +396,10 @@ MSTAR_API int mstar_rope_kv_write(void* qkv, int act_dtype, const int* positions
     if (slices < 1) slices = 1;
     dim3 grid(num_tokens, slices);
     if (act_dtype == MSTAR_F32)
-        rope_kv_write_kernel<float><<<grid, threads, 0, s>>>(
+        mstar_launch((rope_kv_write_kernel<float>), dim3(grid), dim3(threads), 0, s, 
             (float*)qkv, positions, cache_pos, token_req, block_table, inv_freq, (float*)kv_cache, a);
     else
-        rope_kv_write_kernel<bf16><<<grid, threads, 0, s>>>(
+        mstar_launch((rope_kv_write_kernel<bf16>), dim3(grid), dim3(threads), 0, s, 
             (bf16*)qkv, positions, cache_pos, token_req, block_table, inv_freq, (bf16*)kv_cache, a);
     return launch_status();
 }

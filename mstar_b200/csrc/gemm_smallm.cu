@@ -40,6 +40,7 @@ template <bool GATED, bool M16, typename OutT>
 __global__ void __launch_bounds__(SM_THREADS)
 smallm_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* __restrict__ out,
                    int M, int n_out, int K, int ldx, int ldw, int ldo, int inter) {
+    pdl_wait();
     constexpr int STRIPS = GATED ? 2 : 1;
     __shared__ float red[STRIPS][SM_WARPS][16][8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -87,6 +88,7 @@ smallm_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
         }
     }
 
+    pdl_launch_dependents();   // the weights are here: the next kernel may be scheduled
     // ---- sum the warps' parts of K in shared memory: red[..][token][W row]
 #pragma unroll
     for (int s = 0; s < STRIPS; ++s) {
@@ -126,6 +128,7 @@ template <int NT, bool GATED, typename OutT>
 __global__ void __launch_bounds__(SM_THREADS)
 smallm_wide_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* __restrict__ out,
                    int M, int n_out, int K, int ldx, int ldw, int ldo, int inter) {
+    pdl_wait();
     extern __shared__ float red[];  // [strips][SM_WARPS][16][8*NT]
     constexpr int COLS = 8 * NT;
     constexpr int STRIPS = GATED ? 2 : 1;
@@ -187,6 +190,7 @@ smallm_wide_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, 
         }
     }
 
+    pdl_launch_dependents();   // the weights are here: the next kernel may be scheduled
     // ---- sum the warps' parts of K in shared memory
 #pragma unroll
     for (int s = 0; s < STRIPS; ++s) {
@@ -229,16 +233,16 @@ static int launch_smallm(const bf16* x, const bf16* W, OutT* out, int M, int n_o
                          int ldw, int ldo, int inter, cudaStream_t s) {
     if (M <= 8 && n_out >= 8192 && n_out < 65536) {
         const size_t smem = (size_t)(GATED ? 2 : 1) * SM_WARPS * 16 * 8 * sizeof(float);
-        smallm_wide_gemm_kernel<1, GATED, OutT><<<(n_out + 15) / 16, SM_THREADS, smem, s>>>(
+        mstar_launch((smallm_wide_gemm_kernel<1, GATED, OutT>), dim3((n_out + 15) / 16), dim3(SM_THREADS), smem, s, 
             x, W, out, M, n_out, K, ldx, ldw, ldo, inter);
         return launch_status();
     }
     const int grid = (n_out + 7) / 8;
     if (M <= 8)
-        smallm_gemm_kernel<GATED, false, OutT><<<grid, SM_THREADS, 0, s>>>(x, W, out, M, n_out, K,
+        mstar_launch((smallm_gemm_kernel<GATED, false, OutT>), dim3(grid), dim3(SM_THREADS), 0, s, x, W, out, M, n_out, K,
                                                                            ldx, ldw, ldo, inter);
     else
-        smallm_gemm_kernel<GATED, true, OutT><<<grid, SM_THREADS, 0, s>>>(x, W, out, M, n_out, K,
+        mstar_launch((smallm_gemm_kernel<GATED, true, OutT>), dim3(grid), dim3(SM_THREADS), 0, s, x, W, out, M, n_out, K,
                                                                           ldx, ldw, ldo, inter);
     return launch_status();
 }

@@ -66,6 +66,7 @@ template <bool GATED, bool M16, int NT, typename OutT>
 __global__ void __launch_bounds__(SB_THREADS, (GATED ? 2 : 4) / NT >= 1 ? (GATED ? 2 : 4) / NT : 1)
 smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* __restrict__ out, int M,
                    int n_out, int K, int ldx, int ldw, int ldo, int inter, int* __restrict__ error_word) {
+    pdl_wait();
     constexpr int STRIPS = GATED ? 2 : 1;
     constexpr int GROUPS = STRIPS * NT;               // 8-row groups of a stage
     constexpr int ROWS = 8 * GROUPS;
@@ -173,6 +174,9 @@ smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
             __syncwarp();
             if (lane == 0) sb_arrive(empty + 8 * st);
         }
+        // the last strip's weights are here: the next kernel may be scheduled while the sums
+        // are made
+        if (strip + (int)gridDim.x >= nstrips) pdl_launch_dependents();
         // ---- sum the warps' parts in shared memory: red[group][warp][token][W row]
 #pragma unroll
         for (int s = 0; s < GROUPS; ++s) {
@@ -235,7 +239,7 @@ static int launch_bulk_nt(const bf16* x, const bf16* W, OutT* out, int M, int n_
     }
     const int nstrips = (n_out + 8 * NT - 1) / (8 * NT);
     const int grid = nstrips < resident ? nstrips : resident;
-    kernel<<<grid, SB_THREADS, SMEM, s>>>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, error_word);
+    mstar_launch(kernel, dim3(grid), dim3(SB_THREADS), SMEM, s, x, W, out, M, n_out, K, ldx, ldw, ldo, inter, error_word);
     return launch_status();
 }
 

@@ -72,6 +72,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab,
               unsigned char* __restrict__ seen_mask, const int* __restrict__ seen_rows,
               const long long* __restrict__ seed, const long long* __restrict__ offset,
               int* __restrict__ out) {
+    pdl_wait();
     __shared__ float fs[32];
     __shared__ int is[32];
     __shared__ float best_v[32];
@@ -233,7 +234,7 @@ MSTAR_API int mstar_sample(const float* logits, int ld, int rows, int vocab,
                            const long long* seed, const long long* offset, int* out,
                            void* stream) {
     if (rows <= 0) return 0;
-    sample_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(
+    mstar_launch((sample_kernel), dim3(rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, 
         logits, ld, vocab, temperature, top_k, top_p, penalty, seen_mask, seen_rows, seed, offset,
         out);
     return launch_status();
@@ -242,6 +243,7 @@ MSTAR_API int mstar_sample(const float* logits, int ld, int rows, int vocab,
 // Greedy only: argmax of each row (smallest index among equal maxima).
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out) {
+    pdl_wait();
     __shared__ float best_v[32];
     __shared__ int best_i[32];
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -275,6 +277,6 @@ argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restri
 MSTAR_API int mstar_argmax(const float* logits, int ld, int rows, int vocab, int* out,
                            void* stream) {
     if (rows <= 0) return 0;
-    argmax_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, ld, vocab, out);
+    mstar_launch((argmax_kernel), dim3(rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, logits, ld, vocab, out);
     return launch_status();
 }
