@@ -65,8 +65,8 @@ __host__ __device__ constexpr int sb_smem(bool gated, int nt) {
 template <bool GATED, bool M16, int NT, typename OutT>
 __global__ void __launch_bounds__(SB_THREADS, (GATED ? 2 : 4) / NT >= 1 ? (GATED ? 2 : 4) / NT : 1)
 smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* __restrict__ out, int M,
-                   int n_out, int K, int ldx, int ldw, int ldo, int inter, int* __restrict__ error_word) {
-    pdl_wait();
+                   int n_out, int K, int ldx, int ldw, int ldo, int inter, int w_static,
+                   int* __restrict__ error_word) {
     constexpr int STRIPS = GATED ? 2 : 1;
     constexpr int GROUPS = STRIPS * NT;               // 8-row groups of a stage
     constexpr int ROWS = 8 * GROUPS;
@@ -95,6 +95,10 @@ smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
 
     if (warp == SB_WARPS) {
         // ------------------------------------------------------------------ producer
+        // Weights that nothing writes while the engine runs are asked for at once, while the
+        // kernel before this one is still draining; otherwise W is the output of some kernel
+        // like x, and the copies wait for it.
+        if (!w_static) pdl_wait();
         // lane r asks for row r of the stage: rows n0 .. n0 + 8 NT - 1 (and inter + the same)
         int c = 0;
         bool ok = true;
@@ -124,6 +128,7 @@ smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
     }
 
     // ---------------------------------------------------------------------- consumers
+    pdl_wait();                           // x is the output of the kernel before
     const int g = lane >> 2, t = lane & 3;
     const bf16* xa = x + (size_t)min(g, M - 1) * ldx + 8 * t;
     const bf16* xb = x + (size_t)min(g + 8, M - 1) * ldx + 8 * t;
@@ -219,7 +224,7 @@ smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
 
 template <bool GATED, bool M16, int NT, typename OutT>
 static int launch_bulk_nt(const bf16* x, const bf16* W, OutT* out, int M, int n_out, int K, int ldx, int ldw,
-                          int ldo, int inter, int* error_word, cudaStream_t s) {
+                          int ldo, int inter, int w_static, int* error_word, cudaStream_t s) {
     static int resident = 0;   // CTAs of this variant that fit on the GPU at once
     auto kernel = smallm_bulk_kernel<GATED, M16, NT, OutT>;
     constexpr int SMEM = sb_smem(GATED, NT);
@@ -239,7 +244,7 @@ static int launch_bulk_nt(const bf16* x, const bf16* W, OutT* out, int M, int n_
     }
     const int nstrips = (n_out + 8 * NT - 1) / (8 * NT);
     const int grid = nstrips < resident ? nstrips : resident;
-    mstar_launch(kernel, dim3(grid), dim3(SB_THREADS), SMEM, s, x, W, out, M, n_out, K, ldx, ldw, ldo, inter, error_word);
+    mstar_launch(kernel, dim3(grid), dim3(SB_THREADS), SMEM, s, x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word);
     return launch_status();
 }
 
@@ -260,13 +265,13 @@ static int pick_nt(int n_out, bool gated) {
 
 template <bool GATED, bool M16, typename OutT>
 static int launch_bulk(const bf16* x, const bf16* W, OutT* out, int M, int n_out, int K, int ldx, int ldw,
-                       int ldo, int inter, int* error_word, cudaStream_t s) {
+                       int ldo, int inter, int w_static, int* error_word, cudaStream_t s) {
     switch (pick_nt(n_out, GATED)) {
         case 4:
             if constexpr (!GATED)
-                return launch_bulk_nt<GATED, M16, 4, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, error_word, s);
-        case 2: return launch_bulk_nt<GATED, M16, 2, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, error_word, s);
-        default: return launch_bulk_nt<GATED, M16, 1, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, error_word, s);
+                return launch_bulk_nt<GATED, M16, 4, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word, s);
+        case 2: return launch_bulk_nt<GATED, M16, 2, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word, s);
+        default: return launch_bulk_nt<GATED, M16, 1, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word, s);
     }
 }
 
@@ -275,10 +280,12 @@ static int launch_bulk(const bf16* x, const bf16* W, OutT* out, int M, int n_out
 // row stride ldw, out: bf16 or float (out_dtype) with row stride ldo.  Returns 0, a CUDA error
 // code, or -1 when the shape is refused: M outside 1..16, K no multiple of 32, leading
 // dimensions not multiples of 8 elements or pointers not 16-byte aligned (bulk copies), N odd
-// for the gated form.  `error_word`: device int, set to 13 / 14 if a bounded wait ran out.
+// for the gated form.  `w_static`: nonzero promises that nothing earlier on the stream writes W
+// (model weights), which lets the copies start before the kernel before this one has ended.
+// `error_word`: device int, set to 13 / 14 if a bounded wait ran out.
 MSTAR_API int mstar_gemm_smallm_bulk_bf16(const void* x, const void* W, void* out, int M, int N, int K,
                                           int ldx, int ldw, int ldo, int gated, int out_dtype,
-                                          int* error_word, void* stream) {
+                                          int w_static, int* error_word, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 16 || K <= 0 || K % 32 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || error_word == nullptr) return -1;
     if (((uintptr_t)x & 15) != 0 || ((uintptr_t)W & 15) != 0) return -1;
@@ -288,13 +295,13 @@ MSTAR_API int mstar_gemm_smallm_bulk_bf16(const void* x, const void* W, void* ou
     const bf16* wp = (const bf16*)W;
     if (gated) {
         if (M > 8)
-            return launch_bulk<true, true, bf16>(xp, wp, (bf16*)out, M, N / 2, K, ldx, ldw, ldo, N / 2, error_word, s);
-        return launch_bulk<true, false, bf16>(xp, wp, (bf16*)out, M, N / 2, K, ldx, ldw, ldo, N / 2, error_word, s);
+            return launch_bulk<true, true, bf16>(xp, wp, (bf16*)out, M, N / 2, K, ldx, ldw, ldo, N / 2, w_static, error_word, s);
+        return launch_bulk<true, false, bf16>(xp, wp, (bf16*)out, M, N / 2, K, ldx, ldw, ldo, N / 2, w_static, error_word, s);
     }
     if (out_dtype == MSTAR_F32) {
-        if (M > 8) return launch_bulk<false, true, float>(xp, wp, (float*)out, M, N, K, ldx, ldw, ldo, 0, error_word, s);
-        return launch_bulk<false, false, float>(xp, wp, (float*)out, M, N, K, ldx, ldw, ldo, 0, error_word, s);
+        if (M > 8) return launch_bulk<false, true, float>(xp, wp, (float*)out, M, N, K, ldx, ldw, ldo, 0, w_static, error_word, s);
+        return launch_bulk<false, false, float>(xp, wp, (float*)out, M, N, K, ldx, ldw, ldo, 0, w_static, error_word, s);
     }
-    if (M > 8) return launch_bulk<false, true, bf16>(xp, wp, (bf16*)out, M, N, K, ldx, ldw, ldo, 0, error_word, s);
-    return launch_bulk<false, false, bf16>(xp, wp, (bf16*)out, M, N, K, ldx, ldw, ldo, 0, error_word, s);
+    if (M > 8) return launch_bulk<false, true, bf16>(xp, wp, (bf16*)out, M, N, K, ldx, ldw, ldo, 0, w_static, error_word, s);
+    return launch_bulk<false, false, bf16>(xp, wp, (bf16*)out, M, N, K, ldx, ldw, ldo, 0, w_static, error_word, s);
 }

@@ -100,7 +100,7 @@ class Model:
                                device=self.runtime.device)
         rows = ops.gather_add_rows(stream.h, stream.take_delta(), want_rows)
         x = self.final_norm.norm_rows(rows)
-        return ops.linear(x, self.head, out_dtype=torch.float32)
+        return ops.linear(x, self.head, out_dtype=torch.float32, static_weights=True)
 
 
 def resolve_dtype(dtype) -> torch.dtype:

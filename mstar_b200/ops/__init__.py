@@ -347,15 +347,16 @@ def smallm_kernel(m: int, gated: bool) -> str:
     return "registers" if gated and m <= 8 else "bulk"
 
 
-def _gemm_smallm(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, gated: bool):
+def _gemm_smallm(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, gated: bool,
+                 static_weights: bool = False):
     m, k = x.shape
     n = w.shape[0]
     out = torch.empty((m, n // 2 if gated else n), dtype=out_dtype, device=x.device)
     if smallm_kernel(m, gated) == "bulk":
         code = lib.get("gemm_smallm_bulk").mstar_gemm_smallm_bulk_bf16(
             x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), w.stride(0),
-            out.stride(0), int(gated), _dt(out), tcgen05_error_word(x.device).data_ptr(),
-            _stream())
+            out.stride(0), int(gated), _dt(out), int(static_weights),
+            tcgen05_error_word(x.device).data_ptr(), _stream())
         what = "gemm_smallm_bulk"
     else:
         code = lib.get("gemm_smallm").mstar_gemm_smallm_bf16(
@@ -452,15 +453,18 @@ def tcgen05_tile(m: int, n: int) -> int | None:
     return None
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None):
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
+           static_weights: bool = False):
     """x[M,K] @ w[N,K]^T.  bfloat16 with at most ``SMALL_M`` rows: this package's
     weight-streaming kernel; more rows: this package's tcgen05 kernels where
     ``tcgen05_tile`` says so, else the library GEMM; anything involving a float32
-    operand runs in true float32."""
+    operand runs in true float32.  ``static_weights`` promises that no kernel earlier on
+    the stream writes ``w`` (model parameters): the weight-streaming kernel then starts
+    its copies while the kernel before it is still draining."""
     _need_cuda(x, w)
     out_dtype = out_dtype or x.dtype
     if out_dtype in (torch.bfloat16, torch.float32) and _smallm_ok(x, w):
-        return _gemm_smallm(x, w, out_dtype, gated=False)
+        return _gemm_smallm(x, w, out_dtype, gated=False, static_weights=static_weights)
     if out_dtype in (torch.bfloat16, torch.float32) and _tc_ok(x, w):
         tile = tcgen05_tile(x.shape[0], w.shape[0])
         if tile is not None:
@@ -478,12 +482,12 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     return convert(y, out_dtype)
 
 
-def gated_up(x: torch.Tensor, w_gate_up: torch.Tensor):
+def gated_up(x: torch.Tensor, w_gate_up: torch.Tensor, static_weights: bool = False):
     """silu(x Wg^T) * (x Wu^T) for the fused matrix [Wg; Wu]: one kernel for few
     bfloat16 rows, else the product followed by the SiLU-multiply kernel."""
     _need_cuda(x, w_gate_up)
     if _smallm_ok(x, w_gate_up) and w_gate_up.shape[0] % 2 == 0:
-        return _gemm_smallm(x, w_gate_up, torch.bfloat16, gated=True)
+        return _gemm_smallm(x, w_gate_up, torch.bfloat16, gated=True, static_weights=static_weights)
     if (_tc_ok(x, w_gate_up) and w_gate_up.shape[0] % 16 == 0
             and tcgen05_tile(x.shape[0], w_gate_up.shape[0]) is not None):
         return gemm_tcgen05_gated(x, w_gate_up)

@@ -53,7 +53,7 @@ _SIGNATURES = {
         "mstar_gemm_smallm_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     },
     "gemm_smallm_bulk": {
-        "mstar_gemm_smallm_bulk_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
+        "mstar_gemm_smallm_bulk_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
     },
     "gemm_tcgen05": {
         "mstar_gemm_tcgen05_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],

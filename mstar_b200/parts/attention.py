@@ -55,13 +55,13 @@ class Attention:
 
     def forward(self, x, ctx: StepContext, cache: LayerCache):
         s = self.spec
-        qkv = ops.linear(x, self.w_in)
+        qkv = ops.linear(x, self.w_in, static_weights=True)
         write_heads = 0 if s.shares_kv else s.num_kv_heads
         self.position.apply(qkv, ctx, None if s.shares_kv else cache.kv, cache.block_table,
                             cache.page_size, s.num_heads, write_heads)
         out = qkv.new_empty((ctx.num_tokens, s.num_heads * s.head_dim))
         self.attend(qkv, out, ctx, cache)
-        return ops.linear(out, self.w_out)
+        return ops.linear(out, self.w_out, static_weights=True)
 
     def attend(self, qkv, out, ctx: StepContext, cache: LayerCache) -> None:
         """bfloat16 with a head size the tensor-core kernels take: single-token entries

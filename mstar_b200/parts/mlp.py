@@ -25,7 +25,8 @@ class GatedMLP:
         self.down = params["down.weight"]
 
     def forward(self, x, ctx):
-        return ops.linear(ops.gated_up(x, self.gate_up), self.down)
+        return ops.linear(ops.gated_up(x, self.gate_up, static_weights=True), self.down,
+                          static_weights=True)
 
 
 register_part("ffn", "gated_mlp", GatedMLP)
