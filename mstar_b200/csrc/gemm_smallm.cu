@@ -39,8 +39,10 @@ template <> __device__ __forceinline__ void store_out<bf16>(bf16* p, float v) { 
 template <bool GATED, bool M16, typename OutT>
 __global__ void __launch_bounds__(SM_THREADS)
 smallm_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* __restrict__ out,
-                   int M, int n_out, int K, int ldx, int ldw, int ldo, int inter) {
-    pdl_wait();
+                   int M, int n_out, int K, int ldx, int ldw, int ldo, int inter, int w_static) {
+    // Weights that nothing writes while the engine runs are asked for before the wait for
+    // the kernel before this one (whose output x is); see the loop.
+    if (!w_static) pdl_wait();
     constexpr int STRIPS = GATED ? 2 : 1;
     __shared__ float red[STRIPS][SM_WARPS][16][8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -70,6 +72,7 @@ smallm_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
                 for (int s = 0; s < STRIPS; ++s) wv[s][u] = ld_stream(wp[s] + (kb + u) * 32);
             }
         }
+        if (w_static && kb == kb0) pdl_wait();   // the first weights are on their way
 #pragma unroll
         for (int u = 0; u < SM_UNROLL; ++u) {
             if (kb + u < kb1) {
@@ -88,6 +91,7 @@ smallm_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
         }
     }
 
+    if (w_static) pdl_wait();  // a warp without a part of K has not waited yet; nothing is stored before
     pdl_launch_dependents();   // the weights are here: the next kernel may be scheduled
     // ---- sum the warps' parts of K in shared memory: red[..][token][W row]
 #pragma unroll
@@ -127,8 +131,8 @@ smallm_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
 template <int NT, bool GATED, typename OutT>
 __global__ void __launch_bounds__(SM_THREADS)
 smallm_wide_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* __restrict__ out,
-                   int M, int n_out, int K, int ldx, int ldw, int ldo, int inter) {
-    pdl_wait();
+                   int M, int n_out, int K, int ldx, int ldw, int ldo, int inter, int w_static) {
+    if (!w_static) pdl_wait();            // as in the kernel above
     extern __shared__ float red[];  // [strips][SM_WARPS][16][8*NT]
     constexpr int COLS = 8 * NT;
     constexpr int STRIPS = GATED ? 2 : 1;
@@ -171,6 +175,7 @@ smallm_wide_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, 
                 }
             }
         }
+        if (w_static && kb == kb0) pdl_wait();   // the first weights are on their way
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             if (kb + u < kb1) {
@@ -190,6 +195,7 @@ smallm_wide_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, 
         }
     }
 
+    if (w_static) pdl_wait();  // a warp without a part of K has not waited yet; nothing is stored before
     pdl_launch_dependents();   // the weights are here: the next kernel may be scheduled
     // ---- sum the warps' parts of K in shared memory
 #pragma unroll
@@ -230,38 +236,40 @@ smallm_wide_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, 
 
 template <bool GATED, typename OutT>
 static int launch_smallm(const bf16* x, const bf16* W, OutT* out, int M, int n_out, int K, int ldx,
-                         int ldw, int ldo, int inter, cudaStream_t s) {
+                         int ldw, int ldo, int inter, int w_static, cudaStream_t s) {
     if (M <= 8 && n_out >= 8192 && n_out < 65536) {
         const size_t smem = (size_t)(GATED ? 2 : 1) * SM_WARPS * 16 * 8 * sizeof(float);
         mstar_launch((smallm_wide_gemm_kernel<1, GATED, OutT>), dim3((n_out + 15) / 16), dim3(SM_THREADS), smem, s, 
-            x, W, out, M, n_out, K, ldx, ldw, ldo, inter);
+            x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static);
         return launch_status();
     }
     const int grid = (n_out + 7) / 8;
     if (M <= 8)
         mstar_launch((smallm_gemm_kernel<GATED, false, OutT>), dim3(grid), dim3(SM_THREADS), 0, s, x, W, out, M, n_out, K,
-                                                                           ldx, ldw, ldo, inter);
+                                                                           ldx, ldw, ldo, inter, w_static);
     else
         mstar_launch((smallm_gemm_kernel<GATED, true, OutT>), dim3(grid), dim3(SM_THREADS), 0, s, x, W, out, M, n_out, K,
-                                                                          ldx, ldw, ldo, inter);
+                                                                          ldx, ldw, ldo, inter, w_static);
     return launch_status();
 }
 
 // out[M, N] = x W^T (gated == 0), or out[M, N/2] = silu(x Wg^T) * (x Wu^T) for W = [Wg; Wu]
 // (gated == 1).  out_dtype: MSTAR_BF16 or MSTAR_F32.  Returns 0, a CUDA error code, or -1
 // when the shape is refused: M outside 1..16, K no multiple of 32, leading dimensions not
-// multiples of 8 elements (16-byte loads), N odd for the gated form.
+// multiples of 8 elements (16-byte loads), N odd for the gated form.  `w_static`: nonzero
+// promises that nothing earlier on the stream writes W (model weights); the first weight
+// loads are then issued before the wait for the kernel before this one.
 MSTAR_API int mstar_gemm_smallm_bf16(const void* x, const void* W, void* out, int M, int N, int K,
                                      int ldx, int ldw, int ldo, int gated, int out_dtype,
-                                     void* stream) {
+                                     int w_static, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (M > 16 || K <= 0 || K % 32 != 0 || ldx % 8 != 0 || ldw % 8 != 0) return -1;
     if (gated && (N % 2 != 0 || out_dtype != MSTAR_BF16)) return -1;
     cudaStream_t s = (cudaStream_t)stream;
     const bf16* xp = (const bf16*)x;
     const bf16* wp = (const bf16*)W;
-    if (gated) return launch_smallm<true, bf16>(xp, wp, (bf16*)out, M, N / 2, K, ldx, ldw, ldo, N / 2, s);
+    if (gated) return launch_smallm<true, bf16>(xp, wp, (bf16*)out, M, N / 2, K, ldx, ldw, ldo, N / 2, w_static, s);
     if (out_dtype == MSTAR_F32)
-        return launch_smallm<false, float>(xp, wp, (float*)out, M, N, K, ldx, ldw, ldo, 0, s);
-    return launch_smallm<false, bf16>(xp, wp, (bf16*)out, M, N, K, ldx, ldw, ldo, 0, s);
+        return launch_smallm<false, float>(xp, wp, (float*)out, M, N, K, ldx, ldw, ldo, 0, w_static, s);
+    return launch_smallm<false, bf16>(xp, wp, (bf16*)out, M, N, K, ldx, ldw, ldo, 0, w_static, s);
 }

@@ -50,7 +50,7 @@ _SIGNATURES = {
         "mstar_sgemm_nt": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     },
     "gemm_smallm": {
-        "mstar_gemm_smallm_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
+        "mstar_gemm_smallm_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
     },
     "gemm_smallm_bulk": {
         "mstar_gemm_smallm_bulk_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
