@@ -136,11 +136,14 @@ class Scheduler:
             return 1 << 62
         return min(g.num_pages * g.page_size for g in self.manager.groups)
 
-    def _fits(self, requests: list, counts: list) -> bool:
-        if not requests:
-            return True
-        need = self.manager.pages_needed([r.request_id for r in requests], counts)
-        return all(n <= self.manager.free_pages(g) for g, n in enumerate(need))
+    def _need(self, r: Request, count: int) -> list:
+        """New pages per group that ``count`` more tokens of ``r`` take.  The need of a
+        batch is the sum over its requests, so a step's bookkeeping is one call per
+        request and decision instead of one per batch tried."""
+        return self.manager.pages_needed([r.request_id], [count])
+
+    def _free(self) -> list:
+        return [self.manager.free_pages(g) for g in range(len(self.manager.groups))]
 
     def _preempt_last(self, plan: StepPlan, keep: Optional[Request] = None) -> bool:
         """Take the pages of the request admitted last (other than ``keep``)."""
@@ -164,41 +167,83 @@ class Scheduler:
         cfg = self.config
         plan = StepPlan()
         budget = cfg.max_num_batched_tokens
-        chosen: list = []
+        groups = range(len(self.manager.groups))
+        chosen: list = []        # requests of this step, their token counts and page needs
         counts: list = []
+        needs: list = []
+        total = [0 for _ in groups]      # pages the chosen requests take, per group
+        free = self._free()
+
+        def fits(extra: list) -> bool:
+            return all(total[g] + extra[g] <= free[g] for g in groups)
+
+        def take(r: Request, n: int, need: list) -> None:
+            chosen.append(r)
+            counts.append(n)
+            needs.append(need)
+            for g in groups:
+                total[g] += need[g]
+
+        def after_preemption() -> None:
+            """A victim gave its pages back: it leaves the batch, the pools have grown."""
+            nonlocal chosen, counts, needs, total, free
+            kept = [i for i, c in enumerate(chosen) if c.status == "running"]
+            chosen = [chosen[i] for i in kept]
+            counts = [counts[i] for i in kept]
+            needs = [needs[i] for i in kept]
+            total = [sum(n[g] for n in needs) for g in groups]
+            free = self._free()
+
+        def portion(r: Request) -> tuple:
+            """Largest portion of r's pending tokens that the budget and the free pages
+            (after what is already chosen) allow, with its page need; 0 if not even one
+            token fits."""
+            hi = min(r.num_pending(), budget)
+            if hi <= 0:
+                return 0, None
+            need = self._need(r, hi)
+            if fits(need):
+                return hi, need
+            lo, lo_need = 0, None            # largest count known to fit (0: none yet)
+            while hi - lo > 1:               # invariant: lo fits (or is 0), hi does not
+                mid = (lo + hi) // 2
+                need = self._need(r, mid)
+                if fits(need):
+                    lo, lo_need = mid, need
+                else:
+                    hi = mid
+            return lo, lo_need
 
         # 1. one token for every request that is decoding, oldest first
         for r in list(self.running):
-            if r not in self.running or r.num_pending() != 1:
+            if r.status != "running" or r.num_pending() != 1:
                 continue
             if len(chosen) >= cfg.max_batch_size or budget < 1:
                 break
-            while not self._fits(chosen + [r], counts + [1]):
+            need = self._need(r, 1)
+            while not fits(need):
                 if not self._preempt_last(plan, keep=r):
                     break
-                kept = [(c, n) for c, n in zip(chosen, counts) if c in self.running]
-                chosen, counts = [c for c, _ in kept], [n for _, n in kept]
-            if r not in self.running:
-                continue
-            if not self._fits(chosen + [r], counts + [1]):
+                after_preemption()
+            if not fits(need):
                 # alone and still no page: the pool cannot hold this request
                 self._finish(r, "cache_exhausted", held=True)
                 plan.finished.append(r)
+                free = self._free()
                 continue
-            chosen.append(r)
-            counts.append(1)
+            take(r, 1, need)
             budget -= 1
 
         # 2. prompt portions of running requests, oldest first
+        decoding = {id(r) for r in chosen}
         for r in list(self.running):
-            if r in chosen or r.num_pending() < 1:
+            if id(r) in decoding or r.num_pending() < 1:
                 continue
             if len(chosen) >= cfg.max_batch_size or budget < 1:
                 break
-            n = self._portion(r, budget, chosen, counts)
+            n, need = portion(r)
             if n > 0:
-                chosen.append(r)
-                counts.append(n)
+                take(r, n, need)
                 budget -= n
 
         # 3. admit waiting requests while slots, the cap and pages allow
@@ -210,15 +255,14 @@ class Scheduler:
             if self.manager.free_slots() < 1:
                 break
             r = self.waiting[0]
-            if len(r.all_tokens()) + 1 > self._capacity_tokens():
+            if len(r.prompt) + len(r.output) + 1 > self._capacity_tokens():
                 self.waiting.popleft()
                 self._finish(r, "cache_exhausted", held=False)
                 plan.finished.append(r)
                 continue
             r.slot = self._admit(r.request_id)
-            n = self._portion(r, budget, chosen, counts)
-            if n > 0 and r.preemptions and not self._fits(chosen + [r],
-                                                          counts + [r.num_pending() + 1]):
+            n, need = portion(r)
+            if n > 0 and r.preemptions and not fits(self._need(r, r.num_pending() + 1)):
                 n = 0    # a pre-empted request returns only when all it had fits again
             if n <= 0:
                 self._release(r.request_id)   # no page for even one token now
@@ -228,8 +272,7 @@ class Scheduler:
             r.status = "running"
             self.running.append(r)
             plan.admitted.append(r)
-            chosen.append(r)
-            counts.append(n)
+            take(r, n, need)
             budget -= n
 
         # nothing can run although requests hold pages: they block one another (or one
@@ -243,27 +286,13 @@ class Scheduler:
                 self._preempt_last(plan, keep=oldest)
 
         for r, n in zip(chosen, counts):
-            toks = r.all_tokens()[r.num_computed:r.num_computed + n]
+            if n == 1 and r.num_pending() == 1:
+                toks = [r.output[-1] if r.output else r.prompt[-1]]
+            else:
+                toks = r.all_tokens()[r.num_computed:r.num_computed + n]
             plan.entries.append(ScheduledEntry(r, toks, r.num_computed + n == len(r.prompt)
                                                + len(r.output)))
         return plan
-
-    def _portion(self, r: Request, budget: int, chosen: list, counts: list) -> int:
-        """Largest portion of r's pending tokens that the budget and the free pages
-        (after what is already chosen) allow; 0 if not even one token fits."""
-        hi = min(r.num_pending(), budget)
-        if hi <= 0:
-            return 0
-        if self._fits(chosen + [r], counts + [hi]):
-            return hi
-        lo = 0                       # largest count known to fit (0: none yet)
-        while hi - lo > 1:           # invariant: lo fits (or is 0), hi does not
-            mid = (lo + hi) // 2
-            if self._fits(chosen + [r], counts + [mid]):
-                lo = mid
-            else:
-                hi = mid
-        return lo
 
     # -- after the forward pass -------------------------------------------
     def update(self, plan: StepPlan, sampled: dict) -> list:

@@ -27,7 +27,9 @@ def _dt(t: torch.Tensor) -> int:
 
 
 def _stream() -> int:
-    return torch.cuda.current_stream().cuda_stream
+    """Handle of the current CUDA stream of the current device (the raw accessors cost a
+    tenth of ``torch.cuda.current_stream()``, which matters at some 300 launches a step)."""
+    return torch._C._cuda_getCurrentRawStream(torch._C._cuda_getDevice())
 
 
 def _need_cuda(*tensors) -> None:
