@@ -145,10 +145,11 @@ class LLM:
 
     def _try_pipeline(self, prev) -> Optional[tuple]:
         """Launch the decode step that follows the in-flight one, if it can be foreseen:
-        nothing waits to be admitted, and every request of the in-flight step was
-        decoding.  Returns the new in-flight record, or None."""
+        no waiting request could be admitted now (a slot that the in-flight step frees is
+        filled one step late, as a stop takes effect one step late), and every request of
+        the in-flight step was decoding.  Returns the new in-flight record, or None."""
         plan, sampling, tokens = prev
-        if self.scheduler.waiting or tokens is None or len(sampling) != len(plan.entries):
+        if self.scheduler.may_admit() or tokens is None or len(sampling) != len(plan.entries):
             return None
         if any(len(e.tokens) != 1 for e in plan.entries):
             return None

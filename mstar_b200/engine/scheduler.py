@@ -121,6 +121,19 @@ class Scheduler:
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)
 
+    def may_admit(self) -> bool:
+        """Whether the next ``schedule`` could take a request from the waiting queue: one
+        waits, and neither the cap on running requests, the batch size nor the state slots
+        stand in the way (pages are not looked at)."""
+        if not self.waiting:
+            return False
+        cap = self.config.max_concurrent_requests
+        if cap is not None and len(self.running) >= cap:
+            return False
+        if len(self.running) >= self.config.max_batch_size:
+            return False
+        return self.manager.free_slots() >= 1
+
     # -- helpers ----------------------------------------------------------
     def _finish(self, r: Request, reason: str, held: bool) -> None:
         if held:

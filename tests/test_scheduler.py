@@ -191,3 +191,42 @@ def test_batch_size_cap():
     assert len(plan.entries) == 2
     plan, _ = run_step(cm, sch)
     assert len(plan.entries) == 2
+
+
+def test_may_admit_tells_whether_a_waiting_request_could_enter():
+    """The engine launches the next decode step ahead only while no waiting request could
+    be admitted: behind a full cap, a full batch or no free slot."""
+    cm, sch = make(cap=2, slots=8, budget=64)
+    assert not sch.may_admit()                        # nobody waits
+    for i in range(3):
+        sch.add(req(f"r{i}", 4, max_out=3))
+    assert sch.may_admit()
+    run_step(cm, sch)                                 # r0 and r1 enter, r2 waits behind the cap
+    assert [r.request_id for r in sch.running] == ["r0", "r1"] and len(sch.waiting) == 1
+    assert not sch.may_admit()
+    while len(sch.running) == 2:
+        run_step(cm, sch)
+    assert sch.may_admit()                            # one finished: r2 can enter now
+    cm2, sch2 = make(slots=1, budget=64)
+    sch2.add(req("a", 4)), sch2.add(req("b", 4))
+    run_step(cm2, sch2)
+    assert not sch2.may_admit()                       # the only state slot is taken
+    cm3, sch3 = make(batch=1, budget=64)
+    sch3.add(req("a", 4)), sch3.add(req("b", 4))
+    run_step(cm3, sch3)
+    assert not sch3.may_admit()                       # the batch is full
+
+
+def test_scheduling_cost_does_not_grow_with_the_square_of_the_batch():
+    """One cache-manager query per request and decision: a step with 64 decoding requests
+    asks for page needs about 64 times, not 64 * 64."""
+    cm, sch = make(pages=4000, slots=80, budget=4096, batch=64)
+    for i in range(64):
+        sch.add(req(f"r{i}", 8, max_out=50))
+    run_step(cm, sch)
+    calls = []
+    orig = cm.pages_needed
+    cm.pages_needed = lambda ids, counts: (calls.append(len(ids)), orig(ids, counts))[1]
+    plan, _ = run_step(cm, sch)
+    assert len(plan.entries) == 64
+    assert len(calls) <= 70 and max(calls) == 1
