@@ -242,8 +242,11 @@ static int launch_bulk_nt(const bf16* x, const bf16* W, OutT* out, int M, int n_
         if (per_sm < 1) return -2;
         resident = per_sm * sms;
     }
+    // as many CTAs as give every CTA the same number of strips (within one): 320 strips on
+    // 296 resident CTAs would leave 272 of them waiting for the 24 that take a second strip
     const int nstrips = (n_out + 8 * NT - 1) / (8 * NT);
-    const int grid = nstrips < resident ? nstrips : resident;
+    const int rounds = (nstrips + resident - 1) / resident;
+    const int grid = (nstrips + rounds - 1) / rounds;
     mstar_launch(kernel, dim3(grid), dim3(SB_THREADS), SMEM, s, x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word);
     return launch_status();
 }
