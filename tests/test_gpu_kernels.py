@@ -298,6 +298,19 @@ def test_prefill_attention_both_kernels(which, nq, nkv, page, hd, monkeypatch):
     assert tc_clean() == 0
 
 
+@pytest.mark.parametrize("page", [8, 16])
+def test_attention_kernels_over_long_contexts(page):
+    """Thousands of keys: the producers fetch block-table entries 32 at a time and wrap
+    their rings many times; one key far back carries a sixth of the weight."""
+    got, want, _ = paged_case([2500, 1], [5000, 4100], 6, 2, 128, page, torch.bfloat16, seed=3,
+                              kernel="prefill")
+    assert (got - want).abs().max() < 2e-2
+    got, want, vs = paged_case([1, 1, 1], [9000, 70, 4097], 6, 2, 128, page, torch.bfloat16,
+                               seed=4, spike=(0, 8000), kernel="decode")
+    assert (got - want).abs().max() < 2e-2
+    assert tc_clean() == 0
+
+
 def test_prefill_attention_kernel_choice(monkeypatch):
     from mstar_b200 import ops
 
