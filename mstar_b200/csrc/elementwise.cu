@@ -11,12 +11,20 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------- embedding
+// out[t] = float(table[id]) with id = ids[t], or, where `src` is given and src[t] >= 0,
+// id = prev[src[t]]: a token that the step before sampled and that is still on the device
+// (the engine launches a step before it has read the last one's tokens).
 template <typename W>
 __global__ void embed_rows_kernel(const W* __restrict__ table, const int* __restrict__ ids,
+                                  const int* __restrict__ src, const int* __restrict__ prev,
                                   float* __restrict__ out, int vocab, int hidden) {
     pdl_wait();
     const int t = blockIdx.x;
-    const int id = ids[t];
+    int id = ids[t];
+    if (src != nullptr) {
+        const int from = src[t];
+        if (from >= 0) id = prev[from];
+    }
     float* o = out + (size_t)t * hidden;
     if (id < 0 || id >= vocab) {  // host validates ids; never read out of the table
         for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = 0.f;
@@ -26,15 +34,21 @@ __global__ void embed_rows_kernel(const W* __restrict__ table, const int* __rest
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(row[i]);
 }
 
-MSTAR_API int mstar_embed_rows(const void* table, int table_dtype, const int* ids, float* out,
-                               int num_tokens, int vocab, int hidden, void* stream) {
+// `src` and `prev` are both null or both given (src: [num_tokens] ints, -1 where ids holds
+// the token; prev: int tokens on the device).
+MSTAR_API int mstar_embed_rows(const void* table, int table_dtype, const int* ids, const int* src,
+                               const int* prev, float* out, int num_tokens, int vocab, int hidden,
+                               void* stream) {
     if (num_tokens <= 0) return 0;
+    if ((src == nullptr) != (prev == nullptr)) return -1;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == MSTAR_F32)
-        mstar_launch((embed_rows_kernel<float>), dim3(num_tokens), dim3(threads), 0, s, (const float*)table, ids, out, vocab, hidden);
+        mstar_launch((embed_rows_kernel<float>), dim3(num_tokens), dim3(threads), 0, s, (const float*)table, ids,
+                     src, prev, out, vocab, hidden);
     else
-        mstar_launch((embed_rows_kernel<bf16>), dim3(num_tokens), dim3(threads), 0, s, (const bf16*)table, ids, out, vocab, hidden);
+        mstar_launch((embed_rows_kernel<bf16>), dim3(num_tokens), dim3(threads), 0, s, (const bf16*)table, ids,
+                     src, prev, out, vocab, hidden);
     return launch_status();
 }
 

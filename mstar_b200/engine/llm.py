@@ -76,9 +76,16 @@ class LLM:
         self.log_stats = log_stats
         self.stats = EngineStats()
         self._auto_id = 0
-        # a decode step that has been launched but whose tokens have not been read back
+        # the step that has been launched but whose tokens have not been read back: (plan,
+        # ids of the requests it samples for, their tokens on the device, the pinned host
+        # buffer they are copied to, the event after that copy)
         self._inflight = None
         self.pipelined_steps = 0
+        self._reported = 0              # finished requests handed to the caller so far
+        # pinned landing places of the sampled tokens: two steps can be under way
+        self._host_tokens = [torch.empty(max(max_batch_size, 1), dtype=torch.int32, pin_memory=True)
+                             for _ in range(3)]
+        self._turn = 0
 
     def _pages_from_memory(self, page_size: int, fraction: float) -> list:
         free, _ = torch.cuda.mem_get_info(self.device)
@@ -113,115 +120,94 @@ class LLM:
         return request_id
 
     def has_unfinished(self) -> bool:
-        return self.scheduler.has_work() or self._inflight is not None
+        return (self.scheduler.has_work() or self._inflight is not None
+                or self._reported < len(self.scheduler.finished))
 
     # -- one step ---------------------------------------------------------
-    # Steady decoding is pipelined one step deep, as the reference's worker does
-    # (mstar/worker/worker.py:2118-2211, 1328-1550: step N+1 is built and submitted
-    # while step N runs, and a stop takes effect one step late, worker.py:1612-1629):
-    # after launching step N the engine does not wait for its tokens; the next call
-    # launches step N+1 for the same requests with the tokens taken on the device, and
-    # only then reads step N's tokens back.  A request that turns out to have stopped at
-    # step N has one token computed in vain; a request that reaches max_output_tokens is
-    # foreseen and left out.
+    # Steps are pipelined one deep, as in the reference's worker (mstar/worker/worker.py:
+    # 2118-2211, 1328-1550: step N+1 is built and submitted while step N runs, and a stop
+    # takes effect one step late, worker.py:1612-1629).  A call plans and launches step N+1
+    # first and reads step N's tokens back afterwards: the tokens that step N sampled are
+    # fed to step N+1 on the device (the embedding takes them from the sampler's output),
+    # the scheduler counts them as places whose values arrive later.  So the GPU works on
+    # step N+1 while the host reads, finishes requests, and plans; a request that turns out
+    # to have stopped at step N has one token computed in vain, a request that reaches
+    # max_output_tokens is foreseen and left out.
 
-    def _launch(self, plan) -> tuple:
+    def _launch(self, plan, prev) -> tuple:
         """Run the plan's forward pass and sampling; tokens stay on the device."""
-        entries = [StepEntry(e.request.request_id, e.tokens,
-                             (len(e.tokens) - 1,) if e.samples else ())
-                   for e in plan.entries]
-        logits = self.stepper.step(entries)
+        source = {}
+        if prev is not None:
+            source = {rid: j for j, rid in enumerate(prev[1])}
+        entries, pending = [], {}
+        for i, e in enumerate(plan.entries):
+            tokens = e.tokens
+            if tokens[-1] is None:              # sampled by the step in flight
+                if len(tokens) != 1 or e.request.request_id not in source:
+                    raise RuntimeError("a token is missing that no step in flight will bring")
+                pending[i] = source[e.request.request_id]
+                tokens = [0]
+            entries.append(StepEntry(e.request.request_id, tokens,
+                                     (len(tokens) - 1,) if e.samples else ()))
+        logits = self.stepper.step(entries, pending, prev[2] if pending else None)
         sampling = [e.request.request_id for e in plan.entries if e.samples]
-        tokens = self.sampler.sample(sampling, logits) if sampling else None
-        return sampling, tokens
+        if not sampling:
+            return None
+        tokens = self.sampler.sample(sampling, logits)
+        # their copy to the host is queued now, before the next step is: reading it later
+        # waits for this step only
+        turn = self._turn = (self._turn + 1) % len(self._host_tokens)
+        if self._host_tokens[turn].numel() < len(sampling):
+            self._host_tokens[turn] = torch.empty(len(sampling), dtype=torch.int32, pin_memory=True)
+        host = self._host_tokens[turn][:len(sampling)]
+        host.copy_(tokens, non_blocking=True)
+        arrived = torch.cuda.Event()
+        arrived.record()
+        return plan, sampling, tokens, host, arrived
 
-    def _account(self, plan, sampled: dict) -> list:
-        finished = self.scheduler.update(plan, sampled)
-        self.stats.steps += 1
-        self.stats.prompt_tokens += sum(len(e.tokens) for e in plan.entries if not (
-            e.samples and len(e.tokens) == 1))
-        self.stats.generated_tokens += len(sampled)
-        return finished
-
-    def _try_pipeline(self, prev) -> Optional[tuple]:
-        """Launch the decode step that follows the in-flight one, if it can be foreseen:
-        no waiting request could be admitted now (a slot that the in-flight step frees is
-        filled one step late, as a stop takes effect one step late), and every request of
-        the in-flight step was decoding.  Returns the new in-flight record, or None."""
-        plan, sampling, tokens = prev
-        if self.scheduler.may_admit() or tokens is None or len(sampling) != len(plan.entries):
-            return None
-        if any(len(e.tokens) != 1 for e in plan.entries):
-            return None
-        if len(plan.entries) != len(self.scheduler.running):
-            return None
-        keep = [i for i, e in enumerate(plan.entries)
-                if len(e.request.output) + 1 < e.request.params.max_output_tokens]
-        if not keep:
-            return None
-        requests = [plan.entries[i].request for i in keep]
-        ids = [r.request_id for r in requests]
-        from ..cache.manager import CacheExhausted
-        from .scheduler import ScheduledEntry, StepPlan
-
-        source = tokens if len(keep) == len(plan.entries) else tokens[
-            torch.tensor(keep, dtype=torch.long, device=self.device)]
-        try:
-            logits = self.stepper.step_decode_from_device(ids, source)
-        except CacheExhausted:
-            return None                      # the scheduler decides who gives up pages
-        if logits is None:
-            return None
-        next_tokens = self.sampler.sample(ids, logits)
-        next_plan = StepPlan(entries=[ScheduledEntry(r, [None], True) for r in requests])
-        self.pipelined_steps += 1
-        return next_plan, ids, next_tokens
+    def _finished_and_complete(self) -> list:
+        """Requests that have finished and whose last tokens have arrived, each once."""
+        out = []
+        done = self.scheduler.finished
+        while self._reported < len(done):
+            r = done[self._reported]
+            if r.output and r.output[-1] is None:
+                break                            # its last token is still in flight
+            out.append(r)
+            self._reported += 1
+        return out
 
     def step(self) -> list:
-        """Schedule and run one batch; returns the requests that finished."""
+        """Plan and launch one batch, then read the tokens of the batch before; returns the
+        requests that finished."""
         t0 = time.perf_counter()
-        finished: list = []
-        if self._inflight is not None:
-            prev = self._inflight
-            nxt = self._try_pipeline(prev)                    # launch N+1 first ...
-            plan, sampling, tokens = prev
-            sampled = dict(zip(sampling, tokens.tolist()))    # ... then read N back
-            finished += self._account(plan, sampled)
-            if nxt is not None:
-                # requests that stopped at step N ran step N+1 in vain: drop them
-                nplan, nids, ntokens = nxt
-                alive = [i for i, e in enumerate(nplan.entries) if e.request.status == "running"]
-                if len(alive) != len(nplan.entries):
-                    nplan.entries = [nplan.entries[i] for i in alive]
-                    nids = [nids[i] for i in alive]
-                    ntokens = ntokens[torch.tensor(alive, dtype=torch.long, device=self.device)] \
-                        if alive else None
-                for e in nplan.entries:                       # the token fed was step N's
-                    e.tokens = [e.request.output[-1]]
-                nxt = (nplan, nids, ntokens) if nplan.entries else None
-            self._inflight = nxt
-            if self.log_stats:
-                self.stats.step_seconds.append(time.perf_counter() - t0)
-            return finished
+        prev = self._inflight
+        self._inflight = None
         plan = self.scheduler.schedule()
-        finished += list(plan.finished)
         self.stats.preemptions += len(plan.preempted)
         for r in plan.admitted:
             self.sampler.add_request(r.request_id, r.params, r.slot, generated=r.output)
         if plan.entries:
-            sampling, tokens = self._launch(plan)
-            decode_only = (tokens is not None and len(sampling) == len(plan.entries)
-                           and all(len(e.tokens) == 1 for e in plan.entries))
-            if decode_only and self.stepper.cuda_graphs:
-                self._inflight = (plan, sampling, tokens)     # read back at the next call
-            else:
-                sampled = dict(zip(sampling, tokens.tolist())) if sampling else {}
-                finished += self._account(plan, sampled)
-        elif not plan.preempted and not plan.finished and self.scheduler.has_work():
+            launched = self._launch(plan, prev)
+            self.scheduler.advance(plan)
+            self.stats.steps += 1
+            self.stats.prompt_tokens += sum(len(e.tokens) for e in plan.entries if not (
+                e.samples and len(e.tokens) == 1))
+            if prev is not None:
+                self.pipelined_steps += 1
+            self._inflight = launched           # None if the step samples nothing
+        elif (prev is None and not plan.preempted and not plan.finished
+              and self.scheduler.has_work()):
             raise RuntimeError("the scheduler can make no progress: no request fits the cache")
+        if prev is not None:
+            old_plan, old_sampling, _, host, arrived = prev
+            arrived.synchronize()
+            sampled = dict(zip(old_sampling, host.tolist()))
+            self.scheduler.resolve(old_plan, sampled)
+            self.stats.generated_tokens += len(sampled)
         if self.log_stats:
             self.stats.step_seconds.append(time.perf_counter() - t0)
-        return finished
+        return self._finished_and_complete()
 
     def generate(self, prompts, sampling_params=None, request_ids=None) -> list:
         """Generate for one prompt (a list of token ids) or several (a list of lists).

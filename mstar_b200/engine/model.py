@@ -91,7 +91,7 @@ class Model:
                 block_tables: Sequence[torch.Tensor],
                 want_rows: Optional[torch.Tensor]) -> torch.Tensor:
         """Run the tokens of one step; return float logits [len(want_rows), vocab]."""
-        stream = ResidualStream(ops.embed_rows(self.embed, token_ids))
+        stream = ResidualStream(ops.embed_rows(self.embed, token_ids, source=ctx.token_source))
         for entry in self.layout.order:
             self.blocks[entry.block].forward(stream, ctx, storage.layer_cache(entry.cache,
                                                                                block_tables))

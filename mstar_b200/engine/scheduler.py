@@ -308,22 +308,56 @@ class Scheduler:
         return plan
 
     # -- after the forward pass -------------------------------------------
-    def update(self, plan: StepPlan, sampled: dict) -> list:
-        """``sampled``: request id -> token for every entry with ``samples``.  Advances
-        computed counts, appends tokens, finishes and frees.  Returns the requests that
-        finished in this step."""
-        done = []
+    # A step's bookkeeping is split in two so that the engine can launch the next step
+    # before it has read this one's tokens: ``advance`` right after the launch (counts, a
+    # place for each sampled token, the finish on max_output_tokens, which needs no
+    # value), ``resolve`` when the values have arrived (the finish on a stop token, which
+    # therefore takes effect one step late, as in the reference's worker,
+    # mstar/worker/worker.py:1612-1629).  ``update`` is both at once.
+    def advance(self, plan: StepPlan) -> None:
+        """The plan has been launched: its tokens count as computed, every entry that
+        samples gets a place (None) at the end of its request's output."""
         for e in plan.entries:
             r = e.request
             r.num_computed += len(e.tokens)
             if not e.samples:
                 continue
-            tok = int(sampled[r.request_id])
-            r.output.append(tok)
-            if (not r.params.ignore_eos) and tok in self.stop_token_ids:
-                self._finish(r, "stop", held=True)
-                done.append(r)
-            elif len(r.output) >= r.params.max_output_tokens:
+            r.output.append(None)
+            if len(r.output) >= r.params.max_output_tokens and r.status == "running":
                 self._finish(r, "length", held=True)
+
+    def resolve(self, plan: StepPlan, sampled: dict) -> list:
+        """``sampled``: request id -> token for every entry of the (advanced) plan with
+        ``samples``.  Fills the places, finishes on stop tokens and frees.  Returns the
+        requests that finished with this step."""
+        done = []
+        for e in plan.entries:
+            if not e.samples:
+                continue
+            r = e.request
+            where = len(r.output)              # the first of the (at most two) open places
+            while where > 0 and r.output[where - 1] is None:
+                where -= 1
+            if where == len(r.output):
+                continue        # stopped a step ago: this token was computed in vain
+            tok = int(sampled[r.request_id])
+            r.output[where] = tok
+            if (not r.params.ignore_eos) and tok in self.stop_token_ids:
+                del r.output[where + 1:]       # the place the step after took, if any
+                if r.status == "finished":
+                    r.finish_reason = "stop"   # the last allowed token was a stop token
+                elif r.status == "running":
+                    self._finish(r, "stop", held=True)
+                else:                          # pre-empted meanwhile: it holds nothing
+                    self.waiting.remove(r)
+                    self._finish(r, "stop", held=False)
                 done.append(r)
+            elif r.status == "finished" and where == len(r.output) - 1:
+                done.append(r)                 # finished on its length, now complete
         return done
+
+    def update(self, plan: StepPlan, sampled: dict) -> list:
+        """``advance`` and ``resolve`` in one: for callers that read a step's tokens before
+        they plan the next."""
+        self.advance(plan)
+        return self.resolve(plan, sampled)

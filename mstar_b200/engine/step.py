@@ -72,7 +72,7 @@ class DecodeGraph:
         self.widths = list(widths)
         mgr, storage = stepper.manager, stepper.storage
         self.pad_pages = [storage.pad_page(g) for g in range(len(mgr.groups))]
-        self.extra = (("token_ids", bucket), ("want_rows", bucket))
+        self.extra = (("token_ids", bucket), ("want_rows", bucket), ("token_src", bucket))
         probe = mgr.fill_batch([], [], extra=self.extra, widths=self.widths, pad_entries=bucket,
                                pad_page=self.pad_pages, pad_slot=storage.pad_slot)
         self.offsets = probe.offsets
@@ -94,11 +94,11 @@ class DecodeGraph:
             qo_indptr=view("qo_indptr"), kv_len=view("kv_len"), slots=view("slots"),
             q_lens=[1] * bucket, kv_lens=[bound] * bucket,
             host_slots=[storage.pad_slot] * bucket, max_q_len=1, max_kv_len=bound,
-            num_decode=bucket)
+            num_decode=bucket, token_source=(view("token_src"), stepper.device_tokens))
         self.tables = [view(f"table{g}").view(bucket, -1) for g in range(len(mgr.groups))]
         self.token_ids = view("token_ids")
         self.want_rows = view("want_rows")
-        self._stage([], [])
+        self._stage([], [], None)
         model = stepper.model
         side = torch.cuda.Stream(device=stepper.device)
         side.wait_stream(torch.cuda.current_stream())
@@ -113,8 +113,10 @@ class DecodeGraph:
                                         self.want_rows)
         self.launches = ops_lib.launch_count() - before   # own kernels in one replay
 
-    def _stage(self, requests: list, tokens: list) -> int:
-        """Fill the next pinned buffer for this batch and start its copy to the device."""
+    def _stage(self, requests: list, tokens: list, sources) -> int:
+        """Fill the next pinned buffer for this batch and start its copy to the device.
+        ``sources[i]``: index into the stepper's device tokens that request i's token is
+        taken from, or -1 (``tokens[i]`` is it); None: all from ``tokens``."""
         turn = self.turn
         self.turn = (turn + 1) % self.RING
         if self.events[turn] is not None:
@@ -130,20 +132,22 @@ class DecodeGraph:
         index.packed[off + n:off + length] = 0
         off, length = index.offsets["want_rows"]
         index.packed[off:off + length] = np.arange(length, dtype=np.int32)
+        off, length = index.offsets["token_src"]
+        index.packed[off:off + length] = -1
+        if sources is not None:
+            index.packed[off:off + n] = sources
         self.dev.copy_(pinned, non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self.events[turn] = ev
         return self.size * 4
 
-    def run(self, requests: list, tokens: list, device_tokens=None) -> torch.Tensor:
-        """``device_tokens``: int32 tensor on the device holding the requests' tokens (the
-        sampler's output of the previous step); it replaces ``tokens`` without the host
-        ever seeing the values."""
-        nbytes = self._stage(requests, tokens)
+    def run(self, requests: list, tokens: list, sources=None) -> torch.Tensor:
+        """``sources``: per request, the index into the stepper's device tokens (the
+        sampler's output of the step before) that replaces ``tokens[i]`` without the host
+        ever seeing the value, or -1."""
+        nbytes = self._stage(requests, tokens, sources)
         self.stepper.last_h2d_bytes = nbytes
-        if device_tokens is not None:
-            self.token_ids[:len(requests)].copy_(device_tokens)
         self.graph.replay()
         ops_lib.add_launches(self.launches)
         return self.logits[:len(requests)]
@@ -160,6 +164,9 @@ class Stepper:
         self.cuda_graphs = bool(cuda_graphs) and getattr(model, "graph_safe", False)
         self._graphs: dict = {}
         self.graph_replays = 0
+        # tokens sampled by the step before, for steps launched before the host has read
+        # them (see ``step``); captured graphs read this buffer
+        self.device_tokens = torch.zeros(max(DECODE_BUCKETS), dtype=torch.int32, device=self.device)
 
     # -- requests ---------------------------------------------------------
     def add_request(self, request: Hashable) -> int:
@@ -180,14 +187,32 @@ class Stepper:
         self._staging = torch.empty(n, dtype=torch.int32, pin_memory=True)
         return self._staging.numpy()
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], pending: Optional[dict] = None,
+             device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run one batch; returns float32 logits [number of wanted places, vocab] on
         the device, in the order of ``entries`` and of each entry's ``want``.
-        Raises ``CacheExhausted`` (nothing changed) if the pages do not suffice."""
+        Raises ``CacheExhausted`` (nothing changed) if the pages do not suffice.
+
+        ``pending``: entry index -> index into ``device_tokens`` (int32 on the device, the
+        tokens the step before sampled).  Such an entry brings one token whose value the
+        host does not know yet (its ``tokens`` hold any valid id); the step is launched
+        without waiting for it."""
         vocab = self.model.vocab_size
         entries = list(entries)
         if not entries:
             return torch.empty((0, vocab), dtype=torch.float32, device=self.device)
+        pending = pending or {}
+        if pending:
+            if device_tokens is None or device_tokens.dtype != torch.int32:
+                raise ValueError("pending tokens need the int32 device tensor they come from")
+            if device_tokens.numel() > self.device_tokens.numel():
+                self.device_tokens = torch.zeros(device_tokens.numel(), dtype=torch.int32,
+                                                 device=self.device)
+                self._graphs.clear()                # they captured the old buffer
+            for i, src in pending.items():
+                if len(entries[i].tokens) != 1 or not 0 <= src < device_tokens.numel():
+                    raise ValueError("a pending entry brings one token from the device tokens")
+            self.device_tokens[:device_tokens.numel()].copy_(device_tokens, non_blocking=True)
         for e in entries:
             if len(e.tokens) == 0:
                 raise ValueError(f"request {e.request!r} brings no tokens to this step")
@@ -200,7 +225,7 @@ class Stepper:
         # single tokens first: kernels specialised for one query per request take
         # tokens [0, num_decode), the others the rest
         if self.cuda_graphs and all(len(e.tokens) == 1 for e in entries):
-            logits = self._step_decode_graph(entries)
+            logits = self._step_decode_graph(entries, pending)
             if logits is not None:
                 return logits
         order = sorted(range(len(entries)), key=lambda i: (len(entries[i].tokens) != 1, i))
@@ -213,14 +238,21 @@ class Stepper:
         total = starts[-1]
 
         self.manager.reserve(requests, counts)
-        index: BatchIndex = self.manager.fill_batch(
-            requests, counts, extra=(("token_ids", total), ("want_rows", len(want_rows))),
-            alloc=self._pinned)
+        extra = [("token_ids", total), ("want_rows", len(want_rows))]
+        if pending:
+            extra.append(("token_src", total))
+        index: BatchIndex = self.manager.fill_batch(requests, counts, extra=tuple(extra),
+                                                    alloc=self._pinned)
         o, n = index.offsets["token_ids"]
         index.packed[o:o + n] = np.fromiter((t for e in ordered for t in e.tokens),
                                             dtype=np.int32, count=total)
         o, n = index.offsets["want_rows"]
         index.packed[o:o + n] = np.asarray(want_rows, dtype=np.int32)
+        if pending:
+            o, n = index.offsets["token_src"]
+            index.packed[o:o + n] = -1
+            for i, src in pending.items():
+                index.packed[o + start_of[i]] = src
 
         dev = torch.empty(index.packed.size, dtype=torch.int32, device=self.device)
         dev.copy_(self._staging[:index.packed.size], non_blocking=True)
@@ -236,7 +268,8 @@ class Stepper:
             positions=view("positions"), cache_pos=view("cache_pos"),
             qo_indptr=view("qo_indptr"), kv_len=view("kv_len"), slots=view("slots"),
             q_lens=counts, kv_lens=index.kv_len.tolist(), host_slots=index.slots.tolist(),
-            max_q_len=max(counts), max_kv_len=int(index.kv_len.max()), num_decode=num_decode)
+            max_q_len=max(counts), max_kv_len=int(index.kv_len.max()), num_decode=num_decode,
+            token_source=(view("token_src"), self.device_tokens) if pending else None)
         tables = [view(f"table{g}").view(len(ordered), -1)
                   for g in range(len(self.manager.groups))]
         logits = self.model.forward(view("token_ids"), ctx, self.storage, tables,
@@ -247,17 +280,7 @@ class Stepper:
         return logits
 
 
-    def step_decode_from_device(self, requests: list, device_tokens: torch.Tensor):
-        """One decode step for ``requests`` whose next tokens are still on the device
-        (``device_tokens``, int32, one per request, in order): the step is launched
-        without waiting for them.  Logits for every request; None if this batch cannot
-        run as a captured graph (the caller then takes the ordinary path)."""
-        if not self.cuda_graphs or _bucket(len(requests)) is None:
-            return None
-        entries = [StepEntry(r, (0,), (0,)) for r in requests]
-        return self._step_decode_graph(entries, device_tokens=device_tokens)
-
-    def _step_decode_graph(self, entries: list, device_tokens=None):
+    def _step_decode_graph(self, entries: list, pending: Optional[dict] = None):
         """A batch of single tokens as the replay of a captured graph; None when the
         batch is larger than the largest captured shape."""
         bucket = _bucket(len(entries))
@@ -270,7 +293,10 @@ class Stepper:
         graph = self._graphs.get(key)
         if graph is None:
             graph = self._graphs[key] = DecodeGraph(self, bucket, list(widths))
-        logits = graph.run(requests, [e.tokens[0] for e in entries], device_tokens)
+        sources = None
+        if pending:
+            sources = [pending.get(i, -1) for i in range(len(entries))]
+        logits = graph.run(requests, [e.tokens[0] for e in entries], sources)
         for request in requests:
             self.manager.commit(request, 1)
         self.steps += 1

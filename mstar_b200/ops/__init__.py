@@ -43,16 +43,24 @@ def _ptr(t) -> int:
     return 0 if t is None else t.data_ptr()
 
 
-def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None):
-    """out[t] = float(table[ids[t]]); the residual stream is float in both dtypes."""
+def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None,
+               source=None):
+    """out[t] = float(table[ids[t]]); the residual stream is float in both dtypes.
+    ``source`` = (src, prev): where src[t] >= 0 the token is prev[src[t]] instead, a token
+    that is on the device only (int32 tensors, src as long as ids)."""
     _need_cuda(table, ids)
     assert ids.dtype == torch.int32 and table.dim() == 2 and table.is_contiguous()
     n, (vocab, hidden) = ids.numel(), table.shape
     if out is None:
         out = torch.empty((n, hidden), dtype=torch.float32, device=table.device)
+    src = prev = None
+    if source is not None:
+        src, prev = source
+        _need_cuda(src, prev)
+        assert src.dtype == torch.int32 and prev.dtype == torch.int32 and src.numel() == n
     check(lib.get("elementwise").mstar_embed_rows(
-        table.data_ptr(), _dt(table), ids.data_ptr(), out.data_ptr(), n, vocab, hidden,
-        _stream()), "embed_rows")
+        table.data_ptr(), _dt(table), ids.data_ptr(), _ptr(src), _ptr(prev), out.data_ptr(), n,
+        vocab, hidden, _stream()), "embed_rows")
     return out
 
 

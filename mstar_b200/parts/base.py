@@ -77,6 +77,9 @@ class StepContext:
     max_kv_len: int = 0
     # entries [0, num_decode) bring exactly one token each (tokens [0, num_decode))
     num_decode: int = 0
+    # (src, prev) or None: where src[t] >= 0, token t is prev[src[t]], a token that the step
+    # before sampled and that only the device holds yet (int32 tensors)
+    token_source: Optional[tuple] = None
     extras: dict = field(default_factory=dict)
 
 

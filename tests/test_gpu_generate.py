@@ -120,3 +120,70 @@ def test_command_line(model_folders):
     record = json.loads(out.stdout.strip().splitlines()[-1])
     assert record["token_ids"] == P.plain_greedy(tensors, raw, prompt, 5)
     assert "generated_tokens=5" in out.stderr
+
+
+@pytest.mark.parametrize("graphs", [True, False])
+def test_tokens_taken_from_the_device_give_the_same_logits(model_folders, graphs):
+    """A step may bring tokens that only the device holds (what the step before sampled):
+    decode-only batches (a graph replay) and batches mixed with a prompt portion give the
+    logits they give with the same tokens passed from the host."""
+    from mstar_b200.engine.model import load_model
+    from mstar_b200.engine.step import StepEntry, make_stepper
+
+    folder, raw, _ = model_folders["tiny_a"]
+    model = load_model(folder, dtype="float32")
+    vocab = raw["vocab_size"]
+    prompts = [H.request_tokens(vocab, n, seed=500 + n) for n in (6, 11, 3)]
+    late = H.request_tokens(vocab, 9, seed=77)
+    nxt = [5, 17, 3]
+
+    def run(from_device: bool):
+        st = make_stepper(model, page_size=4, num_pages=64, cuda_graphs=graphs)
+        for i in range(3):
+            st.add_request(i)
+        st.add_request("late")
+        st.step([StepEntry(i, prompts[i], ()) for i in range(3)])
+        on_device = torch.tensor([nxt[2], 999 % vocab, nxt[0], nxt[1]], dtype=torch.int32,
+                                 device="cuda:0")          # in another order, with a stranger
+        where = {0: 2, 1: 3, 2: 0}
+        outs = []
+        for mixed in (False, True):
+            entries = [StepEntry(i, [0 if from_device else nxt[i]], (0,)) for i in range(3)]
+            if mixed:
+                entries.insert(1, StepEntry("late", late, (len(late) - 1,)))
+            pending = None
+            if from_device:
+                pending = {k: where[e.request] for k, e in enumerate(entries)
+                           if e.request != "late"}
+            outs.append(st.step(entries, pending, on_device if from_device else None).clone())
+        return outs
+
+    for a, b in zip(run(False), run(True)):
+        assert torch.equal(a, b)
+
+
+def test_stop_and_length_through_the_pipelined_entry_point(model_folders, tmp_path):
+    """Steps are launched before the tokens of the step before are read: a request that
+    stops is cut at its stop token although one more token was computed for it, and the
+    other requests of the batch are not disturbed."""
+    from mstar_b200 import LLM, SamplingParams
+
+    folder, raw, tensors = model_folders["tiny_a"]
+    prompts = [H.request_tokens(raw["vocab_size"], n, seed=600 + n) for n in (4, 9, 13, 6)]
+    free = SamplingParams(temperature=0.0, max_output_tokens=12, ignore_eos=True)
+    ref = LLM(folder, dtype="float32", page_size=4, max_num_pages=64).generate(prompts, free)
+    # declare the 5th token of request 1 a stop token: config.json's eos_token_id
+    stop = ref[1].token_ids[4]
+    from mstar_b200.config.registry import config_from_dict
+    from mstar_b200.weights.random_init import write_model_folder
+
+    alt = tmp_path / "with_stop"
+    write_model_folder(alt, config_from_dict({**raw, "eos_token_id": int(stop)}), 0, tensors=tensors)
+    llm = LLM(alt, dtype="float32", page_size=4, max_num_pages=64)
+    got = llm.generate(prompts, SamplingParams(temperature=0.0, max_output_tokens=12))
+    for r, g in zip(ref, got):
+        cut = r.token_ids.index(stop) + 1 if stop in r.token_ids else len(r.token_ids)
+        assert g.token_ids == r.token_ids[:cut]
+        assert g.finish_reason == ("stop" if stop in r.token_ids else "length")
+    assert llm.pipelined_steps > 0
+    assert llm.stepper.manager.num_requests() == 0 and llm.stepper.manager.check() == 0

@@ -230,3 +230,97 @@ def test_scheduling_cost_does_not_grow_with_the_square_of_the_batch():
     plan, _ = run_step(cm, sch)
     assert len(plan.entries) == 64
     assert len(calls) <= 70 and max(calls) == 1
+
+
+def launch_then_read(cm, sch, pending, token):
+    """One engine step the pipelined way: plan and launch the next batch (``advance``),
+    then read the batch before (``resolve``).  ``pending``: the plan in flight or None.
+    Returns (the new plan in flight, requests reported as finished by the resolve)."""
+    plan = sch.schedule()
+    ids = [e.request.request_id for e in plan.entries]
+    counts = [len(e.tokens) for e in plan.entries]
+    cm.reserve(ids, counts)
+    for i, c in zip(ids, counts):
+        cm.commit(i, c)
+    sch.advance(plan)
+    done = []
+    if pending is not None:
+        sampled = {e.request.request_id: token(e.request) for e in pending.entries if e.samples}
+        done = sch.resolve(pending, sampled)
+    assert cm.check() == 0
+    return plan, done
+
+
+def test_advance_then_resolve_a_stop_takes_effect_one_step_late():
+    """The next step is planned before the last one's tokens are known: places (None) stand
+    for them; a request that stopped has one token computed in vain, which is dropped."""
+    cm, sch = make(budget=64)
+    sch.add(req("a", 4, max_out=10))
+    sch.add(req("b", 4, max_out=10))
+    count = {"a": 0, "b": 0}
+
+    def token(r):                       # a stops with its second token, b never
+        count[r.request_id] += 1
+        return 99 if (r.request_id == "a" and count["a"] == 2) else 7
+
+    p0, _ = launch_then_read(cm, sch, None, token)            # prompts; samples pending
+    a, b = p0.entries[0].request, p0.entries[1].request
+    assert a.output == [None] and b.output == [None]
+    p1, done = launch_then_read(cm, sch, p0, token)           # decode 1 launched, p0 read
+    assert p1.entries[0].tokens == [None] and a.output == [7, None] and not done
+    p2, done = launch_then_read(cm, sch, p1, token)           # decode 2 launched, p1 read: a stopped
+    assert [r.request_id for r in done] == ["a"] and a.finish_reason == "stop"
+    assert a.output == [7, 99]                                # the place of decode 2 is gone
+    assert a.status == "finished" and [r.request_id for r in sch.running] == ["b"]
+    p3, done = launch_then_read(cm, sch, p2, token)           # a's token of decode 2 is ignored
+    assert not done and a.output == [7, 99] and b.output == [7, 7, 7, None]
+    assert all(e.request is b for e in p3.entries)
+
+
+def test_advance_foresees_the_length_and_resolve_reports_it_complete():
+    cm, sch = make(budget=64)
+    sch.add(req("a", 4, max_out=2))
+    p0, _ = launch_then_read(cm, sch, None, lambda r: 7)
+    a = p0.entries[0].request
+    p1, done = launch_then_read(cm, sch, p0, lambda r: 7)
+    assert a.status == "finished" and a.finish_reason == "length"     # foreseen at the launch
+    assert not done and a.output == [7, None]                         # ... but not complete
+    p2, done = launch_then_read(cm, sch, p1, lambda r: 5)
+    assert not p2.entries and [r.request_id for r in done] == ["a"] and a.output == [7, 5]
+    # the last allowed token is a stop token: the reason says so
+    sch.add(req("b", 4, max_out=1))
+    p0, _ = launch_then_read(cm, sch, None, lambda r: 99)
+    b = p0.entries[0].request
+    assert b.finish_reason == "length"
+    _, done = launch_then_read(cm, sch, p0, lambda r: 99)
+    assert [r.request_id for r in done] == ["b"] and b.finish_reason == "stop" and b.output == [99]
+
+
+def test_a_preempted_request_keeps_the_place_of_its_token_in_flight():
+    cm, sch = make(pages=6, page=4, budget=64)
+    sch.add(req("old", 7, max_out=20))
+    sch.add(req("new", 7, max_out=20))
+    inflight, _ = launch_then_read(cm, sch, None, lambda r: 7)
+    victim = None
+    for _ in range(12):
+        plan = sch.schedule()
+        if plan.preempted:
+            victim = plan.preempted[0]
+            assert victim.request_id == "new" and victim.output[-1] is None
+            ids = [e.request.request_id for e in plan.entries]
+            cm.reserve(ids, [1] * len(ids))
+            for i in ids:
+                cm.commit(i, 1)
+            sch.advance(plan)
+            sch.resolve(inflight, {e.request.request_id: 7 for e in inflight.entries if e.samples})
+            break
+        ids = [e.request.request_id for e in plan.entries]
+        counts = [len(e.tokens) for e in plan.entries]
+        cm.reserve(ids, counts)
+        for i, c in zip(ids, counts):
+            cm.commit(i, c)
+        sch.advance(plan)
+        sch.resolve(inflight, {e.request.request_id: 7 for e in inflight.entries if e.samples})
+        inflight = plan
+    assert victim is not None and None not in victim.output     # the value arrived all the same
+    assert victim.status == "waiting" and victim.num_computed == 0
