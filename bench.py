@@ -39,7 +39,7 @@ ORPHEUS_3B = dict(
 )
 PROMPT_LEN = 2048
 CONTEXT = 4096
-PAGE_SIZE = 16
+PAGE_SIZE = 64
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 

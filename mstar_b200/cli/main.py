@@ -67,7 +67,7 @@ def _generate(args) -> None:
 
     dtype = args.dtype or deploy.get("autocast_dtype") or "bfloat16"
     llm = LLM(args.model, dtype=dtype,
-              page_size=args.page_size or kv.get("page_size", 16),
+              page_size=args.page_size or kv.get("page_size", 64),
               max_num_pages=args.max_num_pages or kv.get("max_num_pages"),
               max_num_batched_tokens=args.max_num_batched_tokens,
               max_concurrent_requests=args.max_concurrent_requests

@@ -601,12 +601,15 @@ decode_attention_ring_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeA
             const int* bt = a.block_table + (size_t)a.token_req[t] * a.bt_stride;
             // pages beyond the request's last one are replaced by it: masked keys stay finite
             const int last_page = (hi - 1) / ps;
-            const int per_tile = DEC_TILE / ps;
+            // a tile is DEC_TILE / ps whole pages, or, with pages of 128 or 256 keys, a part of one
+            const int per_tile = ps < DEC_TILE ? DEC_TILE / ps : 1;
+            const int box_rows = ps < DEC_TILE ? ps : DEC_TILE;
             const int ntiles = (ke - ks + DEC_TILE - 1) / DEC_TILE;
             int mine = 0, have_from = -1;              // lanes hold pages have_from .. +31
             for (int it = 0; it < ntiles; ++it, ++c) {
                 const int st = c % S;
-                const int base_page = (ks + it * DEC_TILE) / ps;
+                const int key0 = ks + it * DEC_TILE;
+                const int base_page = key0 / ps;
                 if (have_from < 0 || base_page + per_tile > have_from + 32) {
                     have_from = base_page;
                     mine = bt[min(base_page + lane, last_page)];
@@ -625,10 +628,12 @@ decode_attention_ring_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeA
                 const int p = lane / HALVES, h = lane % HALVES;
                 const int page = __shfl_sync(0xffffffffu, mine, (base_page + p - have_from) & 31);
                 if (p < per_tile) {
-                    unsigned char* kdst = ring + (size_t)st * 2 * TILE_BYTES + h * (64 * 128) + p * ps * 128;
-                    tma_load_2d(tc_smem(kdst), &kv_map, full + 8 * st, h * 64, ((page * 2) * a.nkv + kvh) * ps);
+                    unsigned char* kdst = ring + (size_t)st * 2 * TILE_BYTES + h * (64 * 128) + p * box_rows * 128;
+                    const int in_page = key0 % ps;      // 0 unless the page is larger than the tile
+                    tma_load_2d(tc_smem(kdst), &kv_map, full + 8 * st, h * 64,
+                                ((page * 2) * a.nkv + kvh) * ps + in_page);
                     tma_load_2d(tc_smem(kdst + TILE_BYTES), &kv_map, full + 8 * st, h * 64,
-                                ((page * 2 + 1) * a.nkv + kvh) * ps);
+                                ((page * 2 + 1) * a.nkv + kvh) * ps + in_page);
                 }
             }
         }
@@ -867,17 +872,17 @@ static int launch_decode_ring(const CUtensorMap& map, const DecodeArgs& a, int t
 }
 
 // Tensor map of a cache [pages, 2, nkv, page_size, hd] (bfloat16) seen as the matrix
-// [pages * 2 * nkv * page_size, hd] with boxes of page_size rows x 64 features, 128-byte
-// swizzle.  `out_map` receives the 128-byte map.  Returns 0, -1 (shape not taken), -3 / -4.
+// [pages * 2 * nkv * page_size, hd] with boxes of min(page_size, 64) rows x 64 features,
+// 128-byte swizzle; page sizes 8..64 that divide 64, 128 and 256.  `out_map` receives the 128-byte map.  Returns 0, -1 (shape not taken), -3 / -4.
 MSTAR_API int mstar_make_kv_tensor_map(void* out_map, const void* kv_cache, long long pages, int nkv,
                                        int page_size, int hd) {
-    if (hd % 64 != 0 || hd > 256 || page_size < 8 || page_size > 64 || DEC_TILE % page_size != 0)
-        return -1;
+    const bool small_page = page_size >= 8 && page_size <= 64 && DEC_TILE % page_size == 0;
+    if (hd % 64 != 0 || hd > 256 || !(small_page || page_size == 128 || page_size == 256)) return -1;
     EncodeTiledFn fn = encode_tiled_fn();
     if (fn == nullptr) return -3;
     const cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)pages * 2 * nkv * page_size};
     const cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
-    const cuuint32_t box[2] = {64, (cuuint32_t)page_size};
+    const cuuint32_t box[2] = {64, (cuuint32_t)(page_size < DEC_TILE ? page_size : DEC_TILE)};
     const cuuint32_t elem[2] = {1, 1};
     const CUresult r = fn(reinterpret_cast<CUtensorMap*>(out_map), CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
                           const_cast<void*>(kv_cache), dims, strides, box, elem,
@@ -898,7 +903,8 @@ MSTAR_API int mstar_paged_decode_attention_bf16_tma(
     if (chunk <= 0 || chunk % DEC_TILE != 0 || splits < 1 || splits > MERGE_MAX_SPLITS) return -1;
     if (splits > 1 && scratch == nullptr) return -1;
     if (tokens > 65535 || nkv > 65535) return -1;
-    if (page_size < 8 || page_size > 64 || DEC_TILE % page_size != 0) return -1;
+    const bool small_page = page_size >= 8 && page_size <= 64 && DEC_TILE % page_size == 0;
+    if (!(small_page || page_size == 128 || page_size == 256)) return -1;
     DecodeArgs a;
     a.q = (const bf16*)q;
     a.kv = (const bf16*)kv_cache;
@@ -927,6 +933,7 @@ MSTAR_API int mstar_paged_decode_attention_bf16_tma(
         per_item = (e != nullptr && strcmp(e, "per_item") == 0) ? 1 : 0;
     }
     if (per_item) {
+        if (!small_page) return -1;       // that kernel copies whole pages
         switch (hd) {
             case 64: return launch_decode_tma<64>(map, a, tokens, error_word, s);
             case 128: return launch_decode_tma<128>(map, a, tokens, error_word, s);

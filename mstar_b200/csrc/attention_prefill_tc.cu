@@ -207,13 +207,16 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillT
         // (one dependent global load per page would cost more than the copies), lane 0
         // waits for the stages and issues the copies.
         const int last_page = (hi - 1) / ps;
-        const int per_tile = PT_KEYS / ps;            // pages per tile: 1, 2, 4 or 8
+        // a tile is 1, 2, 4 or 8 whole pages, or, with pages of 128 or 256 keys, a part of one
+        const int per_tile = ps < PT_KEYS ? PT_KEYS / ps : 1;
+        const int box_rows = ps < PT_KEYS ? ps : PT_KEYS;
         int mine = 0, have_from = -1;                 // lanes hold pages have_from .. +31
         bool ok = true;
         for (int j = 0; j < ntiles; ++j) {
             const int s = j & 1;
             const uint32_t free_parity = (((uint32_t)j >> 1) & 1u) ^ 1u;
-            const int base_page = j * per_tile;
+            const int base_page = j * PT_KEYS / ps;
+            const int in_page = j * PT_KEYS % ps;     // 0 unless the page is larger than the tile
             if (have_from < 0 || base_page + per_tile > have_from + 32) {
                 have_from = base_page;
                 // pages beyond the last are replaced by the last: masked rows stay finite
@@ -229,12 +232,12 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillT
             // are issued side by side
             const int p = lane / NB, h = lane % NB;
             const int page = __shfl_sync(0xffffffffu, mine, (base_page + p - have_from) & 31);
-            const uint32_t dst_off = (uint32_t)(s * PT_KV_TILE + h * (PT_KEYS * 128) + p * ps * 128);
+            const uint32_t dst_off = (uint32_t)(s * PT_KV_TILE + h * (PT_KEYS * 128) + p * box_rows * 128);
             if (lane == 0) mbar_expect_tx(k_full + 8 * s, PT_KV_TILE);
             __syncwarp();
             if (p < per_tile)
                 tma_load_2d(tc_smem(k_s + dst_off), &kv_map, k_full + 8 * s, h * 64,
-                            ((page * 2) * a.nkv + kvh) * ps);
+                            ((page * 2) * a.nkv + kvh) * ps + in_page);
             // values, once O += P V of tile j-2 is done
             if (lane == 0 && !mbar_wait(v_empty + 8 * s, free_parity)) {
                 atomicExch(error_word, 7);
@@ -245,7 +248,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillT
             __syncwarp();
             if (p < per_tile)
                 tma_load_2d(tc_smem(v_s + dst_off), &kv_map, v_full + 8 * s, h * 64,
-                            ((page * 2 + 1) * a.nkv + kvh) * ps);
+                            ((page * 2 + 1) * a.nkv + kvh) * ps + in_page);
         }
     } else if (warp == 4) {
         // ------------------------------------------------ S = Q K^T, while the softmax works on
@@ -487,7 +490,7 @@ static int launch_prefill_tc(const CUtensorMap& map, const PrefillTcArgs& a, dim
 }
 
 // Entries [first_entry, first_entry + entries) of the batch.  head_dim must be 64, 128 or
-// 256, the page size 8..64 dividing 64, no window.  `kv_map`: the cache's tensor map.
+// 256, the page size 8..64 dividing 64, or 128 or 256, no window.  `kv_map`: the cache's tensor map.
 // Returns 0, a CUDA error code or -1 (shape refused).  `error_word` receives 6..12 if a wait
 // ran out (6: the shared memory was not aligned as the swizzle needs).
 MSTAR_API int mstar_paged_prefill_attention_tc(
@@ -498,7 +501,9 @@ MSTAR_API int mstar_paged_prefill_attention_tc(
     if ((hd != 64 && hd != 128 && hd != 256) || !(scale > 0.f) || nkv <= 0 || nq % nkv != 0 ||
         kv_map == nullptr || error_word == nullptr)
         return -1;
-    if (page_size < 8 || page_size > 64 || PT_KEYS % page_size != 0) return -1;
+    if (!((page_size >= 8 && page_size <= 64 && PT_KEYS % page_size == 0) || page_size == 128 ||
+          page_size == 256))
+        return -1;
     if (entries > 65535) return -1;
     PrefillTcArgs a;
     a.q = (const bf16*)q;

@@ -47,7 +47,7 @@ class EngineStats:
 
 class LLM:
     def __init__(self, model, dtype: str = "bfloat16", device: str = "cuda:0", *,
-                 page_size: int = 16, max_num_pages: Optional[int] = None,
+                 page_size: int = 64, max_num_pages: Optional[int] = None,
                  kv_cache_memory_fraction: float = 0.85,
                  max_num_batched_tokens: int = 2048,
                  max_concurrent_requests: Optional[int] = 64, max_batch_size: int = 64,

@@ -205,6 +205,9 @@ def decode_split(tokens: int, num_kv_heads: int, max_len: int, ring: bool = Fals
     return chunk, splits
 
 
+# page sizes whose caches the TMA kernels take: boxes of min(page, 64) keys
+TMA_PAGE_SIZES = (8, 16, 32, 64, 128, 256)
+
 _kv_maps: dict = {}
 
 
@@ -243,6 +246,8 @@ def paged_decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
         max_len = min(max_len, window)
     kv_map = kv_tensor_map(kv_cache) if not window else None
     ring = kv_map is not None and os.environ.get("MSTAR_DECODE_ATTENTION") != "per_item"
+    if not ring and page_size > 64:
+        kv_map = None                       # the per-item TMA kernel copies whole pages
     chunk, splits = decode_split(tokens, num_kv_heads, max(max_len, 1), ring=ring)
     scratch = None
     if splits > 1:
@@ -273,12 +278,11 @@ def paged_decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
 
 def prefill_attention_kernel(has_kv_map: bool, head_dim: int, page_size: int) -> str:
     """"tcgen05" or "mma": which prefill attention kernel runs.  The tcgen05 kernel takes
-    head_dim 64, 128 or 256, no window and page sizes 8..64 dividing 64, and is the faster
-    one from the shortest portions on; MSTAR_PREFILL_ATTENTION=mma selects the other one."""
+    head_dim 64, 128 or 256, no window and the page sizes of ``TMA_PAGE_SIZES``, and is the
+    faster one from the shortest portions on; MSTAR_PREFILL_ATTENTION=mma selects the other."""
     import os
 
-    takes = (has_kv_map and head_dim in (64, 128, 256) and 8 <= page_size <= 64
-             and 64 % page_size == 0)
+    takes = has_kv_map and head_dim in (64, 128, 256) and page_size in TMA_PAGE_SIZES
     if not takes or os.environ.get("MSTAR_PREFILL_ATTENTION") == "mma":
         return "mma"
     return "tcgen05"

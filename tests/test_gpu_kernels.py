@@ -245,7 +245,8 @@ def test_paged_attention_window_edge(act):
 
 # page sizes 8..64 with head sizes 64/128/256 take the TMA path of the decode kernel
 SHAPES_FAST = [(6, 2, 64, 4), (5, 1, 32, 16), (3, 3, 16, 8), (24, 8, 128, 16), (2, 1, 256, 2),
-               (16, 1, 64, 16), (4, 2, 256, 8), (6, 3, 128, 32), (8, 8, 64, 64)]
+               (16, 1, 64, 16), (4, 2, 256, 8), (6, 3, 128, 32), (8, 8, 64, 64),
+               (6, 2, 128, 128), (4, 4, 64, 256), (3, 1, 256, 128)]   # pages larger than a tile
 
 
 @pytest.mark.parametrize("nq,nkv,hd,page", SHAPES_FAST)
@@ -298,7 +299,7 @@ def test_prefill_attention_both_kernels(which, nq, nkv, page, hd, monkeypatch):
     assert tc_clean() == 0
 
 
-@pytest.mark.parametrize("page", [8, 16])
+@pytest.mark.parametrize("page", [8, 16, 128])
 def test_attention_kernels_over_long_contexts(page):
     """Thousands of keys: the producers fetch block-table entries 32 at a time and wrap
     their rings many times; one key far back carries a sixth of the weight."""
