@@ -14,6 +14,9 @@
 // library call; here one kernel does penalty, max, thresholds for top-k / top-p by
 // bisection over the ordered bit patterns of the logits, and an inverse-CDF draw in
 // index order.  The sampled token is marked in the request's seen-mask row.
+#include <cooperative_groups.h>
+#include <string.h>
+
 #include "common.cuh"
 
 #define SAMPLE_THREADS 1024
@@ -228,12 +231,371 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab,
     }
 }
 
+// ------------------------------------------------------------------ cluster variant
+// The same sampling with a thread-block cluster of 8 CTAs per row: each CTA keeps an
+// eighth of the row in shared memory (the penalised logits and their exponentials), so the
+// row is read from global memory once; the thresholds of top-k and top-p are found by radix
+// selection (three rounds of 11, 11 and 10 bits with a histogram per round, summed across
+// the cluster through distributed shared memory) instead of 32 passes of bisection each.
+// The selection runs on keys that spread the row's range [min, max] linearly over 32 bits
+// (a monotone map of the penalised logits: the bit patterns themselves would put nearly
+// all tokens into the few bins of their common exponents, and the histogram's atomics
+// would serialise); logits closer than range / 2^32 count as tied, and ties with the last
+// kept token are kept, as before.  Probability mass is counted in 64-bit fixed
+// point (exp * 2^40, exact integer sums), so that no sum depends on the order in which it
+// is made: the same (seed, offset) always draws the same token.  With the reference's
+// default options (temperature, top-p and a repetition penalty) a row of 157 k logits takes
+// tens of microseconds instead of three milliseconds.
+#define CS_CLUSTER 8
+#define CS_THREADS 512
+#define CS_BINS 2048
+#define CS_SCALE 1099511627776.f      // 2^40
+
+namespace cg = cooperative_groups;
+
+__device__ __forceinline__ unsigned long long cs_fixed(float e) { return __float2ull_rz(e * CS_SCALE); }
+
+// Sum of one u64 per thread over the block; every thread gets it.  `scratch`: 32 u64.
+__device__ __forceinline__ unsigned long long cs_block_sum(unsigned long long v, unsigned long long* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    unsigned long long r = lane < CS_THREADS / 32 ? scratch[lane] : 0ull;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+    return r;
+}
+
+// One value per CTA -> the values of all CTAs of the cluster, in rank order.  `slot`: 8 u64
+// in this CTA's shared memory (the same variable in every CTA).
+__device__ __forceinline__ void cs_gather(cg::cluster_group& cluster, unsigned long long mine,
+                                          unsigned long long* slot, unsigned long long (&all)[CS_CLUSTER]) {
+    if (threadIdx.x == 0) slot[0] = mine;
+    cluster.sync();
+#pragma unroll
+    for (int r = 0; r < CS_CLUSTER; ++r) all[r] = *cluster.map_shared_rank(slot, r);
+    cluster.sync();          // nobody overwrites its slot before everybody has read it
+}
+
+// The bin of a radix round.  hist: this CTA's histogram (counts or masses, u64), complete for
+// this CTA's threads only after the barrier inside; ghist: the cluster-wide histogram, kept
+// in rank 0's shared memory and zero between rounds.  Every CTA adds its non-empty bins to it
+// (remote atomics: stores, no round trips); rank 0 walks the bins from the top and finds the
+// bin b where the running sum `above + sum(bins > b)` is still below `need` and `above +
+// sum(bins >= b)` reaches it, and writes (b, above + sum(bins > b)) into every CTA's `result`.
+// Returns b (0 if the need is never reached) and updates `above`.
+__device__ __forceinline__ int cs_pick_bin(cg::cluster_group& cluster, int rank, unsigned long long* hist,
+                                           unsigned long long* ghist, unsigned long long* scratch,
+                                           unsigned long long* result, unsigned long long need,
+                                           unsigned long long& above) {
+    constexpr int PER = CS_BINS / CS_THREADS;      // bins per thread: 4
+    const int tid = threadIdx.x;
+    __syncthreads();                                // this CTA's histogram is complete
+    unsigned long long* total = cluster.map_shared_rank(ghist, 0);
+    for (int bin = tid; bin < CS_BINS; bin += CS_THREADS) {
+        const unsigned long long v = hist[bin];
+        if (v != 0ull) atomicAdd(total + bin, v);
+    }
+    cluster.sync();                                 // every CTA's bins have arrived
+    if (rank == 0) {
+        unsigned long long mine[PER];
+        unsigned long long local = 0ull;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) {
+            mine[j] = ghist[tid * PER + j];
+            ghist[tid * PER + j] = 0ull;            // ready for the next round
+            local += mine[j];
+        }
+        // suffix sums over the threads' totals: after = sum of the bins of threads > tid
+        const int lane = tid & 31, warp = tid >> 5;
+        unsigned long long incl = local;            // inclusive suffix within the warp
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned long long up = __shfl_down_sync(0xffffffffu, incl, o);
+            if (lane + o < 32) incl += up;
+        }
+        if (lane == 0) scratch[warp] = incl;        // the warp's total
+        __syncthreads();
+        unsigned long long after = incl - local;    // bins of higher lanes of this warp
+        for (int w = warp + 1; w < CS_THREADS / 32; ++w) after += scratch[w];
+        const unsigned long long before = above + after;        // everything in higher bins
+        if (tid == 0) {                             // the answer if nothing reaches the need
+            for (int r = 0; r < CS_CLUSTER; ++r) {
+                unsigned long long* dst = cluster.map_shared_rank(result, r);
+                dst[0] = 0ull;
+                dst[1] = above;
+            }
+        }
+        __syncthreads();
+        if (before < need && before + local >= need) {          // at most one thread
+            unsigned long long run = before;
+            for (int j = PER - 1; j >= 0; --j) {
+                if (run + mine[j] >= need) {
+                    for (int r = 0; r < CS_CLUSTER; ++r) {
+                        unsigned long long* dst = cluster.map_shared_rank(result, r);
+                        dst[0] = (unsigned long long)(tid * PER + j);
+                        dst[1] = run;
+                    }
+                    break;
+                }
+                run += mine[j];
+            }
+        }
+    }
+    cluster.sync();                                 // the result has been written everywhere
+    above = result[1];
+    return (int)result[0];
+}
+
+__global__ void __cluster_dims__(CS_CLUSTER, 1, 1) __launch_bounds__(CS_THREADS)
+sample_cluster_kernel(const float* __restrict__ logits, int ld, int vocab, int chunk,
+                      const float* __restrict__ temperature, const int* __restrict__ top_k,
+                      const float* __restrict__ top_p, const float* __restrict__ penalty,
+                      unsigned char* __restrict__ seen_mask, const int* __restrict__ seen_rows,
+                      const long long* __restrict__ seed, const long long* __restrict__ offset,
+                      int* __restrict__ out) {
+    pdl_wait();
+    cg::cluster_group cluster = cg::this_cluster();
+    extern __shared__ __align__(16) unsigned char cs_smem[];
+    float* sv = reinterpret_cast<float*>(cs_smem);                  // penalised logits [chunk]
+    float* se = sv + chunk;                                         // exponentials [chunk]
+    unsigned long long* hist = reinterpret_cast<unsigned long long*>(se + chunk);
+    unsigned long long* ghist = hist + CS_BINS;
+    __shared__ unsigned long long scratch[32];
+    __shared__ unsigned long long slot[1];
+    __shared__ unsigned long long result[2];
+    __shared__ float best_v[32], low_v[32];
+    __shared__ int best_i[32];
+
+    const int row = blockIdx.x / CS_CLUSTER, rank = (int)cluster.block_rank();
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int base = rank * chunk;
+    const int n = max(0, min(chunk, vocab - base));
+    const float* x = logits + (size_t)row * ld;
+    const float pen = penalty != nullptr ? penalty[row] : 1.f;
+    const int srow = (seen_mask != nullptr && seen_rows != nullptr) ? seen_rows[row] : -1;
+    unsigned char* my_seen = srow >= 0 ? seen_mask + (size_t)srow * vocab : nullptr;
+    const unsigned char* seen = (my_seen != nullptr && pen != 1.f) ? my_seen : nullptr;
+
+    for (int b = tid; b < CS_BINS; b += CS_THREADS) ghist[b] = 0ull;   // before the first cluster barrier
+    // ---- the row, once: penalty, maximum and argmax (smallest index among equal maxima)
+    float bv = -INFINITY, lowest = INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = tid; i < n; i += CS_THREADS) {
+        float v = x[base + i];
+        if (seen != nullptr && seen[base + i]) v = v > 0.f ? v / pen : v * pen;
+        sv[i] = v;
+        if (v > bv || (v == bv && base + i < bi)) { bv = v; bi = base + i; }
+        if (v > -INFINITY) lowest = fminf(lowest, v);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        lowest = fminf(lowest, __shfl_xor_sync(0xffffffffu, lowest, o));
+    }
+    if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; low_v[warp] = lowest; }
+    __syncthreads();
+    if (warp == 0) {
+        bv = lane < CS_THREADS / 32 ? best_v[lane] : -INFINITY;
+        bi = lane < CS_THREADS / 32 ? best_i[lane] : 0x7fffffff;
+        lowest = lane < CS_THREADS / 32 ? low_v[lane] : INFINITY;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            lowest = fminf(lowest, __shfl_xor_sync(0xffffffffu, lowest, o));
+        }
+        if (lane == 0) low_v[0] = lowest;
+    }
+    __syncthreads();
+    lowest = low_v[0];
+    unsigned long long all[CS_CLUSTER];
+    // (value, index) packed: the ordered bits of the value above, the index below (inverted,
+    // so that the larger word is the larger value or, among equals, the smaller index)
+    cs_gather(cluster, ((unsigned long long)ordered_bits(bv) << 32) | (unsigned)(0x7fffffff - bi), slot, all);
+    unsigned long long top = 0ull;
+#pragma unroll
+    for (int r = 0; r < CS_CLUSTER; ++r) top = all[r] > top ? all[r] : top;
+    const float vmax = from_ordered_bits((unsigned)(top >> 32));
+    const int amax = 0x7fffffff - (int)(unsigned)(top & 0xffffffffu);
+
+    const float temp = temperature[row];
+    if (temp <= 0.f) {                      // uniform over the cluster; all reads are done
+        if (rank == 0 && tid == 0) {
+            out[row] = amax;
+            if (my_seen != nullptr) my_seen[amax] = 1;
+        }
+        return;
+    }
+    const float inv_temp = 1.f / temp;
+    // the row's minimum over the cluster (ordered bits inverted: the largest word is the smallest value)
+    cs_gather(cluster, (unsigned long long)(~ordered_bits(lowest)), slot, all);
+    unsigned long long low_word = 0ull;
+#pragma unroll
+    for (int r = 0; r < CS_CLUSTER; ++r) low_word = all[r] > low_word ? all[r] : low_word;
+    const float vmin = fminf(from_ordered_bits(~(unsigned)low_word), vmax);
+    // exponentials, and the selection keys in place of the logits
+    const double spread = vmax > vmin ? 4294967295.0 / ((double)vmax - (double)vmin) : 0.0;
+    unsigned* sq = reinterpret_cast<unsigned*>(sv);
+    for (int i = tid; i < n; i += CS_THREADS) {
+        const float v = sv[i];
+        se[i] = expf((v - vmax) * inv_temp);
+        const double q = v > vmin ? ((double)v - (double)vmin) * spread : 0.0;
+        sq[i] = q >= 4294967295.0 ? 0xffffffffu : (unsigned)q;
+    }
+    __syncthreads();
+
+    // ---- top-k: tau = the k-th largest key, by radix selection on counts
+    unsigned tau = 0u;
+    const int k = top_k != nullptr ? top_k[row] : 0;
+    if (k > 0 && k < vocab) {
+        unsigned prefix = 0u;
+        unsigned long long above = 0ull;
+        int decided = 0;
+        for (int round = 0; round < 3; ++round) {
+            const int bits = round < 2 ? 11 : 10;
+            const int shift = 32 - decided - bits;
+            for (int b = tid; b < CS_BINS; b += CS_THREADS) hist[b] = 0ull;
+            __syncthreads();
+            for (int i = tid; i < n; i += CS_THREADS) {
+                const unsigned key = sq[i];
+                if (decided == 0 || (key >> (32 - decided)) == prefix)
+                    atomicAdd(&hist[(key >> shift) & ((1u << bits) - 1u)], 1ull);
+            }
+            const int bin = cs_pick_bin(cluster, rank, hist, ghist, scratch, result, (unsigned long long)k, above);
+            prefix = (prefix << bits) | (unsigned)bin;
+            decided += bits;
+        }
+        tau = prefix;
+    }
+
+    // ---- mass of the kept tokens
+    unsigned long long mass = 0ull;
+    for (int i = tid; i < n; i += CS_THREADS)
+        if (sq[i] >= tau) mass += cs_fixed(se[i]);
+    mass = cs_block_sum(mass, scratch);
+    cs_gather(cluster, mass, slot, all);
+    unsigned long long total = 0ull;
+#pragma unroll
+    for (int r = 0; r < CS_CLUSTER; ++r) total += all[r];
+
+    // ---- top-p: the largest tau2 >= tau whose tokens (x >= tau2) hold p of that mass
+    const float p = top_p != nullptr ? top_p[row] : 1.f;
+    if (p < 1.f) {
+        const unsigned long long need = (unsigned long long)((double)p * (double)total);
+        unsigned prefix = 0u;
+        unsigned long long above = 0ull;
+        int decided = 0;
+        for (int round = 0; round < 3; ++round) {
+            const int bits = round < 2 ? 11 : 10;
+            const int shift = 32 - decided - bits;
+            for (int b = tid; b < CS_BINS; b += CS_THREADS) hist[b] = 0ull;
+            __syncthreads();
+            for (int i = tid; i < n; i += CS_THREADS) {
+                const unsigned key = sq[i];
+                if (key >= tau && (decided == 0 || (key >> (32 - decided)) == prefix))
+                    atomicAdd(&hist[(key >> shift) & ((1u << bits) - 1u)], cs_fixed(se[i]));
+            }
+            const int bin = cs_pick_bin(cluster, rank, hist, ghist, scratch, result, need > 0ull ? need : 1ull, above);
+            prefix = (prefix << bits) | (unsigned)bin;
+            decided += bits;
+        }
+        if (prefix > tau) {
+            tau = prefix;
+            mass = 0ull;
+            for (int i = tid; i < n; i += CS_THREADS)
+                if (sq[i] >= tau) mass += cs_fixed(se[i]);
+            mass = cs_block_sum(mass, scratch);
+            cs_gather(cluster, mass, slot, all);
+            total = 0ull;
+#pragma unroll
+            for (int r = 0; r < CS_CLUSTER; ++r) total += all[r];
+        }
+    }
+
+    // ---- inverse-CDF draw over the kept tokens in index order (exact integer prefix sums)
+    unsigned c[4];
+    const unsigned long long sd = seed != nullptr ? (unsigned long long)seed[row] : 0ull;
+    const unsigned long long of = offset != nullptr ? (unsigned long long)offset[row] : 0ull;
+    c[0] = (unsigned)of; c[1] = (unsigned)(of >> 32); c[2] = 0u; c[3] = 0u;
+    philox4x32_10((unsigned)sd, (unsigned)(sd >> 32), c);
+    const double u = (double)(c[0] >> 8) * (1.0 / 16777216.0);   // [0, 1)
+    unsigned long long target = (unsigned long long)(u * (double)total);
+    if (target >= total) target = total - 1;                      // total > 0: the maximum counts 2^40
+    unsigned long long before_me = 0ull;                          // mass of the CTAs of lower rank
+#pragma unroll
+    for (int r = 0; r < CS_CLUSTER; ++r)
+        if (r < rank) before_me += all[r];
+    if (target >= before_me && target < before_me + all[rank]) {  // the token is in this CTA
+        const int per = (n + CS_THREADS - 1) / CS_THREADS;
+        const int begin = min(tid * per, n), end = min(begin + per, n);
+        unsigned long long mine = 0ull;
+        for (int i = begin; i < end; ++i)
+            if (sq[i] >= tau) mine += cs_fixed(se[i]);
+        // exclusive prefix of `mine` over the threads
+        unsigned long long incl = mine;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned long long up = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += up;
+        }
+        __syncthreads();
+        if (lane == 31) scratch[warp] = incl;
+        __syncthreads();
+        unsigned long long excl = before_me + incl - mine;
+        for (int w = 0; w < warp; ++w) excl += scratch[w];
+        if (mine > 0ull && target >= excl && target < excl + mine) {
+            unsigned long long run = excl;
+            int pick = amax;
+            for (int i = begin; i < end; ++i) {
+                if (sq[i] >= tau) {
+                    run += cs_fixed(se[i]);
+                    if (target < run) { pick = base + i; break; }
+                }
+            }
+            out[row] = pick;
+            if (my_seen != nullptr) my_seen[pick] = 1;
+        }
+    }
+}
+
+static int cs_chunk(int vocab) { return ((vocab + CS_CLUSTER - 1) / CS_CLUSTER + 3) & ~3; }
+static size_t cs_smem_bytes(int vocab) {
+    return (size_t)cs_chunk(vocab) * 8 + 2 * CS_BINS * sizeof(unsigned long long);
+}
+
 MSTAR_API int mstar_sample(const float* logits, int ld, int rows, int vocab,
                            const float* temperature, const int* top_k, const float* top_p,
                            const float* penalty, unsigned char* seen_mask, const int* seen_rows,
                            const long long* seed, const long long* offset, int* out,
                            void* stream) {
     if (rows <= 0) return 0;
+    // rows of up to ~200 k logits fit the shared memory of a cluster of 8 CTAs
+    static int one_block = -1;          // MSTAR_SAMPLER=block: the one-block-per-row kernel
+    if (one_block < 0) {
+        const char* e = getenv("MSTAR_SAMPLER");
+        one_block = (e != nullptr && strcmp(e, "block") == 0) ? 1 : 0;
+    }
+    const size_t smem = cs_smem_bytes(vocab);
+    if (!one_block && smem <= 200 * 1024 && rows <= 65535 / CS_CLUSTER * CS_CLUSTER) {
+        static size_t configured = 0;
+        if (smem > configured) {
+            cudaError_t e = cudaFuncSetAttribute(sample_cluster_kernel,
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+            configured = smem;
+        }
+        mstar_launch((sample_cluster_kernel), dim3(rows * CS_CLUSTER), dim3(CS_THREADS), smem,
+                     (cudaStream_t)stream, logits, ld, vocab, cs_chunk(vocab), temperature, top_k, top_p,
+                     penalty, seen_mask, seen_rows, seed, offset, out);
+        return launch_status();
+    }
     mstar_launch((sample_kernel), dim3(rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, 
         logits, ld, vocab, temperature, top_k, top_p, penalty, seen_mask, seen_rows, seed, offset,
         out);
