@@ -452,6 +452,47 @@ def test_sample_is_the_inverse_cdf_of_the_plain_distribution(opts):
     assert draw(logits, 0.8, [99] * rows, offsets, **opts).tolist() != got
 
 
+def test_sample_at_the_size_of_a_real_vocabulary():
+    """156,940 logits a row, every option at once (the reference's defaults are a
+    temperature, top-p and a repetition penalty): the kept set and the draw follow the
+    plain distribution; rows of one batch with different options do not disturb each other."""
+    from mstar_b200 import ops
+
+    vocab, rows = 156940, 6
+    logits = rnd(rows, vocab, seed=9, scale=3.0)
+    seen = torch.zeros(rows, vocab, dtype=torch.uint8, device=DEV)
+    seen[:, ::7] = 1
+    temp = torch.tensor([0.6, 0.6, 1.3, 0.6, 0.0, 0.9], device=DEV)
+    top_k = torch.tensor([0, 50, 0, 200, 0, 1], dtype=torch.int32, device=DEV)
+    top_p = torch.tensor([0.8, 1.0, 0.95, 0.5, 1.0, 1.0], device=DEV)
+    pen = torch.tensor([1.3, 1.0, 1.3, 1.1, 1.3, 1.0], device=DEV)
+    srows = torch.arange(rows, dtype=torch.int32, device=DEV)
+    seeds = torch.arange(100, 100 + rows, dtype=torch.int64, device=DEV)
+    offs = torch.arange(rows, dtype=torch.int64, device=DEV)
+    before = seen.clone()
+    got = ops.sample(logits, temp, top_k=top_k, top_p=top_p, penalty=pen, seen_mask=seen,
+                     seen_rows=srows, seed=seeds, offset=offs).tolist()
+    for r, tok in enumerate(got):
+        x = logits[r].cpu()
+        if temp[r] == 0:
+            pl = P.plain_sampling_distribution(x, 1.0, penalty=float(pen[r]), seen=before[r].cpu())
+            assert tok == int(pl.argmax())
+            continue
+        p = P.plain_sampling_distribution(x, float(temp[r]), top_k=int(top_k[r]),
+                                          top_p=float(top_p[r]), penalty=float(pen[r]),
+                                          seen=before[r].cpu())
+        assert p[tok] > 0, f"row {r}: token {tok} is outside the kept set"
+        cdf = torch.cumsum(p, 0)
+        u = P.plain_uniform(100 + r, r)
+        lo = cdf[tok - 1].item() if tok else 0.0
+        assert lo - 1e-4 <= u <= cdf[tok].item() + 1e-4, (r, tok, u)
+        assert seen[r, tok] == 1
+    assert int(seen.sum() - before.sum()) <= rows
+    again = ops.sample(logits, temp, top_k=top_k, top_p=top_p, penalty=pen, seen_mask=before,
+                       seen_rows=srows, seed=seeds, offset=offs).tolist()
+    assert again == got
+
+
 def test_sample_frequencies_follow_the_distribution():
     vocab, rows = 50, 4096
     logits = rnd(1, vocab, seed=8).repeat(rows, 1).contiguous()
