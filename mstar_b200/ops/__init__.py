@@ -2,8 +2,10 @@
 
 Each function validates shapes and dtypes, then launches a kernel from
 ``csrc/`` on the current CUDA stream.  Tensors must live on the GPU; nothing
-here computes on the CPU.  Matrix products in bfloat16 use the library GEMM
-(cuBLAS through ``torch.mm``), as the reference does for every linear layer
+here computes on the CPU.  Matrix products in bfloat16: this package's
+weight-streaming kernels for up to 16 rows, its tcgen05 kernels for the LM head and
+for gate/up at prompt size, and the library GEMM (cuBLAS through ``torch.mm``)
+elsewhere, as the reference uses for every linear layer
 (mstar/model/components/distributed/linear.py:101, 412); the float32 product
 is this package's own true-32-bit kernel.
 """
