@@ -160,8 +160,75 @@ class RunningMeanMixer:
         return out
 
 
+@dataclass(frozen=True)
+class TopOneExpertsSpec:
+    """Toy feed-forward with routing: a float router picks one of `experts` small
+    relu(x W1) W2 experts per token; its output is weighted by the router's softmax."""
+    kind: str = "toy_top1_experts"
+    hidden_size: int = 0
+    expert_size: int = 0
+    experts: int = 0
+
+
+class TopOneExperts:
+    @classmethod
+    def param_specs(cls, spec):
+        from mstar_b200.weights.names import ParamSpec
+        return {"router.weight": ParamSpec((spec.experts, spec.hidden_size)),
+                "w1.weight": ParamSpec((spec.experts * spec.expert_size, spec.hidden_size)),
+                "w2.weight": ParamSpec((spec.experts * spec.hidden_size, spec.expert_size))}
+
+    def __init__(self, spec, params, runtime):
+        self.spec = spec
+        self.router, self.w1, self.w2 = (params[k] for k in ("router.weight", "w1.weight",
+                                                             "w2.weight"))
+
+    def forward(self, x, ctx):
+        s = self.spec
+        scores = torch.softmax(x.float() @ self.router.float().T, dim=-1)   # router in float
+        weight, expert = scores.max(dim=-1)
+        out = torch.zeros_like(x)
+        for e in range(s.experts):
+            rows = (expert == e).nonzero().flatten()
+            if rows.numel() == 0:
+                continue
+            w1 = self.w1[e * s.expert_size:(e + 1) * s.expert_size].float()
+            w2 = self.w2[e * s.hidden_size:(e + 1) * s.hidden_size].float()
+            y = torch.relu(x[rows].float() @ w1.T) @ w2.T
+            out[rows] = (weight[rows, None] * y).to(x.dtype)
+        return out
+
+
+@dataclass(frozen=True)
+class QueryGrowthSpec:
+    """Toy position encoding: no rotation; the query of position p is scaled by
+    1 + rate * p (keys and values are written as they are)."""
+    kind: str = "toy_query_growth"
+    head_dim: int = 0
+    rate: float = 0.0
+
+
+class QueryGrowth:
+    @classmethod
+    def param_specs(cls, spec):
+        return {}
+
+    def __init__(self, spec, params, runtime):
+        self.spec = spec
+
+    def apply(self, qkv, ctx, kv_cache, block_table, page_size, num_heads, num_kv_heads):
+        from mstar_b200 import ops
+        nq = num_heads * self.spec.head_dim
+        grow = 1.0 + self.spec.rate * ctx.positions.float()
+        qkv[:, :nq] = (qkv[:, :nq].float() * grow[:, None]).to(qkv.dtype)
+        ops.rope_kv_write(qkv, ctx.positions, ctx.cache_pos, ctx.token_req, block_table, None,
+                          kv_cache, num_heads, num_kv_heads, self.spec.head_dim, 0, False,
+                          page_size)
+
+
 class ToyConfig:
     architecture = "ToyMixedForCausalLM"
+    EXPERTS, EXPERT_SIZE, RATE = 3, 40, 0.02
     H, NH, NKV, HD, INTER, VOCAB, WINDOW, EPS = 64, 4, 2, 16, 96, 128, 8, 1e-5
 
     def to_dict(self):
@@ -185,12 +252,20 @@ class ToyConfig:
             return AttentionSpec(hidden_size=self.H, num_heads=self.NH, num_kv_heads=self.NKV,
                                  head_dim=self.HD, position=pos, **kw)
 
+        routed = TopOneExpertsSpec(hidden_size=self.H, expert_size=self.EXPERT_SIZE,
+                                   experts=self.EXPERTS)
+        grown = AttentionSpec(hidden_size=self.H, num_heads=self.NH, num_kv_heads=self.NKV,
+                              head_dim=self.HD,
+                              position=QueryGrowthSpec(head_dim=self.HD, rate=self.RATE))
         blocks = [BlockSpec("prenorm", attn(), ffn, norm, norm),
                   BlockSpec("prenorm", RunningMeanSpec(hidden_size=self.H), ffn, norm, norm),
                   BlockSpec("prenorm", attn(shares_kv=True), ffn, norm, norm),
-                  BlockSpec("prenorm", attn(window=self.WINDOW), ffn, norm, norm)]
-        # block 2 reads the cache block 0 wrote; block 1 runs twice, with a state each time
-        order = [RunEntry(0, 0), RunEntry(1, 1), RunEntry(2, 0), RunEntry(3, 2), RunEntry(1, 3)]
+                  BlockSpec("prenorm", attn(window=self.WINDOW), ffn, norm, norm),
+                  BlockSpec("prenorm", grown, routed, norm, norm)]
+        # block 2 reads the cache block 0 wrote; block 1 runs twice, with a state each time;
+        # block 4 has a position encoding and a routed feed-forward of the test's own
+        order = [RunEntry(0, 0), RunEntry(1, 1), RunEntry(2, 0), RunEntry(3, 2), RunEntry(1, 3),
+                 RunEntry(4, 4)]
         return ModelLayout(vocab_size=self.VOCAB, hidden_size=self.H, blocks=blocks, order=order,
                            final_norm=norm, tie_word_embeddings=True)
 
@@ -205,8 +280,10 @@ def toy_checkpoint_map(config, layout):
                          optional=frozenset({"toy.head.weight"}))
 
 
-def toy_plain_logits(w, cfg: ToyConfig, ids):
-    """Whole-sequence plain forward of the toy model, from the plain part functions."""
+def toy_plain_logits(w, cfg: ToyConfig, ids, margins=None):
+    """Whole-sequence plain forward of the toy model, from the plain part functions.
+    ``margins``: a list that receives, per token, the gap between the router's two largest
+    logits in the routed feed-forward (a choice inside rounding noise is not a fault)."""
     T = len(ids)
     pos = torch.arange(T)
     rope_cfg = dict(head_dim=cfg.HD, rope_theta=10000.0, hidden_size=cfg.H,
@@ -218,7 +295,7 @@ def toy_plain_logits(w, cfg: ToyConfig, ids):
     def heads(x, mat, n):
         return (x @ mat.double().T).view(T, n, cfg.HD)
 
-    for block, cache in ((0, 0), (1, 1), (2, 0), (3, 2), (1, 3)):
+    for block, cache in ((0, 0), (1, 1), (2, 0), (3, 2), (1, 3), (4, 4)):
         p = f"toy.blocks.{block}"
         x = P.plain_rms_norm(h, w[f"{p}.norm1.weight"], cfg.EPS)
         if block == 1:
@@ -232,14 +309,33 @@ def toy_plain_logits(w, cfg: ToyConfig, ids):
             else:
                 qkv = w[f"{p}.mixer.qkv.weight"]
                 nk = cfg.NKV * cfg.HD
-                q = P.plain_apply_rope(heads(x, qkv[:nq], cfg.NH), pos, inv)
-                k = P.plain_apply_rope(heads(x, qkv[nq:nq + nk], cfg.NKV), pos, inv)
+                if block == 4:          # the toy position encoding: queries grow with p
+                    q = heads(x, qkv[:nq], cfg.NH) * (1 + cfg.RATE * pos.double())[:, None, None]
+                    k = heads(x, qkv[nq:nq + nk], cfg.NKV)
+                else:
+                    q = P.plain_apply_rope(heads(x, qkv[:nq], cfg.NH), pos, inv)
+                    k = P.plain_apply_rope(heads(x, qkv[nq:nq + nk], cfg.NKV), pos, inv)
                 v = heads(x, qkv[nq + nk:], cfg.NKV)
                 kv_of_cache[cache] = (k, v)
             att = P.plain_attention(q, k, v, window=cfg.WINDOW if block == 3 else None)
             a = att.reshape(T, nq) @ w[f"{p}.mixer.o.weight"].double().T
         h = h + a
         y = P.plain_rms_norm(h, w[f"{p}.norm2.weight"], cfg.EPS)
+        if block == 4:                  # the toy routed feed-forward
+            router_logits = y @ w[f"{p}.ffn.router.weight"].double().T
+            scores = torch.softmax(router_logits, dim=-1)
+            weight, expert = scores.max(dim=-1)
+            if margins is not None:
+                best2 = torch.topk(router_logits, 2, dim=-1).values
+                margins.extend((best2[:, 0] - best2[:, 1]).tolist())
+            m = torch.zeros_like(y)
+            for t in range(T):
+                e = int(expert[t])
+                w1 = w[f"{p}.ffn.w1.weight"].double()[e * cfg.EXPERT_SIZE:(e + 1) * cfg.EXPERT_SIZE]
+                w2 = w[f"{p}.ffn.w2.weight"].double()[e * cfg.H:(e + 1) * cfg.H]
+                m[t] = weight[t] * (torch.relu(y[t] @ w1.T) @ w2.T)
+            h = h + m
+            continue
         gu = w[f"{p}.ffn.gate_up.weight"]
         h = h + P.plain_swiglu(y, gu[:cfg.INTER], gu[cfg.INTER:], w[f"{p}.ffn.down.weight"])
     return P.plain_rms_norm(h, w["toy.final_norm.weight"], cfg.EPS) @ w["toy.embed.weight"].double().T
@@ -251,10 +347,14 @@ def toy_registered():
     from mstar_b200.parts import register_part, unregister_part
 
     register_part("mixer", "toy_running_mean", RunningMeanMixer)
+    register_part("ffn", "toy_top1_experts", TopOneExperts)
+    register_part("position", "toy_query_growth", QueryGrowth)
     register_architecture("ToyMixedForCausalLM", ToyConfig, toy_checkpoint_map)
     yield
     unregister_architecture("ToyMixedForCausalLM")
     unregister_part("mixer", "toy_running_mean")
+    unregister_part("ffn", "toy_top1_experts")
+    unregister_part("position", "toy_query_growth")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -275,20 +375,31 @@ def test_toy_architecture_is_registered_built_and_stepped(toy_registered, dtype)
             t = 1 + 0.1 * torch.randn(spec.shape, generator=g)
         else:
             t = 0.05 * torch.randn(spec.shape, generator=g)
+            if ".ffn.router" in name:
+                t *= 40            # a router that decides: few tokens near a tie
             if ".mixer.q" in name:
                 t[:cfg.NH * cfg.HD + (0 if name.endswith("q.weight") else cfg.NKV * cfg.HD)] *= 3
         tensors["toy." + name] = t.to(torch.bfloat16)
     model = load_model(None, dtype=dtype, device=DEV, config=cfg, tensors=tensors)
     # two page groups (all keys / window of 8) and two state caches
     windows, group_of = plan_groups(model.cache_needs)
-    assert windows == [None, 8] and group_of == [0, None, 1, None]
-    assert [n.state is not None for n in model.cache_needs] == [False, True, False, True]
+    assert windows == [None, 8] and group_of == [0, None, 1, None, 0]
+    assert [n.state is not None for n in model.cache_needs] == [False, True, False, True, False]
 
     reqs = {f"t{i}": H.request_tokens(cfg.VOCAB, n, seed=40 + i) for i, n in enumerate([3, 21, 50, 77])}
-    want = {}
+    # the routed feed-forward sits in the last block, so a token whose two best experts are
+    # within rounding noise of each other differs in its own logits only: those are left out
+    want, close = {}, 0
+    noise = 1e-4 if dtype == "float32" else 0.3       # of router logits as large as 20
     for rid, toks in reqs.items():
-        logits = toy_plain_logits(tensors, cfg, toks)
-        want.update({(rid, i): logits[i] for i in range(len(toks))})
+        margins = []
+        logits = toy_plain_logits(tensors, cfg, toks, margins)
+        for i in range(len(toks)):
+            if margins[i] < noise:
+                close += 1
+            else:
+                want[(rid, i)] = logits[i]
+    assert close <= 0.1 * sum(len(t) for t in reqs.values())
     for steps, what in ((H.whole(reqs), "toy whole"), (H.portions(reqs), "toy portions"),
                         (H.prefill_then_decode(reqs, 32), "toy prefill + decode"),
                         (H.mixed(reqs, seed=2), "toy mixed")):
@@ -296,7 +407,7 @@ def test_toy_architecture_is_registered_built_and_stepped(toy_registered, dtype)
         stepper = make_stepper(model, page_size=4, num_pages=pages, num_slots=4)
         assert stepper.storage.state_bytes_per_request() == 2 * cfg.H * 4
         got = H.run_steps_in_process(stepper, steps)
-        H.compare(got, want, dtype, what)
+        H.compare({k: v for k, v in got.items() if k in want}, want, dtype, what)
         mgr = stepper.manager
         assert mgr.check() == 0 and mgr.free_pages(0) == pages and mgr.free_pages(1) == pages
 
