@@ -246,6 +246,7 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_attention_kernel(DecodeArg
 #define MERGE_MAX_SPLITS 256
 template <int HD>
 __global__ void decode_merge_kernel(DecodeArgs a) {
+    pdl_launch_dependents();   // a short kernel: the long one after it may be scheduled now
     pdl_wait();
     __shared__ float wgt[MERGE_MAX_SPLITS];
     const int head = blockIdx.x, t = blockIdx.y;

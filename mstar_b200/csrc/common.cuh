@@ -100,8 +100,10 @@ static inline int launch_status() { return (int)cudaGetLastError(); }
 // the ramp of CTA scheduling out of the gaps between the many short kernels of a decode step
 // (measured: 2.35 -> 2.22 ms per step at batch 8).  A successor is scheduled once every CTA
 // of the running kernel has called pdl_launch_dependents() or has ended.  The long kernels
-// call it where their last weights or keys have arrived, before their reductions; the short
-// ones leave it to their end.  Calling it at the top of every kernel lets waiting successors
+// call it where their last weights or keys have arrived, before their reductions; the rotary
+// and the split-merge kernel, short ones before long ones, call it at their top (2.16 ->
+// 2.12 ms); the norm kernel leaves it to its end (calling it at its top lets the product
+// after it crowd in on the product before it: 2.37 ms).  Calling it at the top of every kernel lets waiting successors
 // pile up on the SMs and was slower than no overlap at all (2.93 ms).  Every kernel calls
 // pdl_wait() before it touches global memory.  MSTAR_PDL=0 launches everything with full
 // serialization (the calls in the kernels are then no-ops).

@@ -250,6 +250,7 @@ __global__ void rope_kv_write_kernel(A* __restrict__ qkv, const int* __restrict_
                                      const int* __restrict__ block_table,
                                      const float* __restrict__ inv_freq, A* __restrict__ kv_cache,
                                      RopeArgs a) {
+    pdl_launch_dependents();   // a short kernel: the long one after it may be scheduled now
     pdl_wait();
     // grid (token, slice): the items of a token (rotated pairs of q and k, unrotated tail
     // of k, values) are spread over all threads of its slices, one or a few each, so that
@@ -316,6 +317,7 @@ __global__ void rope_kv_write_vec_kernel(A* __restrict__ qkv, const int* __restr
                                          const int* __restrict__ block_table,
                                          const float* __restrict__ inv_freq,
                                          A* __restrict__ kv_cache, RopeArgs a) {
+    pdl_launch_dependents();   // a short kernel: the long one after it may be scheduled now
     pdl_wait();
     const int t = blockIdx.x;
     const int hd = a.hd, half = a.rotary_dim / 2;
