@@ -638,6 +638,7 @@ decode_attention_ring_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeA
                 }
             }
         }
+        pdl_launch_dependents();          // the last keys are asked for
         return;
     }
 

@@ -124,6 +124,7 @@ smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
                               full + 8 * st);
             }
         }
+        pdl_launch_dependents();          // the last weights are asked for
         return;
     }
 
