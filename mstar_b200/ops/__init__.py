@@ -265,6 +265,8 @@ def paged_decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
         if code == -1:
             raise KernelError("TMA decode attention refuses this shape")
         check(code, "paged_decode_attention_tma")
+        if splits > 1:
+            lib.add_launches(1)                 # the merge kernel
         return
     code = lib.get("attention_decode").mstar_paged_decode_attention_bf16(
         q.data_ptr(), q_stride, out.data_ptr(), kv_cache.data_ptr(), block_table.data_ptr(),
@@ -276,6 +278,8 @@ def paged_decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
                           f"head_dim={head_dim} (head_dim in {FAST_ATTENTION_HEAD_DIMS}, at most "
                           "16 query heads per kv head)")
     check(code, "paged_decode_attention")
+    if splits > 1:
+        lib.add_launches(1)                     # the merge kernel
 
 
 def prefill_attention_kernel(has_kv_map: bool, head_dim: int, page_size: int) -> str:
