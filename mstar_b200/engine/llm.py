@@ -119,6 +119,15 @@ class LLM:
         self.scheduler.add(Request(request_id, prompt, params))
         return request_id
 
+    def abort(self, request_id: Hashable) -> bool:
+        """Give a request up, waiting or running: its pages and its slot return at once (a
+        step under way that still computes for it is ordered before whatever uses them
+        next, and its token is dropped when it arrives).  The request is handed back by a
+        later ``step`` with finish reason "abort".  False if it is not known or has
+        finished (the reference: mstar/conductor/conductor.py:764-792, removal deferred
+        while a step is in flight, mstar/worker/worker.py:451-463)."""
+        return self.scheduler.abort(request_id)
+
     def has_unfinished(self) -> bool:
         return (self.scheduler.has_work() or self._inflight is not None
                 or self._reported < len(self.scheduler.finished))

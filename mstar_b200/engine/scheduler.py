@@ -342,6 +342,8 @@ class Scheduler:
                 continue        # stopped a step ago: this token was computed in vain
             tok = int(sampled[r.request_id])
             r.output[where] = tok
+            if r.finish_reason == "abort":
+                continue                       # given up while this step was under way
             if (not r.params.ignore_eos) and tok in self.stop_token_ids:
                 del r.output[where + 1:]       # the place the step after took, if any
                 if r.status == "finished":

@@ -187,3 +187,27 @@ def test_stop_and_length_through_the_pipelined_entry_point(model_folders, tmp_pa
         assert g.finish_reason == ("stop" if stop in r.token_ids else "length")
     assert llm.pipelined_steps > 0
     assert llm.stepper.manager.num_requests() == 0 and llm.stepper.manager.check() == 0
+
+
+def test_abort_through_the_entry_point(model_folders):
+    from mstar_b200 import LLM, SamplingParams
+
+    folder, raw, tensors = model_folders["tiny_a"]
+    prompts = [H.request_tokens(raw["vocab_size"], n, seed=700 + n) for n in (5, 8, 11)]
+    params = SamplingParams(temperature=0.0, max_output_tokens=10, ignore_eos=True)
+    ref = LLM(folder, dtype="float32", page_size=4, max_num_pages=64).generate(prompts, params)
+    llm = LLM(folder, dtype="float32", page_size=4, max_num_pages=64)
+    ids = [llm.add_request(p, params) for p in prompts]
+    done = {}
+    for _ in range(4):                                  # a few steps, one always under way
+        for r in llm.step():
+            done[r.request_id] = r
+    assert llm.abort(ids[1]) and not llm.abort("nobody")
+    while llm.has_unfinished():
+        for r in llm.step():
+            done[r.request_id] = r
+    assert done[ids[1]].finish_reason == "abort" and None not in done[ids[1]].output
+    assert done[ids[1]].output == ref[1].token_ids[:len(done[ids[1]].output)]
+    for k in (0, 2):                                    # the others are not disturbed
+        assert done[ids[k]].output == ref[k].token_ids and done[ids[k]].finish_reason == "length"
+    assert llm.stepper.manager.num_requests() == 0 and llm.stepper.manager.check() == 0

@@ -324,3 +324,19 @@ def test_a_preempted_request_keeps_the_place_of_its_token_in_flight():
         inflight = plan
     assert victim is not None and None not in victim.output     # the value arrived all the same
     assert victim.status == "waiting" and victim.num_computed == 0
+
+
+def test_abort_while_a_step_is_under_way():
+    cm, sch = make(budget=64)
+    sch.add(req("a", 4, max_out=10))
+    sch.add(req("b", 4, max_out=10))
+    p0, _ = launch_then_read(cm, sch, None, lambda r: 7)
+    p1, _ = launch_then_read(cm, sch, p0, lambda r: 7)        # decode 1 under way
+    a = p1.entries[0].request
+    assert sch.abort("a") and a.status == "finished" and a.finish_reason == "abort"
+    assert cm.num_requests() == 1                             # its pages and slot are back
+    p2, done = launch_then_read(cm, sch, p1, lambda r: 99 if r.request_id == "a" else 7)
+    # a's token (a stop token, even) arrives and is dropped
+    assert not done and a.finish_reason == "abort" and None not in a.output
+    assert [e.request.request_id for e in p2.entries] == ["b"]
+    assert not sch.abort("a") and not sch.abort("nobody")
