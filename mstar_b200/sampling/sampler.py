@@ -10,6 +10,7 @@ from __future__ import annotations
 
 from typing import Hashable, Sequence
 
+import numpy as np
 import torch
 
 from .. import ops
@@ -26,6 +27,9 @@ class Sampler:
         self._offset: dict = {}
         self._slot: dict = {}
         self._seen = None  # uint8 [num_slots, vocab], made when a request first needs it
+        self._pinned = [None] * 4
+        self._events = [None] * 4
+        self._turn = 0
 
     def add_request(self, request: Hashable, params: SamplingParams, slot: int,
                     generated: Sequence[int] = ()) -> None:
@@ -64,22 +68,51 @@ class Sampler:
         if all(p.temperature == 0 and p.repetition_penalty == 1.0 for p in ps):
             tokens = ops.argmax(logits)
         else:
-            f32 = torch.tensor([[p.temperature for p in ps], [p.top_p for p in ps],
-                                [p.repetition_penalty for p in ps]], dtype=torch.float32)
-            i32 = torch.tensor([[p.top_k for p in ps],
-                                [self._slot[r] if p.repetition_penalty != 1.0 else -1
-                                 for r, p in zip(requests, ps)]], dtype=torch.int32)
-            i64 = torch.tensor([[self._seed[r] for r in requests],
-                                [self._offset[r] for r in requests]], dtype=torch.int64)
-            f32, i32, i64 = (t.to(self.device, non_blocking=True) for t in (f32, i32, i64))
+            # the rows' options in one pinned buffer and one copy that nothing waits for (a
+            # copy from pageable memory would first wait for the step just launched)
+            n = len(ps)
+            host = self._staging(36 * n)
+            raw = host.numpy()
+            raw[0:8 * n].view(np.int64)[:] = [self._seed[r] for r in requests]
+            raw[8 * n:16 * n].view(np.int64)[:] = [self._offset[r] for r in requests]
+            raw[16 * n:20 * n].view(np.float32)[:] = [p.temperature for p in ps]
+            raw[20 * n:24 * n].view(np.float32)[:] = [p.top_p for p in ps]
+            raw[24 * n:28 * n].view(np.float32)[:] = [p.repetition_penalty for p in ps]
+            raw[28 * n:32 * n].view(np.int32)[:] = [p.top_k for p in ps]
+            raw[32 * n:36 * n].view(np.int32)[:] = [
+                self._slot[r] if p.repetition_penalty != 1.0 else -1 for r, p in zip(requests, ps)]
+            dev = torch.empty(36 * n, dtype=torch.uint8, device=self.device)
+            dev.copy_(host[:36 * n], non_blocking=True)
+            self._copied()
+            seed, offset = dev[0:8 * n].view(torch.int64), dev[8 * n:16 * n].view(torch.int64)
+            temperature = dev[16 * n:20 * n].view(torch.float32)
+            top_p, penalty = (dev[20 * n:24 * n].view(torch.float32),
+                              dev[24 * n:28 * n].view(torch.float32))
+            top_k, seen_rows = (dev[28 * n:32 * n].view(torch.int32),
+                                dev[32 * n:36 * n].view(torch.int32))
             any_k = any(p.top_k > 0 for p in ps)
             any_p = any(p.top_p < 1.0 for p in ps)
             any_pen = self._seen is not None and any(p.repetition_penalty != 1.0 for p in ps)
             tokens = ops.sample(
-                logits, f32[0], top_k=i32[0] if any_k else None,
-                top_p=f32[1] if any_p else None, penalty=f32[2] if any_pen else None,
+                logits, temperature, top_k=top_k if any_k else None,
+                top_p=top_p if any_p else None, penalty=penalty if any_pen else None,
                 seen_mask=self._seen if any_pen else None,
-                seen_rows=i32[1] if any_pen else None, seed=i64[0], offset=i64[1])
+                seen_rows=seen_rows if any_pen else None, seed=seed, offset=offset)
         for r in requests:
             self._offset[r] += 1
         return tokens
+
+    # -- pinned staging: a ring, each buffer guarded by the event after its last copy
+    def _staging(self, nbytes: int) -> torch.Tensor:
+        self._turn = (self._turn + 1) % len(self._pinned)
+        if self._events[self._turn] is not None:
+            self._events[self._turn].synchronize()
+        if self._pinned[self._turn] is None or self._pinned[self._turn].numel() < nbytes:
+            self._pinned[self._turn] = torch.empty(max(nbytes, 36 * 64), dtype=torch.uint8,
+                                                   pin_memory=True)
+        return self._pinned[self._turn]
+
+    def _copied(self) -> None:
+        event = torch.cuda.Event()
+        event.record()
+        self._events[self._turn] = event
