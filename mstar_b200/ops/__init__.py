@@ -481,6 +481,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     operand runs in true float32.  ``static_weights`` promises that no kernel earlier on
     the stream writes ``w`` (model parameters): the weight-streaming kernel then starts
     its copies while the kernel before it is still draining."""
+    bf16 = x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda and w.is_cuda
+    m, n = x.shape[0], w.shape[0]
+    if (bf16 and out_dtype is None and m > SMALL_M and n < 8192
+            and os.environ.get("MSTAR_GEMM") is None):
+        # the common case of a prompt portion on a narrow projection, decided first: this
+        # function runs a hundred times in a step that the host has to get launched
+        return torch.mm(x, w.t())
     _need_cuda(x, w)
     out_dtype = out_dtype or x.dtype
     if out_dtype in (torch.bfloat16, torch.float32) and _smallm_ok(x, w):
