@@ -37,6 +37,14 @@ ORPHEUS_3B = dict(
     rms_norm_eps=1e-5, max_position_embeddings=131072, hidden_act="silu",
     torch_dtype="bfloat16",
 )
+# Further sizes of the same architecture (--sizes): Llama 3.2 1B and Llama 3.1 8B.
+LLAMA_1B = dict(ORPHEUS_3B, num_hidden_layers=16, hidden_size=2048, num_attention_heads=32,
+                head_dim=64, vocab_size=128256)
+LLAMA_8B = dict(ORPHEUS_3B, num_hidden_layers=32, hidden_size=4096, num_attention_heads=32,
+                intermediate_size=14336, vocab_size=128256, tie_word_embeddings=False,
+                rope_scaling=dict(ORPHEUS_3B["rope_scaling"], factor=8.0))
+SIZES = {"orpheus-3b": ("Orpheus 3B / Llama 3.2 3B", ORPHEUS_3B),
+         "llama-1b": ("Llama 3.2 1B", LLAMA_1B), "llama-8b": ("Llama 3.1 8B", LLAMA_8B)}
 PROMPT_LEN = 2048
 CONTEXT = 4096
 PAGE_SIZE = 64
@@ -265,7 +273,7 @@ def _time_graph(fn, reps: int = 20, rounds: int = 5) -> float:
     return statistics.median(times)
 
 
-def kernel_bench(name: str, batch: int, ctx: int, small: bool) -> int:
+def kernel_bench(name: str, batch: int, ctx: int, small: bool, cfg: dict) -> int:
     """Time one kernel alone at the benchmark model's shapes: ``--kernel NAME``.  Inputs
     rotate over copies larger than L2 where the kernel is memory-bound.  ``--small``
     shrinks the case for profiler captures (still larger than L2 where it matters)."""
@@ -273,7 +281,6 @@ def kernel_bench(name: str, batch: int, ctx: int, small: bool) -> int:
 
     from mstar_b200 import ops
 
-    cfg = ORPHEUS_3B
     nq, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
     dev = "cuda:0"
@@ -386,9 +393,12 @@ def main() -> int:
                          "rope_kv_write) at --batch rows / requests and --ctx keys")
     ap.add_argument("--ctx", type=int, default=PROMPT_LEN)
     ap.add_argument("--small", action="store_true", help="a smaller case, for profiler captures")
+    ap.add_argument("--sizes", default="orpheus-3b", choices=sorted(SIZES),
+                    help="layer sizes; the default is the benchmark model")
     args = ap.parse_args()
+    model_name, sizes = SIZES[args.sizes]
     if args.kernel:
-        return kernel_bench(args.kernel, args.batch, args.ctx, args.small)
+        return kernel_bench(args.kernel, args.batch, args.ctx, args.small, sizes)
     if args.impl == "reference":
         return reference_arm()
     if args.gpus != 1:
@@ -401,7 +411,7 @@ def main() -> int:
     from mstar_b200.engine.step import make_stepper
     from mstar_b200.ops import lib
 
-    cfg = dict(ORPHEUS_3B)
+    cfg = dict(sizes)
     full_layers = cfg["num_hidden_layers"]
     if args.layers:
         cfg["num_hidden_layers"] = args.layers
@@ -430,21 +440,23 @@ def main() -> int:
     step_bytes = bytes_of_decode_step(cfg, model, head["kv_lens"])
     achieved = step_bytes / (head["ms_per_step"] / 1e3) / 1e9
     record = {
-        "metric": "decode tok/s at batch 8 (Orpheus 3B bf16, 2,048-token cached prompts)",
+        "metric": f"decode tok/s at batch {args.batch} ({model_name.split(' / ')[0]} bf16, "
+                  "2,048-token cached prompts)",
         "value": round(head["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": warmup, "ms_per_step": round(head["ms_per_step"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic token ids, random-init weights N(0, 0.02)",
         "config": {
-            "model": "Orpheus 3B / Llama 3.2 3B", "global_batch": args.batch,
+            "model": model_name, "global_batch": args.batch,
             "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "parallelism": "single GPU",
             "layers": cfg["num_hidden_layers"], "layers_of_model": full_layers,
             "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
             "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
             "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
-            "tied_embeddings": True, "rope": "theta 5e5, llama3 x32 (1, 4, 8192)",
+            "tied_embeddings": cfg["tie_word_embeddings"],
+            "rope": f"theta 5e5, llama3 x{cfg['rope_scaling']['factor']:g} (1, 4, 8192)",
             "rms_eps": cfg["rms_norm_eps"], "page_size": PAGE_SIZE,
-            "l2": "inputs larger than L2 (weights 6.6 GB per step)",
+            "l2": f"inputs larger than L2 (weights {model.parameter_bytes() / 1e9:.1f} GB per step)",
             "peaks": pk["source"]},
         "e2e": {"value": round(e2e["tokens_per_s"], 1), "unit": "tokens/s",
                 "h2d_bytes_per_step": e2e["h2d_bytes_per_step"],

@@ -2,7 +2,9 @@
 8 key/value heads of 128, feed-forward 8192, vocabulary 156,940, tied head, llama3 rotary
 scaling x32) with two layers, against the plain model: whole prompt, portions, and a
 mixed batch.  At these sizes the product path runs the kernels serving runs: the
-tcgen05 gate/up and LM-head products, the small-M products, the tensor-core attention."""
+tcgen05 gate/up and LM-head products, the small-M products, the tensor-core attention.
+The same at the layer sizes of Llama 3.2 1B (width 2048, 32 query heads of 64) and of
+Llama 3.1 8B (width 4096, feed-forward 14336, a head of its own, scaling x8)."""
 import pytest
 import torch
 
@@ -19,6 +21,13 @@ CFG = dict(
                   "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
     rms_norm_eps=1e-5, max_position_embeddings=131072, hidden_act="silu",
 )
+SIZES = {
+    "3b": CFG,
+    "1b": dict(CFG, hidden_size=2048, num_attention_heads=32, head_dim=64, vocab_size=128256),
+    "8b": dict(CFG, hidden_size=4096, num_attention_heads=32, intermediate_size=14336,
+               vocab_size=128256, tie_word_embeddings=False,
+               rope_scaling=dict(CFG["rope_scaling"], factor=8.0)),
+}
 LENGTHS = [150, 37]
 # Tolerances at this size, derived as for the tiny models (tests/helpers.py): the plain
 # model evaluated in float32 instead of float64 differs from itself by 2.9e-5 (max) and
@@ -27,15 +36,21 @@ LENGTHS = [150, 37]
 # rounded to bfloat16 at the places where the engine stores bfloat16 (normed rows, q, k,
 # v, attention output, projections, gate, up, their product) differs from float64 by
 # 0.18 (max) and 0.018 (mean) on these requests, logits being as large as 5.5; the
-# tolerance is 1.5 times that rounding noise.
-TOLS = {"float32": (1.3e-4, 1.3e-5), "bfloat16": (0.27, 0.027)}
+# tolerance is 1.5 times that rounding noise.  The other sizes by the same two rules
+# from their own noise: 1B 1.4e-5 / 1.5e-6 in float32 and 0.086 / 0.0105 in bfloat16,
+# 8B 2.7e-5 / 3.0e-6 and 0.20 / 0.020.
+TOLS = {"3b": {"float32": (1.3e-4, 1.3e-5), "bfloat16": (0.27, 0.027)},
+        "1b": {"float32": (6.2e-5, 6.9e-6), "bfloat16": (0.13, 0.0158)},
+        "8b": {"float32": (1.2e-4, 1.37e-5), "bfloat16": (0.305, 0.030)}}
 
 
-@pytest.fixture(scope="module")
-def big(tmp_path_factory):
+@pytest.fixture(scope="module", params=["3b", "1b", "8b"])
+def big(request):
     from mstar_b200.config.registry import config_from_dict
     from mstar_b200.weights.random_init import random_checkpoint
 
+    size = request.param
+    CFG = SIZES[size]
     cfg = config_from_dict(CFG)
     tensors = random_checkpoint(cfg, seed=3, std=0.02, device="cuda:0")
     for key in tensors:                       # sharper attention, as in the tiny models
@@ -45,14 +60,15 @@ def big(tmp_path_factory):
             for i, n in enumerate(LENGTHS)}
     cpu = {k: v.cpu() for k, v in tensors.items()}
     want = {}
-    head = cpu["model.embed_tokens.weight"].double()
+    head = cpu["model.embed_tokens.weight" if CFG["tie_word_embeddings"]
+               else "lm_head.weight"].double()
     for rid, toks in reqs.items():
         hidden = P.plain_hidden_states(cpu, CFG, toks)
         rows = sorted({0, 1, 15, 16, 17, len(toks) // 2, len(toks) - 2, len(toks) - 1})
         logits = hidden[rows] @ head.T
         want.update({(rid, r): logits[i] for i, r in enumerate(rows)})
     del head
-    return cfg, tensors, reqs, want
+    return size, cfg, tensors, reqs, want
 
 
 def only_wanted(steps, want):
@@ -71,17 +87,18 @@ def test_orpheus_sized_layers_match_the_plain_model(big, dtype):
     from mstar_b200.engine.model import load_model
     from mstar_b200.engine.step import make_stepper
 
-    cfg, tensors, reqs, want = big
+    size, cfg, tensors, reqs, want = big
+    tol, mean_tol = TOLS[size][dtype]
     model = load_model(None, dtype=dtype, device="cuda:0", config=cfg, tensors=tensors)
-    for steps, what in ((H.whole(reqs), "3B-sized layers, whole"),
-                        (H.portions(reqs, sizes=(64, 2, 30, 17)), "3B-sized layers, portions"),
-                        (H.mixed(reqs, seed=1, prompt_frac=0.8), "3B-sized layers, mixed")):
+    for steps, what in ((H.whole(reqs), f"{size}-sized layers, whole"),
+                        (H.portions(reqs, sizes=(64, 2, 30, 17)), f"{size}-sized layers, portions"),
+                        (H.mixed(reqs, seed=1, prompt_frac=0.8), f"{size}-sized layers, mixed")):
         steps = only_wanted(steps, want)
         pages = H.max_tokens_of(steps, 16) // 16
         stepper = make_stepper(model, page_size=16, num_pages=pages, num_slots=4)
         got = H.run_steps_in_process(stepper, steps)
         assert set(got) == set(want)
-        worst = H.compare(got, want, dtype, what, tol=TOLS[dtype][0], mean_tol=TOLS[dtype][1])
+        worst = H.compare(got, want, dtype, what, tol=tol, mean_tol=mean_tol)
         print(f"{what} [{dtype}]: worst abs error {worst:.3e}")
     del model
     torch.cuda.empty_cache()
