@@ -342,6 +342,29 @@ def kernel_bench(name: str, batch: int, ctx: int, small: bool, cfg: dict) -> int
         flops = 2.0 * batch * n * k
         out.update(ms=ms, n=n, k=k, gbs=nbytes / ms / 1e6,
                    frac_hbm=nbytes / ms / 1e6 / pk["hbm_gbs"], tflops=flops / ms / 1e9)
+    elif name == "qkv_rope":
+        # the decode form of the mixer's first product: product, rotation and cache write
+        n, k = (nq + 2 * nkv) * hd, H
+        copies = max(1, -(-(160 << 20) // (n * k * 2)))
+        ws = [rnd(n, k, scale=0.02) for _ in range(copies)]
+        x = rnd(batch, k)
+        pages_per = -(-ctx // PAGE_SIZE)
+        kv = rnd(batch * pages_per + 1, 2, nkv, PAGE_SIZE, hd)
+        table = torch.arange(batch * pages_per, dtype=torch.int32, device=dev).view(batch, -1)
+        pos = torch.full((batch,), ctx - 1, dtype=torch.int32, device=dev)
+        req = torch.arange(batch, dtype=torch.int32, device=dev)
+        inv = torch.rand(hd // 2, device=dev)
+        state = {"i": 0}
+
+        def fn():
+            w = ws[state["i"] % copies]
+            state["i"] += 1
+            return ops.qkv_rope_write(x, w, pos, pos, req, table, inv, kv, nq, nkv, hd, PAGE_SIZE,
+                                      static_weights=True)
+
+        ms = _time_graph(fn, reps=max(copies * 2, 8))
+        out.update(ms=ms, n=n, k=k, gbs=n * k * 2 / ms / 1e6,
+                   frac_hbm=n * k * 2 / ms / 1e6 / pk["hbm_gbs"])
     elif name in ("add_rmsnorm", "rope_kv_write"):
         rows = batch
         if name == "add_rmsnorm":
@@ -389,7 +412,7 @@ def main() -> int:
                     help="fewer layers than the model has (named in the record)")
     ap.add_argument("--kernel", default=None,
                     help="time one kernel alone (decode_attention, prefill_attention, gemm_qkv, "
-                         "gemm_o, gemm_gate_up, gemm_down, gemm_lm_head, add_rmsnorm, "
+                         "gemm_o, gemm_gate_up, gemm_down, gemm_lm_head, qkv_rope, add_rmsnorm, "
                          "rope_kv_write) at --batch rows / requests and --ctx keys")
     ap.add_argument("--ctx", type=int, default=PROMPT_LEN)
     ap.add_argument("--small", action="store_true", help="a smaller case, for profiler captures")

@@ -23,6 +23,15 @@
 // assigned to threads as in gemm_smallm.cu) and x from global memory (it is small and stays
 // in L1/L2), and are summed through shared memory at the end of a strip.
 //
+// A third form is the attention mixer's first product for decoded tokens: y = x Wqkv^T with
+// the rotary encoding of q and k and the write of k and v into their cache pages done where
+// the sums are made.  A strip then holds rows j .. j + 8 NT - 1 and hd/2 + the same of one
+// head, the two halves of 8 NT rotated pairs (the gated form's row layout with another
+// distance), so both partners of a pair meet in one thread; q leaves rotated, k and v go to
+// (page, slot) of the token's cache position and nowhere else.  Arithmetic as in the separate
+// kernel (elementwise.cu): sums rounded to bfloat16, angle = float(position) * inv_freq[j],
+// sincosf, rotation in float.
+//
 // Every mbarrier wait is bounded; a wait that runs out sets the error word (13 producer, 14
 // consumer) and the CTA leaves (the consumer warps together, after their next barrier).
 // The reference uses the library GEMM for these products
@@ -53,6 +62,22 @@ __device__ __forceinline__ void sb_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
+// the forms of the kernel; the last two have two 8 NT-row groups per strip
+#define SB_PLAIN 0
+#define SB_GATED 1
+#define SB_ROPE 2
+
+// what the rotary form needs beside the product's operands
+struct SbRope {
+    const int* positions;    // [M] position of a token for the angles
+    const int* cache_pos;    // [M] its place in its request's cache
+    const int* token_req;    // [M] row of the block table
+    const int* block_table;
+    const float* inv_freq;   // [hd / 2]
+    bf16* kv_cache;          // [pages, 2, nkv, page_size, hd]
+    int nq, nkv, hd, page_size, bt_stride;
+};
+
 __host__ __device__ constexpr int sb_rows(bool gated, int nt) { return (gated ? 16 : 8) * nt; }
 __host__ __device__ constexpr int sb_pitch() { return SB_KC * 2 + SB_PAD; }
 __host__ __device__ constexpr int sb_stage_bytes(bool gated, int nt) { return sb_rows(gated, nt) * sb_pitch(); }
@@ -62,11 +87,21 @@ __host__ __device__ constexpr int sb_smem(bool gated, int nt) {
 }
 
 // M16: tokens 8..15 exist (else the upper half of the MMA's rows is zero)
-template <bool GATED, bool M16, int NT, typename OutT>
-__global__ void __launch_bounds__(SB_THREADS, (GATED ? 2 : 4) / NT >= 1 ? (GATED ? 2 : 4) / NT : 1)
+// first output feature of a strip
+template <int MODE, int NT>
+__device__ __forceinline__ int sb_strip_n0(int strip, const SbRope& rp) {
+    if (MODE != SB_ROPE) return strip * 8 * NT;
+    const int per_head = (rp.hd / 2) / (8 * NT);
+    const int h = strip / per_head;
+    return h * rp.hd + (strip - h * per_head) * 8 * NT;
+}
+
+template <int MODE, bool M16, int NT, typename OutT>
+__global__ void __launch_bounds__(SB_THREADS, (MODE ? 2 : 4) / NT >= 1 ? (MODE ? 2 : 4) / NT : 1)
 smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* __restrict__ out, int M,
                    int n_out, int K, int ldx, int ldw, int ldo, int inter, int w_static,
-                   int* __restrict__ error_word) {
+                   int* __restrict__ error_word, SbRope rp) {
+    constexpr bool GATED = MODE != SB_PLAIN;          // two row groups per strip
     constexpr int STRIPS = GATED ? 2 : 1;
     constexpr int GROUPS = STRIPS * NT;               // 8-row groups of a stage
     constexpr int ROWS = 8 * GROUPS;
@@ -80,7 +115,7 @@ smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
     volatile int* failed = reinterpret_cast<volatile int*>(bars + 2 * SB_STAGES);
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int nstrips = (n_out + 8 * NT - 1) / (8 * NT);
+    const int nstrips = MODE == SB_ROPE ? n_out / (16 * NT) : (n_out + 8 * NT - 1) / (8 * NT);
     const int nch = (K + SB_KC - 1) / SB_KC;
 
     if (tid == 0) {
@@ -103,7 +138,7 @@ smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
         int c = 0;
         bool ok = true;
         for (int strip = blockIdx.x; strip < nstrips && ok; strip += gridDim.x) {
-            const int n0 = strip * 8 * NT;
+            const int n0 = sb_strip_n0<MODE, NT>(strip, rp);
             const int row = min(n0 + lane % (8 * NT), n_out - 1) + (lane / (8 * NT)) * inter;
             const bf16* src_row = W + (size_t)(lane < ROWS ? row : 0) * ldw;
             for (int ch = 0; ch < nch; ++ch, ++c) {
@@ -135,7 +170,7 @@ smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
     const bf16* xb = x + (size_t)min(g + 8, M - 1) * ldx + 8 * t;
     int c = 0;
     for (int strip = blockIdx.x; strip < nstrips; strip += gridDim.x) {
-        const int n0 = strip * 8 * NT;
+        const int n0 = sb_strip_n0<MODE, NT>(strip, rp);
         float acc[GROUPS][4];
 #pragma unroll
         for (int s = 0; s < GROUPS; ++s) acc[s][0] = acc[s][1] = acc[s][2] = acc[s][3] = 0.f;
@@ -209,8 +244,36 @@ smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
                         sum += red[(((s * NT + j) * SB_WARPS + w) * 16 + m) * 8 + r];
                     v[s] = sum;
                 }
+                if (MODE == SB_ROPE) {
+                    // n is the first partner's feature: head h, pair i of its hd/2
+                    const int hd = rp.hd, half = hd / 2;
+                    const int h = n0 / hd, i = n - h * hd;
+                    float y0 = __bfloat162float(__float2bfloat16_rn(v[0]));
+                    float y1 = __bfloat162float(__float2bfloat16_rn(v[STRIPS - 1]));
+                    if (h < rp.nq + rp.nkv) {
+                        float sn, cs;
+                        sincosf((float)rp.positions[m] * rp.inv_freq[i], &sn, &cs);
+                        const float x0 = y0, x1 = y1;
+                        y0 = x0 * cs - x1 * sn;
+                        y1 = x1 * cs + x0 * sn;
+                    }
+                    bf16* dst;
+                    if (h < rp.nq) {
+                        dst = reinterpret_cast<bf16*>(out) + (size_t)m * ldo + h * hd + i;
+                    } else {
+                        const int cp = rp.cache_pos[m];
+                        const int page = rp.block_table[(size_t)rp.token_req[m] * rp.bt_stride + cp / rp.page_size];
+                        const int slot = cp - (cp / rp.page_size) * rp.page_size;
+                        const int hk = h - rp.nq;        // key heads, then value heads: the page's order
+                        dst = rp.kv_cache + ((size_t)page * 2 * rp.nkv + hk) * rp.page_size * hd +
+                              (size_t)slot * hd + i;
+                    }
+                    dst[0] = __float2bfloat16_rn(y0);
+                    dst[half] = __float2bfloat16_rn(y1);
+                    continue;
+                }
                 float y = v[0];
-                if (GATED) {
+                if (MODE == SB_GATED) {
                     // gate and up are rounded to bfloat16 first, as the unfused path stores them
                     const float gate = __bfloat162float(__float2bfloat16_rn(v[0]));
                     const float up = __bfloat162float(__float2bfloat16_rn(v[STRIPS - 1]));
@@ -223,12 +286,13 @@ smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
     }
 }
 
-template <bool GATED, bool M16, int NT, typename OutT>
+template <int MODE, bool M16, int NT, typename OutT>
 static int launch_bulk_nt(const bf16* x, const bf16* W, OutT* out, int M, int n_out, int K, int ldx, int ldw,
-                          int ldo, int inter, int w_static, int* error_word, cudaStream_t s) {
+                          int ldo, int inter, int w_static, int* error_word, cudaStream_t s,
+                          const SbRope& rp = SbRope{}) {
     static int resident = 0;   // CTAs of this variant that fit on the GPU at once
-    auto kernel = smallm_bulk_kernel<GATED, M16, NT, OutT>;
-    constexpr int SMEM = sb_smem(GATED, NT);
+    auto kernel = smallm_bulk_kernel<MODE, M16, NT, OutT>;
+    constexpr int SMEM = sb_smem(MODE != SB_PLAIN, NT);
     if (resident == 0) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
         if (e != cudaSuccess) return (int)e;
@@ -245,10 +309,10 @@ static int launch_bulk_nt(const bf16* x, const bf16* W, OutT* out, int M, int n_
     }
     // as many CTAs as give every CTA the same number of strips (within one): 320 strips on
     // 296 resident CTAs would leave 272 of them waiting for the 24 that take a second strip
-    const int nstrips = (n_out + 8 * NT - 1) / (8 * NT);
+    const int nstrips = MODE == SB_ROPE ? n_out / (16 * NT) : (n_out + 8 * NT - 1) / (8 * NT);
     const int rounds = (nstrips + resident - 1) / resident;
     const int grid = (nstrips + rounds - 1) / rounds;
-    mstar_launch(kernel, dim3(grid), dim3(SB_THREADS), SMEM, s, x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word);
+    mstar_launch(kernel, dim3(grid), dim3(SB_THREADS), SMEM, s, x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word, rp);
     return launch_status();
 }
 
@@ -273,9 +337,9 @@ static int launch_bulk(const bf16* x, const bf16* W, OutT* out, int M, int n_out
     switch (pick_nt(n_out, GATED)) {
         case 4:
             if constexpr (!GATED)
-                return launch_bulk_nt<GATED, M16, 4, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word, s);
-        case 2: return launch_bulk_nt<GATED, M16, 2, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word, s);
-        default: return launch_bulk_nt<GATED, M16, 1, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word, s);
+                return launch_bulk_nt<GATED ? SB_GATED : SB_PLAIN, M16, 4, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word, s);
+        case 2: return launch_bulk_nt<GATED ? SB_GATED : SB_PLAIN, M16, 2, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word, s);
+        default: return launch_bulk_nt<GATED ? SB_GATED : SB_PLAIN, M16, 1, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word, s);
     }
 }
 
@@ -308,4 +372,31 @@ MSTAR_API int mstar_gemm_smallm_bulk_bf16(const void* x, const void* W, void* ou
     }
     if (M > 8) return launch_bulk<false, true, bf16>(xp, wp, (bf16*)out, M, N, K, ldx, ldw, ldo, 0, w_static, error_word, s);
     return launch_bulk<false, false, bf16>(xp, wp, (bf16*)out, M, N, K, ldx, ldw, ldo, 0, w_static, error_word, s);
+}
+
+// The attention mixer's first product for few tokens, with the rotary encoding and the cache
+// write where the sums are made: q_out[M, nq hd] = rotated (x Wq^T); rotated x Wk^T and
+// x Wv^T go to the tokens' cache slots.  W: [(nq + 2 nkv) hd, K], rows [q heads | k heads |
+// v heads]; split-half pairs over the whole head (rotary_dim == hd); kv_cache bfloat16
+// [pages, 2, nkv, page_size, hd].  Returns -1 when the shape is refused: M outside 1..16, hd no
+// multiple of 16, K no multiple of 32, strides or pointers unaligned, a null pointer.
+MSTAR_API int mstar_qkv_rope_write_bulk_bf16(const void* x, const void* W, void* q_out, int M, int K, int ldx,
+                                             int ldw, int ldo, const int* positions, const int* cache_pos,
+                                             const int* token_req, const int* block_table, int bt_stride,
+                                             const float* inv_freq, void* kv_cache, int nq, int nkv, int hd,
+                                             int page_size, int w_static, int* error_word, void* stream) {
+    if (M <= 0) return 0;
+    if (M > 16 || K <= 0 || K % 32 != 0 || ldx % 8 != 0 || ldw % 8 != 0 || error_word == nullptr) return -1;
+    if (((uintptr_t)x & 15) != 0 || ((uintptr_t)W & 15) != 0) return -1;
+    if (nq <= 0 || nkv <= 0 || hd <= 0 || hd % 16 != 0 || page_size <= 0) return -1;
+    if (!positions || !cache_pos || !token_req || !block_table || !inv_freq || !kv_cache || !q_out) return -1;
+    const SbRope rp{positions, cache_pos, token_req, block_table, inv_freq, (bf16*)kv_cache,
+                    nq, nkv, hd, page_size, bt_stride};
+    const int n_out = (nq + 2 * nkv) * hd;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (M > 8)
+        return launch_bulk_nt<SB_ROPE, true, 1, bf16>((const bf16*)x, (const bf16*)W, (bf16*)q_out, M, n_out, K,
+                                                      ldx, ldw, ldo, hd / 2, w_static, error_word, s, rp);
+    return launch_bulk_nt<SB_ROPE, false, 1, bf16>((const bf16*)x, (const bf16*)W, (bf16*)q_out, M, n_out, K,
+                                                   ldx, ldw, ldo, hd / 2, w_static, error_word, s, rp);
 }

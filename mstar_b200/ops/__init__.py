@@ -389,6 +389,40 @@ def _gemm_smallm(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, gated
     return out
 
 
+def qkv_rope_write(x: torch.Tensor, w_qkv: torch.Tensor, positions, cache_pos, token_req,
+                   block_table, inv_freq, kv_cache, num_heads: int, num_kv_heads: int,
+                   head_dim: int, page_size: int, static_weights: bool = False):
+    """For few bfloat16 rows (decoded tokens): the product x Wqkv^T, the split-half rotary
+    encoding of q and k over the whole head, and the write of k and v into their cache
+    pages, as one kernel.  Returns q [M, num_heads * head_dim], rotated; or None when this
+    form does not apply (more than ``SMALL_M`` rows, another dtype, no cache to write,
+    MSTAR_SMALLM=registers or MSTAR_FUSED_ROPE=0), and the caller runs ``linear`` and
+    ``rope_kv_write`` instead."""
+    if (kv_cache is None or inv_freq is None or not _smallm_ok(x, w_qkv)
+            or kv_cache.dtype != torch.bfloat16 or head_dim % 16
+            or inv_freq.numel() != head_dim // 2
+            or w_qkv.shape[0] != (num_heads + 2 * num_kv_heads) * head_dim
+            or os.environ.get("MSTAR_FUSED_ROPE") == "0"
+            or os.environ.get("MSTAR_SMALLM") == "registers"):
+        return None
+    _need_cuda(x, w_qkv, positions, cache_pos, token_req, block_table, inv_freq, kv_cache)
+    assert kv_cache.is_contiguous() and inv_freq.dtype == torch.float32
+    assert tuple(kv_cache.shape[1:]) == (2, num_kv_heads, page_size, head_dim)
+    m, k = x.shape
+    q = torch.empty((m, num_heads * head_dim), dtype=torch.bfloat16, device=x.device)
+    code = lib.get("gemm_smallm_bulk").mstar_qkv_rope_write_bulk_bf16(
+        x.data_ptr(), w_qkv.data_ptr(), q.data_ptr(), m, k, x.stride(0), w_qkv.stride(0),
+        q.stride(0), positions.data_ptr(), cache_pos.data_ptr(), token_req.data_ptr(),
+        block_table.data_ptr(), block_table.stride(0), inv_freq.data_ptr(), kv_cache.data_ptr(),
+        num_heads, num_kv_heads, head_dim, page_size, int(static_weights),
+        tcgen05_error_word(x.device).data_ptr(), _stream())
+    if code == -1:
+        raise KernelError(f"fused qkv/rotary product refuses M={m}, K={k}, heads={num_heads}, "
+                          f"kv_heads={num_kv_heads}, head_dim={head_dim}")
+    check(code, "qkv_rope_write")
+    return q
+
+
 _tc_error_words: dict = {}
 
 

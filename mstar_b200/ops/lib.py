@@ -54,6 +54,8 @@ _SIGNATURES = {
     },
     "gemm_smallm_bulk": {
         "mstar_gemm_smallm_bulk_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
+        "mstar_qkv_rope_write_bulk_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i,
+                                           _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp],
     },
     "gemm_tcgen05": {
         "mstar_gemm_tcgen05_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],

@@ -51,14 +51,22 @@ class Attention:
         self.w_in = params["q.weight"] if spec.shares_kv else params["qkv.weight"]
         self.w_out = params["o.weight"]
         self.position = build_part("position", spec.position, {}, runtime)
+        # a position part may offer the first product and its own work as one call
+        self._fused_projection = getattr(self.position, "project_and_apply", None)
         self.scale = spec.scale if spec.scale is not None else spec.head_dim ** -0.5
 
     def forward(self, x, ctx: StepContext, cache: LayerCache):
         s = self.spec
-        qkv = ops.linear(x, self.w_in, static_weights=True)
         write_heads = 0 if s.shares_kv else s.num_kv_heads
-        self.position.apply(qkv, ctx, None if s.shares_kv else cache.kv, cache.block_table,
-                            cache.page_size, s.num_heads, write_heads)
+        qkv = None
+        if self._fused_projection is not None and not s.shares_kv:
+            # queries only, [tokens, heads * head_dim]; keys and values are in the cache
+            qkv = self._fused_projection(x, self.w_in, ctx, cache.kv, cache.block_table,
+                                         cache.page_size, s.num_heads, write_heads)
+        if qkv is None:
+            qkv = ops.linear(x, self.w_in, static_weights=True)
+            self.position.apply(qkv, ctx, None if s.shares_kv else cache.kv, cache.block_table,
+                                cache.page_size, s.num_heads, write_heads)
         out = qkv.new_empty((ctx.num_tokens, s.num_heads * s.head_dim))
         self.attend(qkv, out, ctx, cache)
         return ops.linear(out, self.w_out, static_weights=True)

@@ -71,6 +71,19 @@ class RotaryEncoding:
                           self.inv_freq, kv_cache, num_heads, num_kv_heads, self.spec.head_dim,
                           self.spec.rotary_dim, self.spec.interleaved, page_size)
 
+    def project_and_apply(self, x, w_qkv, ctx, kv_cache, block_table, page_size, num_heads,
+                          num_kv_heads):
+        """Optional entry of a position part: the mixer's first product together with
+        ``apply``, where one kernel does both (a few decoded tokens, split-half pairs over
+        the whole head).  Returns the rotated queries [tokens, num_heads * head_dim], keys
+        and values being in the cache; or None, and the mixer takes the two steps."""
+        s = self.spec
+        if s.interleaved or s.rotary_dim != s.head_dim:
+            return None
+        return ops.qkv_rope_write(x, w_qkv, ctx.positions, ctx.cache_pos, ctx.token_req,
+                                  block_table, self.inv_freq, kv_cache, num_heads, num_kv_heads,
+                                  s.head_dim, page_size, static_weights=True)
+
 
 class NoPositionEncoding:
     """Position part of kind "none": keys and values are written as they are."""

@@ -551,6 +551,61 @@ def test_small_m_gemm(m, n, k, variant, monkeypatch):
     assert tc_clean() == 0                                  # no bounded wait ran out
 
 
+@pytest.mark.parametrize("m", [1, 5, 8, 13, 16])
+@pytest.mark.parametrize("nq,nkv,hd,k,page", [(6, 3, 48, 96, 4), (5, 1, 32, 64, 8), (4, 4, 16, 32, 4),
+                                              (24, 8, 128, 1056, 64), (3, 1, 256, 2080, 16)])
+def test_qkv_product_with_rotary_and_cache_write(m, nq, nkv, hd, k, page):
+    """The decode form of the mixer's first product (product, rotation, cache write in one
+    kernel) against the float64 rotation of the float64 product, and against the two
+    separate kernels: tokens of several requests at scattered cache positions, head sizes
+    in steps of 16, a K that is no multiple of the ring's chunk."""
+    from mstar_b200 import ops
+
+    x = rnd(m, k, dtype=torch.bfloat16, seed=m + hd)
+    w = rnd((nq + 2 * nkv) * hd, k, dtype=torch.bfloat16, seed=nq, scale=0.1)
+    inv = torch.tensor([500000.0 ** (-2.0 * j / hd) for j in range(hd // 2)],
+                       dtype=torch.float32, device=DEV)
+    # token i belongs to request i % 3 and lies at a cache position of its own; positions
+    # for the angles differ from the cache positions
+    per_req = 6
+    table = torch.randperm(3 * per_req, generator=torch.Generator().manual_seed(m)).to(
+        torch.int32).view(3, per_req).to(DEV)
+    token_req = torch.tensor([i % 3 for i in range(m)], dtype=torch.int32, device=DEV)
+    cache_pos = torch.tensor([(7 * i + 3) % (per_req * page) for i in range(m)],
+                             dtype=torch.int32, device=DEV)
+    assert len({(int(r), int(c)) for r, c in zip(token_req, cache_pos)}) == m
+    pos = cache_pos + 1000
+    kv = scatter_cache(3 * per_req, nkv, page, hd, torch.bfloat16)
+    q = ops.qkv_rope_write(x, w, pos, cache_pos, token_req, table, inv, kv, nq, nkv, hd, page)
+    assert q is not None and q.shape == (m, nq * hd) and tc_clean() == 0
+
+    # the two separate kernels
+    kv2 = scatter_cache(3 * per_req, nkv, page, hd, torch.bfloat16)
+    qkv = ops.linear(x, w)
+    ops.rope_kv_write(qkv, pos, cache_pos, token_req, table, inv, kv2, nq, nkv, hd, hd, False, page)
+    assert (q.float() - qkv[:, :nq * hd].float()).abs().max() <= 2 ** -7 * qkv.float().abs().max()
+    assert (kv.float() - kv2.float()).abs().max() <= 2 ** -7 * kv2.float().abs().max()
+
+    # float64: rotate the exact product
+    y = (x.double() @ w.double().T).cpu()
+    scale = y.abs().max()
+    qr = P.plain_apply_rope(y[:, :nq * hd].view(m, nq, hd), pos.cpu(), inv.double().cpu())
+    kr = P.plain_apply_rope(y[:, nq * hd:(nq + nkv) * hd].view(m, nkv, hd), pos.cpu(),
+                            inv.double().cpu())
+    vr = y[:, (nq + nkv) * hd:].view(m, nkv, hd)
+    assert (q.double().cpu().view(m, nq, hd) - qr).abs().max() < 0.012 * scale
+    written = torch.zeros(kv.shape[0], page, dtype=torch.bool)
+    for i in range(m):
+        cp = int(cache_pos[i])
+        pg = int(table[int(token_req[i]), cp // page])
+        written[pg, cp % page] = True
+        assert (kv[pg, 0, :, cp % page].double().cpu() - kr[i]).abs().max() < 0.012 * scale
+        assert (kv[pg, 1, :, cp % page].double().cpu() - vr[i]).abs().max() < 0.012 * scale
+    # nothing else in the cache is touched
+    untouched = kv.cpu().permute(0, 3, 1, 2, 4)[~written]
+    assert untouched.abs().max() == 0
+
+
 def test_small_m_gemm_refuses_more_rows():
     from mstar_b200 import ops
 
