@@ -36,6 +36,10 @@ struct DecodeArgs {
     // > 0: the chunk is made on the device from the longest of these tokens' key ranges (see
     // live_chunk), `chunk` being its upper bound; 0: `chunk` as given
     int live_tokens;
+    // nonzero: the caller promises that the kernel before this one on the stream wrote, of the
+    // cache, nothing but each token's own key and value (the keys before them are from earlier
+    // steps), and none of the index arrays
+    int keys_static;
 };
 
 // The chunk that cuts the longest key range among the launch's tokens into `splits` equal
@@ -555,7 +559,12 @@ template <int HD>
 __global__ void __launch_bounds__(RING_THREADS)
 decode_attention_ring_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeArgs a, int tokens,
                              RingLayout lay, int* __restrict__ error_word) {
-    pdl_wait();
+    // With `keys_static` the kernel before this one wrote the queries and each token's own key
+    // and value, and nothing else that is read here: the keys before them were written by
+    // earlier steps and the step's index arrays before its first kernel.  The copies of all
+    // tiles but a token's last then start at once, while that kernel is still draining, and
+    // only the consumers and the last tile wait for it.
+    if (!a.keys_static) pdl_wait();
     constexpr int CPR = HD / 8;
     constexpr int HALVES = HD / 64;
     constexpr uint32_t TILE_BYTES = DEC_TILE * HD * 2;  // keys (or values) of one tile
@@ -592,7 +601,7 @@ decode_attention_ring_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeA
     if (warp == DEC_THREADS / 32) {
         // ------------------------------------------------------------------ producer
         int c = 0;
-        bool ok = true;
+        bool ok = true, waited = !a.keys_static;
         for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
             const int split = item % a.splits, kvh = (item / a.splits) % a.nkv, t = item / (a.splits * a.nkv);
             const int hi = a.cache_pos[t] + 1;
@@ -610,6 +619,10 @@ decode_attention_ring_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeA
             for (int it = 0; it < ntiles; ++it, ++c) {
                 const int st = c % S;
                 const int key0 = ks + it * DEC_TILE;
+                if (!waited && key0 + DEC_TILE >= hi) {   // the tile with the token's own key
+                    pdl_wait();
+                    waited = true;
+                }
                 const int base_page = key0 / ps;
                 if (have_from < 0 || base_page + per_tile > have_from + 32) {
                     have_from = base_page;
@@ -643,6 +656,7 @@ decode_attention_ring_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeA
     }
 
     // ---------------------------------------------------------------------- consumers
+    if (a.keys_static) pdl_wait();        // the queries are the output of the kernel before
     int c = 0;
     for (int item = blockIdx.x; item < items; item += gridDim.x) {
         const int split = item % a.splits, kvh = (item / a.splits) % a.nkv, t = item / (a.splits * a.nkv);
@@ -894,12 +908,14 @@ MSTAR_API int mstar_make_kv_tensor_map(void* out_map, const void* kv_cache, long
 }
 
 // The TMA variant: `kv_map` from mstar_make_kv_tensor_map for this cache; no window.
-// `error_word`: device int, set to 4 if a copy's barrier never completed.
+// `error_word`: device int, set to 4 if a copy's barrier never completed.  `keys_static`:
+// nonzero promises that the kernel before this one on the stream wrote nothing that is read
+// here but the queries and each token's own key and value (see DecodeArgs).
 MSTAR_API int mstar_paged_decode_attention_bf16_tma(
     const void* kv_map, const void* q, int q_stride, void* out, const void* kv_cache,
     const int* block_table, int bt_stride, const int* token_req, const int* cache_pos, int tokens,
-    int nq, int nkv, int hd, int page_size, float scale, int chunk, int splits, float* scratch,
-    int* error_word, void* stream) {
+    int nq, int nkv, int hd, int page_size, float scale, int chunk, int splits, int keys_static,
+    float* scratch, int* error_word, void* stream) {
     if (tokens <= 0) return 0;
     if (nkv <= 0 || nq % nkv != 0 || nq / nkv > 16) return -1;
     if (chunk <= 0 || chunk % DEC_TILE != 0 || splits < 1 || splits > MERGE_MAX_SPLITS) return -1;
@@ -926,6 +942,7 @@ MSTAR_API int mstar_paged_decode_attention_bf16_tma(
     a.splits = splits;
     a.scale_log2e = scale * 1.4426950408889634f;
     a.live_tokens = 0;
+    a.keys_static = keys_static;
     CUtensorMap map;
     memcpy(&map, kv_map, sizeof(map));
     cudaStream_t s = (cudaStream_t)stream;
@@ -986,6 +1003,7 @@ MSTAR_API int mstar_paged_decode_attention_bf16(
     a.splits = splits;
     a.scale_log2e = scale * 1.4426950408889634f;
     a.live_tokens = 0;
+    a.keys_static = 0;
     cudaStream_t s = (cudaStream_t)stream;
     switch (hd) {
         case 16: return launch_decode<16>(a, tokens, s);

@@ -238,9 +238,13 @@ def kv_tensor_map(kv_cache: torch.Tensor):
 def paged_decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv_cache,
                            block_table, token_req, cache_pos, tokens: int, num_heads: int,
                            num_kv_heads: int, head_dim: int, page_size: int, window: int,
-                           scale: float, max_len: int) -> None:
+                           scale: float, max_len: int, static_keys: bool = False) -> None:
     """bfloat16 attention of ``tokens`` single-query rows (token i of q/out/token_req/
-    cache_pos); ``max_len`` bounds the keys any of them sees."""
+    cache_pos); ``max_len`` bounds the keys any of them sees.  ``static_keys`` promises that
+    the kernel before this one on the stream wrote nothing that is read here but the queries
+    and each token's own key and value (a decode step of the engine: the keys before are from
+    earlier steps, the index arrays from before the step's first kernel); the copies of the
+    earlier keys then start while that kernel is still draining."""
     _need_cuda(q, out, kv_cache, block_table, token_req, cache_pos)
     assert q.dtype == torch.bfloat16 and kv_cache.dtype == torch.bfloat16
     assert (q_stride * 2) % 16 == 0 and q.data_ptr() % 16 == 0 and out.is_contiguous()
@@ -260,8 +264,8 @@ def paged_decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
             kv_map, q.data_ptr(), q_stride, out.data_ptr(), kv_cache.data_ptr(),
             block_table.data_ptr(), block_table.stride(0), token_req.data_ptr(),
             cache_pos.data_ptr(), tokens, num_heads, num_kv_heads, head_dim, page_size,
-            float(scale), chunk, splits, _ptr(scratch), tcgen05_error_word(q.device).data_ptr(),
-            _stream())
+            float(scale), chunk, splits, int(static_keys), _ptr(scratch),
+            tcgen05_error_word(q.device).data_ptr(), _stream())
         if code == -1:
             raise KernelError("TMA decode attention refuses this shape")
         check(code, "paged_decode_attention_tma")

@@ -34,7 +34,7 @@ _SIGNATURES = {
     "attention_decode": {
         "mstar_make_kv_tensor_map": [_vp, _vp, _ll, _i, _i, _i],
         "mstar_paged_decode_attention_bf16_tma": [_vp, _vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i,
-                                                  _i, _i, _i, _f, _i, _i, _vp, _vp, _vp],
+                                                  _i, _i, _i, _f, _i, _i, _i, _vp, _vp, _vp],
         "mstar_paged_decode_attention_bf16": [_vp, _i, _vp, _vp, _vp, _i, _vp, _vp, _i, _i, _i,
                                               _i, _i, _i, _f, _i, _i, _vp, _vp],
     },

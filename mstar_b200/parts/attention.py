@@ -83,7 +83,8 @@ class Attention:
                 ops.paged_decode_attention(
                     qkv, qkv.stride(0), out, cache.kv, cache.block_table, ctx.token_req,
                     ctx.cache_pos, nd, s.num_heads, s.num_kv_heads, s.head_dim,
-                    cache.page_size, s.window or 0, self.scale, max(ctx.kv_lens[:nd]))
+                    cache.page_size, s.window or 0, self.scale, max(ctx.kv_lens[:nd]),
+                    static_keys=True)
             if ctx.num_entries > nd:
                 ops.paged_prefill_attention(
                     qkv, qkv.stride(0), out, cache.kv, cache.block_table, ctx.qo_indptr,
