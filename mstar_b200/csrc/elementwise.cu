@@ -57,12 +57,13 @@ MSTAR_API int mstar_embed_rows(const void* table, int table_dtype, const int* id
 // is given; out = resid * rsqrt(mean(resid^2) + eps) * (w + w_offset) in type A.
 // One block per row.  The sum of squares is accumulated per thread over a fixed
 // stride and then reduced in a fixed tree, so a row's result does not depend on
-// which other rows are in the batch.
+// which other rows are in the batch.  `resid_static`: nonzero promises that the kernel
+// before this one on the stream did not write resid (it wrote delta), so resid may be
+// read while that kernel is still draining.
 template <typename A, typename W, bool VEC>
 __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const A* __restrict__ delta,
                                    const W* __restrict__ weight, A* __restrict__ out, int hidden,
-                                   float eps, float w_offset) {
-    pdl_wait();
+                                   float eps, float w_offset, int resid_static) {
     __shared__ float scratch[32];
     const size_t base = (size_t)blockIdx.x * hidden;
     float* r = resid + base;
@@ -71,6 +72,62 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const A* __restric
         // eight elements per thread and step, 16-byte accesses; the order in which a row's
         // squares are summed depends only on the row's width and the block size
         const int chunks = hidden >> 3;
+        if (chunks <= 2 * (int)blockDim.x) {
+            // a thread's one or two chunks stay in registers.  The weight is a parameter, and
+            // with `resid_static` the kernel before this one wrote the delta only: both are
+            // asked for while that kernel is still draining.
+            const int c0 = threadIdx.x, c1 = threadIdx.x + blockDim.x;
+            const bool h0 = c0 < chunks, h1 = c1 < chunks;
+            float v0[8], v1[8], w0[8], w1[8];
+            if (h0) load8(weight + 8 * c0, w0);
+            if (h1) load8(weight + 8 * c1, w1);
+            if (resid_static) {
+                if (h0) load8(r + 8 * c0, v0);
+                if (h1) load8(r + 8 * c1, v1);
+            }
+            pdl_wait();
+            if (!resid_static) {
+                if (h0) load8(r + 8 * c0, v0);
+                if (h1) load8(r + 8 * c1, v1);
+            }
+            if (delta != nullptr) {
+                float d[8];
+                if (h0) {
+                    load8(delta + base + 8 * c0, d);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v0[i] += d[i];
+                    store8(r + 8 * c0, v0);
+                }
+                if (h1) {
+                    load8(delta + base + 8 * c1, d);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v1[i] += d[i];
+                    store8(r + 8 * c1, v1);
+                }
+            }
+            if (h0) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) ss = fmaf(v0[i], v0[i], ss);
+            }
+            if (h1) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) ss = fmaf(v1[i], v1[i], ss);
+            }
+            const float total = block_sum(ss, scratch);
+            const float inv = rsqrtf(total / (float)hidden + eps);
+            if (h0) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v0[i] = v0[i] * inv * (w0[i] + w_offset);
+                store8(out + base + 8 * c0, v0);
+            }
+            if (h1) {
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v1[i] = v1[i] * inv * (w1[i] + w_offset);
+                store8(out + base + 8 * c1, v1);
+            }
+            return;
+        }
+        pdl_wait();
         for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
             float v[8];
             load8(r + 8 * c, v);
@@ -96,6 +153,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const A* __restric
         }
         return;
     }
+    pdl_wait();
     if (delta != nullptr) {
         const A* d = delta + base;
         for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
@@ -120,7 +178,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const A* __restric
 
 MSTAR_API int mstar_add_rmsnorm(float* resid, const void* delta, const void* weight,
                                 int weight_dtype, void* out, int act_dtype, int rows, int hidden,
-                                float eps, float w_offset, void* stream) {
+                                float eps, float w_offset, int resid_static, void* stream) {
     if (rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const bool vec = hidden % 8 == 0 && ((uintptr_t)resid % 32 == 0) && ((uintptr_t)out % 16 == 0) &&
@@ -130,10 +188,11 @@ MSTAR_API int mstar_add_rmsnorm(float* resid, const void* delta, const void* wei
 #define LAUNCH(A, W)                                                                             \
     if (vec)                                                                                     \
         mstar_launch((add_rmsnorm_kernel<A, W, true>), dim3(rows), dim3(threads), 0, s,                                  \
-            resid, (const A*)delta, (const W*)weight, (A*)out, hidden, eps, w_offset);          \
+            resid, (const A*)delta, (const W*)weight, (A*)out, hidden, eps, w_offset,           \
+            resid_static);                                                                       \
     else                                                                                         \
         mstar_launch((add_rmsnorm_kernel<A, W, false>), dim3(rows), dim3(threads), 0, s,                                 \
-            resid, (const A*)delta, (const W*)weight, (A*)out, hidden, eps, w_offset)
+            resid, (const A*)delta, (const W*)weight, (A*)out, hidden, eps, w_offset, resid_static)
     if (act_dtype == MSTAR_F32) {
         if (weight_dtype == MSTAR_F32) { LAUNCH(float, float); } else { LAUNCH(float, bf16); }
     } else {

@@ -67,8 +67,11 @@ def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None 
 
 
 def add_rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, eps: float,
-                out_dtype: torch.dtype, weight_offset: float = 0.0, out=None):
-    """resid += delta (if given), in place in float; returns rmsnorm(resid)*weight."""
+                out_dtype: torch.dtype, weight_offset: float = 0.0, out=None,
+                resid_static: bool = False):
+    """resid += delta (if given), in place in float; returns rmsnorm(resid)*weight.
+    ``resid_static`` promises that the kernel before this one on the stream did not write
+    ``resid`` (it wrote ``delta``): the residual is then read while that kernel drains."""
     _need_cuda(resid, delta, weight)
     assert resid.dtype == torch.float32 and resid.dim() == 2 and resid.is_contiguous()
     rows, hidden = resid.shape
@@ -79,7 +82,8 @@ def add_rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, eps: float,
         out = torch.empty((rows, hidden), dtype=out_dtype, device=resid.device)
     check(lib.get("elementwise").mstar_add_rmsnorm(
         resid.data_ptr(), _ptr(delta), weight.data_ptr(), _dt(weight), out.data_ptr(), _dt(out),
-        rows, hidden, float(eps), float(weight_offset), _stream()), "add_rmsnorm")
+        rows, hidden, float(eps), float(weight_offset), int(resid_static), _stream()),
+        "add_rmsnorm")
     return out
 
 

@@ -32,8 +32,11 @@ class RMSNorm:
 
     def add_norm(self, stream: ResidualStream) -> torch.Tensor:
         """Fold the pending delta into the residual and return the normed rows."""
-        return ops.add_rmsnorm(stream.h, stream.take_delta(), self.weight, self.spec.eps,
-                               self.runtime.dtype, self.spec.weight_offset)
+        delta = stream.take_delta()
+        # a pending delta is the output of the part before: its kernels lie between this
+        # norm and whatever wrote the residual last
+        return ops.add_rmsnorm(stream.h, delta, self.weight, self.spec.eps, self.runtime.dtype,
+                               self.spec.weight_offset, resid_static=delta is not None)
 
     def norm_rows(self, rows_f32: torch.Tensor) -> torch.Tensor:
         """Norm of float rows that carry no pending delta (the final norm on the
