@@ -168,6 +168,28 @@ smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
     const int g = lane >> 2, t = lane & 3;
     const bf16* xa = x + (size_t)min(g, M - 1) * ldx + 8 * t;
     const bf16* xb = x + (size_t)min(g + 8, M - 1) * ldx + 8 * t;
+    // this warp's blocks of a chunk: warp, warp + 8, ...  (at most 4 of 32)
+    constexpr int PER = SB_KC / 32 / SB_WARPS;
+    auto load_x = [&](int ch, uint4 (&xv)[PER], uint4 (&xw)[PER]) {
+#pragma unroll
+        for (int u = 0; u < PER; ++u) {
+            const int k = ch * SB_KC + (warp + u * SB_WARPS) * 32;
+            xv[u] = xw[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (k < K) {
+                xv[u] = __ldg(reinterpret_cast<const uint4*>(xa + k));
+                if (M16) xw[u] = __ldg(reinterpret_cast<const uint4*>(xb + k));
+            }
+        }
+    };
+    // With at most 8 tokens x is asked for one chunk ahead (it does not depend on the strip, so
+    // a strip's last chunk asks for the first of the next): when the weights are there before
+    // x, as in a short product whose ring was filled while the kernel before it drained, the
+    // latency of x would otherwise show once per chunk.  With 16 tokens, and in the rotary form,
+    // the registers do not allow it (measured: slower), and x is asked for just before the wait
+    // for W.
+    constexpr bool AHEAD = !M16 && MODE != SB_ROPE;
+    uint4 xn[PER], xwn[PER];
+    if (AHEAD && (int)blockIdx.x < nstrips) load_x(0, xn, xwn);
     int c = 0;
     for (int strip = blockIdx.x; strip < nstrips; strip += gridDim.x) {
         const int n0 = sb_strip_n0<MODE, NT>(strip, rp);
@@ -177,19 +199,17 @@ smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
         for (int ch = 0; ch < nch; ++ch, ++c) {
             const int st = c % SB_STAGES;
             const int nkb = min(SB_KC, K - ch * SB_KC) / 32;
-            // this warp's blocks of the chunk: warp, warp + 8, ...  (at most 4 of 32); x is asked
-            // for before the wait for W
-            constexpr int PER = SB_KC / 32 / SB_WARPS;
             uint4 xv[PER], xw[PER];
+            if (AHEAD) {
 #pragma unroll
-            for (int u = 0; u < PER; ++u) {
-                const int kb = warp + u * SB_WARPS;
-                xv[u] = xw[u] = make_uint4(0u, 0u, 0u, 0u);
-                if (kb < nkb) {
-                    const int k = ch * SB_KC + kb * 32;
-                    xv[u] = __ldg(reinterpret_cast<const uint4*>(xa + k));
-                    if (M16) xw[u] = __ldg(reinterpret_cast<const uint4*>(xb + k));
+                for (int u = 0; u < PER; ++u) {
+                    xv[u] = xn[u];
+                    xw[u] = xwn[u];
                 }
+                const bool more = ch + 1 < nch || strip + (int)gridDim.x < nstrips;
+                if (more) load_x(ch + 1 < nch ? ch + 1 : 0, xn, xwn);
+            } else {
+                load_x(ch, xv, xw);
             }
             if (!mbar_wait(full + 8 * st, (uint32_t)(c / SB_STAGES) & 1u)) {
                 // give up, but only together with the other warps (they wait at the barrier below)
