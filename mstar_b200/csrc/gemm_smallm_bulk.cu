@@ -338,14 +338,16 @@ static int launch_bulk_nt(const bf16* x, const bf16* W, OutT* out, int M, int n_
 
 // Rows of W per strip by the number of output features: 8 while the strips barely fill the
 // GPU, 16 and 32 where there are many (less traffic for x); the gated form has twice the rows
-// per strip already.  MSTAR_SMALLM_NT=1|2|4 forces one (for measurements).
-static int pick_nt(int n_out, bool gated) {
+// per strip already, and with at most 8 tokens it keeps to them (two CTAs on an SM: measured
+// faster than one with 32 rows).  MSTAR_SMALLM_NT=1|2|4 forces one (for measurements).
+static int pick_nt(int n_out, bool gated, bool m16) {
     static int forced = -1;
     if (forced < 0) {
         const char* e = getenv("MSTAR_SMALLM_NT");
         forced = e ? atoi(e) : 0;
     }
     int nt = n_out >= 32768 ? 4 : (n_out >= 1024 ? 2 : 1);
+    if (gated && !m16) nt = 1;
     if (forced == 1 || forced == 2 || forced == 4) nt = forced;
     if (gated && nt > 2) nt = 2;
     return nt;
@@ -354,7 +356,7 @@ static int pick_nt(int n_out, bool gated) {
 template <bool GATED, bool M16, typename OutT>
 static int launch_bulk(const bf16* x, const bf16* W, OutT* out, int M, int n_out, int K, int ldx, int ldw,
                        int ldo, int inter, int w_static, int* error_word, cudaStream_t s) {
-    switch (pick_nt(n_out, GATED)) {
+    switch (pick_nt(n_out, GATED, M16)) {
         case 4:
             if constexpr (!GATED)
                 return launch_bulk_nt<GATED ? SB_GATED : SB_PLAIN, M16, 4, OutT>(x, W, out, M, n_out, K, ldx, ldw, ldo, inter, w_static, error_word, s);

@@ -365,14 +365,9 @@ def _smallm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
 def smallm_kernel(m: int, gated: bool) -> str:
     """"bulk" or "registers": which weight-streaming kernel takes a product of ``m`` rows.
     The bulk-copy kernel (weights through a shared-memory ring filled by ``cp.async.bulk``)
-    is the faster one except for the fused gate/up form with at most 8 rows;
-    MSTAR_SMALLM=bulk|registers forces one."""
-    import os
-
-    forced = os.environ.get("MSTAR_SMALLM")
-    if forced in ("bulk", "registers"):
-        return forced
-    return "registers" if gated and m <= 8 else "bulk"
+    is the faster one in every form; MSTAR_SMALLM=registers selects the other (weights
+    through registers), for measurements."""
+    return "registers" if os.environ.get("MSTAR_SMALLM") == "registers" else "bulk"
 
 
 def _gemm_smallm(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, gated: bool,
