@@ -251,14 +251,25 @@ __global__ void __launch_bounds__(DEC_THREADS) decode_attention_kernel(DecodeArg
 template <int HD>
 __global__ void decode_merge_kernel(DecodeArgs a) {
     pdl_launch_dependents();   // a short kernel: the long one after it may be scheduled now
-    pdl_wait();
     __shared__ float wgt[MERGE_MAX_SPLITS];
     const int head = blockIdx.x, t = blockIdx.y;
+    // the step's index arrays were there before the step's first kernel
     const int hi = a.cache_pos[t] + 1;
     const int lo = (a.window > 0 && hi > a.window) ? hi - a.window : 0;
     const int chunk = live_chunk(a);               // every warp computes it (uniform)
     const int n = min(a.splits, (hi - lo + chunk - 1) / chunk);
     const size_t base = ((size_t)t * a.nq + head) * a.splits;
+    pdl_wait();
+    // a thread's features of the first splits are asked for together with the maxima and sums,
+    // not after the weights are known: one round trip to memory instead of two
+    constexpr int PD = (HD + 127) / 128, PS = 8;
+    float po[PD][PS];
+#pragma unroll
+    for (int i = 0; i < PD; ++i) {
+        const int d = threadIdx.x + i * blockDim.x;
+#pragma unroll
+        for (int s = 0; s < PS; ++s) po[i][s] = (s < n && d < HD) ? a.part_o[(base + s) * HD + d] : 0.f;
+    }
     if (threadIdx.x < 32) {
         const int lane = threadIdx.x;
         float m = -INFINITY;
@@ -276,9 +287,15 @@ __global__ void decode_merge_kernel(DecodeArgs a) {
         for (int s = lane; s < n; s += 32) wgt[s] *= inv;
     }
     __syncthreads();
-    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+#pragma unroll
+    for (int i = 0; i < PD; ++i) {
+        const int d = threadIdx.x + i * blockDim.x;
+        if (d >= HD) continue;
         float acc = 0.f;
-        for (int s = 0; s < n; ++s) acc = fmaf(a.part_o[(base + s) * HD + d], wgt[s], acc);
+#pragma unroll
+        for (int s = 0; s < PS; ++s)
+            if (s < n) acc = fmaf(po[i][s], wgt[s], acc);
+        for (int s = PS; s < n; ++s) acc = fmaf(a.part_o[(base + s) * HD + d], wgt[s], acc);
         a.out[(size_t)t * a.nq * HD + (size_t)head * HD + d] = __float2bfloat16_rn(acc);
     }
 }
