@@ -262,7 +262,7 @@ __global__ void decode_merge_kernel(DecodeArgs a) {
     pdl_wait();
     // a thread's features of the first splits are asked for together with the maxima and sums,
     // not after the weights are known: one round trip to memory instead of two
-    constexpr int PD = (HD + 127) / 128, PS = 8;
+    constexpr int PD = (HD + 127) / 128, PS = 16;
     float po[PD][PS];
 #pragma unroll
     for (int i = 0; i < PD; ++i) {
