@@ -58,6 +58,11 @@ def test_add_rmsnorm(act, wdtype, hidden):
     assert torch.equal(r2, resid)
     want2 = P.plain_rms_norm(resid.cpu(), (w.double() + 1).cpu(), 1e-6)
     assert (out2.double().cpu() - want2).abs().max() < tol(act, bf16=4e-2)
+    # the promise that the kernel before did not write the residual changes when it is read,
+    # not what comes out
+    r3 = resid.clone()
+    out3 = ops.add_rmsnorm(r3, delta, w, 1e-5, act, resid_static=True)
+    assert torch.equal(out3, out) and torch.equal(r3, r)
 
 
 @pytest.mark.parametrize("act", DTYPES)
@@ -604,6 +609,51 @@ def test_qkv_product_with_rotary_and_cache_write(m, nq, nkv, hd, k, page):
     # nothing else in the cache is touched
     untouched = kv.cpu().permute(0, 3, 1, 2, 4)[~written]
     assert untouched.abs().max() == 0
+
+
+@pytest.mark.parametrize("tokens,ctx", [(8, 700), (3, 64), (16, 129), (1, 2000)])
+def test_decode_sequence_with_promises(tokens, ctx):
+    """A decode step's kernels in a row, as the engine launches them: the fused first product
+    (rotation, cache write) and the attention that is promised static earlier keys, against
+    the separate kernels without promises.  The token's own key is written by the kernel
+    directly before the attention, the earlier keys long before; the results are the same
+    bit for bit, launch after launch."""
+    from mstar_b200 import ops
+
+    nq, nkv, hd, page, k = 24, 8, 128, 64, 512
+    x = rnd(tokens, k, dtype=torch.bfloat16, seed=tokens)
+    w = rnd((nq + 2 * nkv) * hd, k, dtype=torch.bfloat16, seed=ctx, scale=0.05)
+    inv = torch.tensor([500000.0 ** (-2.0 * j / hd) for j in range(hd // 2)],
+                       dtype=torch.float32, device=DEV)
+    pages_per = -(-(ctx + 1) // page)
+    g = torch.Generator().manual_seed(5)
+    table = torch.randperm(tokens * pages_per, generator=g).to(torch.int32).view(tokens, -1).to(DEV)
+    old = rnd(tokens * pages_per, 2, nkv, page, hd, dtype=torch.bfloat16, seed=9)
+    token_req = torch.arange(tokens, dtype=torch.int32, device=DEV)
+    cache_pos = torch.tensor([ctx - (7 * i) % min(ctx, 50) for i in range(tokens)],
+                             dtype=torch.int32, device=DEV)
+
+    def step(fused):
+        kv = old.clone()
+        torch.cuda.synchronize()
+        if fused:
+            q = ops.qkv_rope_write(x, w, cache_pos, cache_pos, token_req, table, inv, kv, nq, nkv,
+                                   hd, page)
+        else:
+            q = ops.linear(x, w)
+            ops.rope_kv_write(q, cache_pos, cache_pos, token_req, table, inv, kv, nq, nkv, hd, hd,
+                              False, page)
+        out = torch.empty(tokens, nq * hd, dtype=torch.bfloat16, device=DEV)
+        ops.paged_decode_attention(q, q.stride(0), out, kv, table, token_req, cache_pos, tokens,
+                                   nq, nkv, hd, page, 0, hd ** -0.5, ctx + 1, static_keys=fused)
+        return out, kv
+
+    want, kv_want = step(False)
+    for _ in range(5):
+        got, kv_got = step(True)
+        assert torch.equal(kv_got, kv_want)
+        assert torch.equal(got, want)
+    assert tc_clean() == 0
 
 
 def test_small_m_gemm_refuses_more_rows():
