@@ -450,15 +450,18 @@ def main() -> int:
     print("[bench] decode ...", file=sys.stderr, flush=True)
     with ClockSampler() as clocks:
         head = time_decode(stepper, args.batch, cfg, args.steps, warmup)
+    # the same steps through the entry point, directly after the device-timed ones (the
+    # long batch-64 run below leaves the GPU under its power cap)
+    print("[bench] end to end ...", file=sys.stderr, flush=True)
+    e2e = time_e2e(model, args.batch, cfg, args.steps, warmup,
+                   args.batch * (CONTEXT // PAGE_SIZE) + 64)
+    print("[bench] decode at batch 1 and 64 ...", file=sys.stderr, flush=True)
     points = {}
     for b in (1, 64):
         r = time_decode(stepper, b, cfg, max(args.steps // 2, 8), warmup)
         points[f"decode_b{b}"] = round(r["tokens_per_s"], 1)
     del stepper
     torch.cuda.empty_cache()
-    print("[bench] end to end ...", file=sys.stderr, flush=True)
-    e2e = time_e2e(model, args.batch, cfg, args.steps, warmup,
-                   args.batch * (CONTEXT // PAGE_SIZE) + 64)
 
     step_bytes = bytes_of_decode_step(cfg, model, head["kv_lens"])
     achieved = step_bytes / (head["ms_per_step"] / 1e3) / 1e9

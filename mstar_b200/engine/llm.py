@@ -86,6 +86,7 @@ class LLM:
         self._host_tokens = [torch.empty(max(max_batch_size, 1), dtype=torch.int32, pin_memory=True)
                              for _ in range(3)]
         self._turn = 0
+        self._copy_stream = torch.cuda.Stream(device=self.device)
 
     def _pages_from_memory(self, page_size: int, fraction: float) -> list:
         free, _ = torch.cuda.mem_get_info(self.device)
@@ -169,9 +170,15 @@ class LLM:
         if self._host_tokens[turn].numel() < len(sampling):
             self._host_tokens[turn] = torch.empty(len(sampling), dtype=torch.int32, pin_memory=True)
         host = self._host_tokens[turn][:len(sampling)]
-        host.copy_(tokens, non_blocking=True)
-        arrived = torch.cuda.Event()
-        arrived.record()
+        # on a stream of its own, so that the next step's input copy and kernels do not
+        # queue behind it (``tokens`` stays referenced until it has arrived)
+        sampled = torch.cuda.Event()
+        sampled.record()
+        with torch.cuda.stream(self._copy_stream):
+            self._copy_stream.wait_event(sampled)
+            host.copy_(tokens, non_blocking=True)
+            arrived = torch.cuda.Event()
+            arrived.record()
         return plan, sampling, tokens, host, arrived
 
     def _finished_and_complete(self) -> list:
