@@ -11,8 +11,9 @@
 // consumer warps only ever wait for data that is already on its way.
 //
 // A CTA owns strips of 8 NT output features (8 NT rows of W; twice that for the fused gate/up
-// form: rows n and inter + n) and walks over its strips (grid = what is resident at once,
-// further strips are taken in further turns without draining the ring).  NT is 1, 2 or 4:
+// form: rows n and inter + n) and walks over its strips (grid = at most what is resident at
+// once, cut so that every CTA takes the same number of strips; further strips are taken in
+// further turns without draining the ring).  NT is 1, 2 or 4:
 // the more rows share one read of x, the less traffic x causes (with 8 tokens and NT = 1 it
 // equals the traffic of W), so wide matrices, which have strips enough, take larger ones.
 // The bytes in flight per SM stay near 200 KB: 4, 2 or 1 CTAs per SM.  The K range of a strip is cut
