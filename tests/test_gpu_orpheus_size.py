@@ -102,3 +102,57 @@ def test_orpheus_sized_layers_match_the_plain_model(big, dtype):
         print(f"{what} [{dtype}]: worst abs error {worst:.3e}")
     del model
     torch.cuda.empty_cache()
+
+
+# A request of 2,500 tokens at the 3B layer sizes: prompt portions of 1,024 (the second and
+# third attend to keys that earlier steps cached, over several key tiles and pages), then the
+# last 8 tokens one by one (decode kernels with their keys split).  Places checked: the
+# first token, both sides of the portion edges, the decoded tail.  Tolerances by the rules
+# above from this request's own noise (float32 3.7e-5 / 4.6e-6, bfloat16 0.19 / 0.025).
+LONG = 2500
+LONG_ROWS = [0, 1023, 1024, 1025, 2047, 2048, 2300, 2491, 2492, 2495, 2498, 2499]
+LONG_TOLS = {"float32": (1.7e-4, 2.1e-5), "bfloat16": (0.29, 0.037)}
+
+
+@pytest.fixture(scope="module")
+def long_request():
+    from mstar_b200.config.registry import config_from_dict
+    from mstar_b200.weights.random_init import random_checkpoint
+
+    cfg = config_from_dict(CFG)
+    tensors = random_checkpoint(cfg, seed=3, std=0.02, device="cuda:0")
+    for key in tensors:
+        if key.endswith("q_proj.weight") or key.endswith("k_proj.weight"):
+            tensors[key] = (tensors[key].float() * 2.0).to(torch.bfloat16)
+    toks = H.request_tokens(CFG["vocab_size"], LONG, seed=90)
+    cpu = {k: v.cpu() for k, v in tensors.items()}
+    hidden = P.plain_hidden_states(cpu, CFG, toks)
+    logits = hidden[LONG_ROWS] @ cpu["model.embed_tokens.weight"].double().T
+    want = {("long", r): logits[i] for i, r in enumerate(LONG_ROWS)}
+    return cfg, tensors, toks, want
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_request_in_portions_then_decoded(long_request, dtype):
+    from mstar_b200.engine.model import load_model
+    from mstar_b200.engine.step import make_stepper
+
+    cfg, tensors, toks, want = long_request
+    model = load_model(None, dtype=dtype, device="cuda:0", config=cfg, tensors=tensors)
+    steps, pos = [], 0
+    cuts = [1024, 1024, LONG - 2048 - 8] + [1] * 8
+    for n in cuts:
+        steps.append({"step": len(steps), "entries": [
+            {"id": "long", "tokens": toks[pos:pos + n], "want": list(range(n))}], "end": []})
+        pos += n
+    assert pos == LONG
+    steps[-1]["end"] = ["long"]
+    steps = only_wanted(steps, want)
+    stepper = make_stepper(model, page_size=64, num_pages=-(-LONG // 64), num_slots=2)
+    got = H.run_steps_in_process(stepper, steps)
+    assert set(got) == set(want)
+    tol, mean_tol = LONG_TOLS[dtype]
+    worst = H.compare(got, want, dtype, "a long request in portions", tol=tol, mean_tol=mean_tol)
+    print(f"long request [{dtype}]: worst abs error {worst:.3e}")
+    del model
+    torch.cuda.empty_cache()
