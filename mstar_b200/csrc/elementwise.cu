@@ -391,6 +391,13 @@ __global__ void rope_kv_write_vec_kernel(A* __restrict__ qkv, const int* __restr
     const int total = rot_items + tail_items + v_items;
     const int first = blockIdx.y * blockDim.x + threadIdx.x;
     const int stride = gridDim.y * blockDim.x;
+    // the token's sines and cosines once per block (every head uses the same); half <= 128
+    __shared__ float tab_sn[128], tab_cs[128];
+    {
+        const float p = (float)positions[t];
+        for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(p * inv_freq[j], &tab_sn[j], &tab_cs[j]);
+    }
+    __syncthreads();
     if (first >= total) return;
 
     A* kdst = nullptr;
@@ -403,19 +410,16 @@ __global__ void rope_kv_write_vec_kernel(A* __restrict__ qkv, const int* __restr
         kdst = kv_cache + (size_t)page * page_elems + (size_t)slot * hd;
         vdst = kdst + (size_t)a.nkv * a.page_size * hd;
     }
-    const float pos = (float)positions[t];
     for (int item = first; item < total; item += stride) {
         if (item < rot_items) {
             const int h = item / hchunks, j0 = (item - h * hchunks) * 8;
             A* src = row + (size_t)h * hd;
-            float x0[8], x1[8], f[8], y0[8], y1[8];
+            float x0[8], x1[8], y0[8], y1[8];
             load8(src + j0, x0);
             load8(src + j0 + half, x1);
-            load8(inv_freq + j0, f);
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
-                float sn, cs;
-                sincosf(pos * f[i], &sn, &cs);
+                const float sn = tab_sn[j0 + i], cs = tab_cs[j0 + i];
                 y0[i] = x0[i] * cs - x1[i] * sn;
                 y1[i] = x1[i] * cs + x0[i] * sn;
             }
@@ -450,7 +454,7 @@ MSTAR_API int mstar_rope_kv_write(void* qkv, int act_dtype, const int* positions
     const int threads = 256;
     // split-half pairs, halves and the unrotated tail in whole groups of 8, float angles
     // table aligned: the vector kernel; else one pair per item
-    const bool vec = !interleaved && rotary_dim > 0 && (rotary_dim / 2) % 8 == 0 && hd % 8 == 0 &&
+    const bool vec = !interleaved && rotary_dim > 0 && rotary_dim <= 256 && (rotary_dim / 2) % 8 == 0 && hd % 8 == 0 &&
                      (hd - rotary_dim) % 8 == 0 && ((uintptr_t)qkv % 32 == 0) &&
                      ((uintptr_t)inv_freq % 32 == 0) && (kv_cache == nullptr || (uintptr_t)kv_cache % 32 == 0) &&
                      act_dtype == MSTAR_BF16;
