@@ -110,7 +110,19 @@ static inline int launch_status() { return (int)cudaGetLastError(); }
 __device__ __forceinline__ void pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// Returns zero, in a way the compiler cannot see through.  A pointer to data that the kernel
+// before this one wrote is passed through pdl_after() with that zero before its first use: a
+// load through a `const __restrict__` pointer (or __ldg) may be compiled as a load of memory
+// that never changes, which the compiler is free to move above the wait; an address that
+// depends on the wait's result cannot be formed before it.
+__device__ __forceinline__ unsigned long long pdl_wait() {
+    unsigned long long zero;
+    asm volatile("griddepcontrol.wait;\n\tmov.u64 %0, 0;" : "=l"(zero)::"memory");
+    return zero;
+}
+template <typename T> __device__ __forceinline__ T* pdl_after(T* p, unsigned long long zero_of_wait) {
+    return reinterpret_cast<T*>(reinterpret_cast<unsigned long long>(p) + zero_of_wait);
+}
 
 static inline int pdl_enabled() {
     static int v = -1;

@@ -42,7 +42,8 @@ smallm_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
                    int M, int n_out, int K, int ldx, int ldw, int ldo, int inter, int w_static) {
     // Weights that nothing writes while the engine runs are asked for before the wait for
     // the kernel before this one (whose output x is); see the loop.
-    if (!w_static) pdl_wait();
+    unsigned long long waited = 0;
+    if (!w_static) waited = pdl_wait();
     constexpr int STRIPS = GATED ? 2 : 1;
     __shared__ float red[STRIPS][SM_WARPS][16][8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -56,8 +57,9 @@ smallm_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
     const bf16* wp[STRIPS];
 #pragma unroll
     for (int s = 0; s < STRIPS; ++s) wp[s] = W + ((size_t)row + (size_t)s * inter) * ldw + 8 * t;
-    const bf16* xa = x + (size_t)min(g, M - 1) * ldx + 8 * t;
-    const bf16* xb = x + (size_t)min(g + 8, M - 1) * ldx + 8 * t;
+    // x is what the kernel before wrote: its addresses are formed after the wait
+    const bf16* xa = pdl_after(x, waited) + (size_t)min(g, M - 1) * ldx + 8 * t;
+    const bf16* xb = pdl_after(x, waited) + (size_t)min(g + 8, M - 1) * ldx + 8 * t;
 
     float acc[STRIPS][4];
 #pragma unroll
@@ -72,7 +74,11 @@ smallm_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
                 for (int s = 0; s < STRIPS; ++s) wv[s][u] = ld_stream(wp[s] + (kb + u) * 32);
             }
         }
-        if (w_static && kb == kb0) pdl_wait();   // the first weights are on their way
+        if (w_static && kb == kb0) {             // the first weights are on their way
+            const unsigned long long z = pdl_wait();
+            xa = pdl_after(xa, z);
+            xb = pdl_after(xb, z);
+        }
 #pragma unroll
         for (int u = 0; u < SM_UNROLL; ++u) {
             if (kb + u < kb1) {
@@ -132,7 +138,8 @@ template <int NT, bool GATED, typename OutT>
 __global__ void __launch_bounds__(SM_THREADS)
 smallm_wide_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT* __restrict__ out,
                    int M, int n_out, int K, int ldx, int ldw, int ldo, int inter, int w_static) {
-    if (!w_static) pdl_wait();            // as in the kernel above
+    unsigned long long waited = 0;
+    if (!w_static) waited = pdl_wait();   // as in the kernel above
     extern __shared__ float red[];  // [strips][SM_WARPS][16][8*NT]
     constexpr int COLS = 8 * NT;
     constexpr int STRIPS = GATED ? 2 : 1;
@@ -154,7 +161,7 @@ smallm_wide_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, 
     }
     const bf16* xr[NT];
 #pragma unroll
-    for (int j = 0; j < NT; ++j) xr[j] = x + (size_t)min(8 * j + g, M - 1) * ldx + 8 * t;
+    for (int j = 0; j < NT; ++j) xr[j] = pdl_after(x, waited) + (size_t)min(8 * j + g, M - 1) * ldx + 8 * t;
 
     float acc[STRIPS][NT][4];
 #pragma unroll
@@ -175,7 +182,11 @@ smallm_wide_gemm_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, 
                 }
             }
         }
-        if (w_static && kb == kb0) pdl_wait();   // the first weights are on their way
+        if (w_static && kb == kb0) {             // the first weights are on their way
+            const unsigned long long z = pdl_wait();
+#pragma unroll
+            for (int j = 0; j < NT; ++j) xr[j] = pdl_after(xr[j], z);
+        }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
             if (kb + u < kb1) {
