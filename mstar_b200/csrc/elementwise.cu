@@ -18,7 +18,7 @@ template <typename W>
 __global__ void embed_rows_kernel(const W* __restrict__ table, const int* __restrict__ ids,
                                   const int* __restrict__ src, const int* __restrict__ prev,
                                   float* __restrict__ out, int vocab, int hidden) {
-    pdl_wait();
+    prev = pdl_after(prev, pdl_wait());       // sampled by the step before
     const int t = blockIdx.x;
     int id = ids[t];
     if (src != nullptr) {
@@ -85,7 +85,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const A* __restric
                 if (h0) load8(r + 8 * c0, v0);
                 if (h1) load8(r + 8 * c1, v1);
             }
-            pdl_wait();
+            delta = pdl_after(delta, pdl_wait());
             if (!resid_static) {
                 if (h0) load8(r + 8 * c0, v0);
                 if (h1) load8(r + 8 * c1, v1);
@@ -127,7 +127,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const A* __restric
             }
             return;
         }
-        pdl_wait();
+        delta = pdl_after(delta, pdl_wait());
         for (int c = threadIdx.x; c < chunks; c += blockDim.x) {
             float v[8];
             load8(r + 8 * c, v);
@@ -153,7 +153,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ resid, const A* __restric
         }
         return;
     }
-    pdl_wait();
+    delta = pdl_after(delta, pdl_wait());
     if (delta != nullptr) {
         const A* d = delta + base;
         for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
@@ -209,7 +209,9 @@ template <typename A>
 __global__ void gather_add_rows_kernel(const float* __restrict__ resid, const A* __restrict__ delta,
                                        const int* __restrict__ rows, float* __restrict__ out,
                                        int hidden) {
-    pdl_wait();
+    const unsigned long long waited = pdl_wait();
+    resid = pdl_after(resid, waited);
+    delta = pdl_after(delta, waited);
     const size_t src = (size_t)rows[blockIdx.x] * hidden;
     const size_t dst = (size_t)blockIdx.x * hidden;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
@@ -237,7 +239,7 @@ MSTAR_API int mstar_gather_add_rows(const float* resid, const void* delta, int a
 template <typename A>
 __global__ void silu_mul_kernel(const A* __restrict__ gate_up, A* __restrict__ out, int inter,
                                 size_t total) {
-    pdl_wait();
+    gate_up = pdl_after(gate_up, pdl_wait());
     for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
          idx += (size_t)gridDim.x * blockDim.x) {
         const size_t row = idx / inter;

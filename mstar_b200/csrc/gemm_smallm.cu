@@ -27,8 +27,10 @@
 __device__ __forceinline__ uint4 ld_stream(const bf16* p) {
     return __ldcs(reinterpret_cast<const uint4*>(p));
 }
+// x: an ordinary load (cached in L1, coherent after the dependency wait; not __ldg, which is
+// for memory that does not change while the kernel lives)
 __device__ __forceinline__ uint4 ld_cached(const bf16* p) {
-    return __ldg(reinterpret_cast<const uint4*>(p));
+    return *reinterpret_cast<const uint4*>(p);
 }
 
 template <typename T> __device__ __forceinline__ void store_out(T* p, float v);

@@ -165,7 +165,10 @@ smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
     }
 
     // ---------------------------------------------------------------------- consumers
-    pdl_wait();                           // x is the output of the kernel before
+    // x is the output of the kernel before: its addresses are formed from the wait's result and
+    // it is read with ordinary loads (a kernel launched early lives while x is being written,
+    // which loads of never-changing memory, __ldg, do not allow)
+    x = pdl_after(x, pdl_wait());
     const int g = lane >> 2, t = lane & 3;
     const bf16* xa = x + (size_t)min(g, M - 1) * ldx + 8 * t;
     const bf16* xb = x + (size_t)min(g + 8, M - 1) * ldx + 8 * t;
@@ -177,8 +180,8 @@ smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
             const int k = ch * SB_KC + (warp + u * SB_WARPS) * 32;
             xv[u] = xw[u] = make_uint4(0u, 0u, 0u, 0u);
             if (k < K) {
-                xv[u] = __ldg(reinterpret_cast<const uint4*>(xa + k));
-                if (M16) xw[u] = __ldg(reinterpret_cast<const uint4*>(xb + k));
+                xv[u] = *reinterpret_cast<const uint4*>(xa + k);
+                if (M16) xw[u] = *reinterpret_cast<const uint4*>(xb + k);
             }
         }
     };

@@ -75,7 +75,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int vocab,
               unsigned char* __restrict__ seen_mask, const int* __restrict__ seen_rows,
               const long long* __restrict__ seed, const long long* __restrict__ offset,
               int* __restrict__ out) {
-    pdl_wait();
+    logits = pdl_after(logits, pdl_wait());   // written by the kernel before
     __shared__ float fs[32];
     __shared__ int is[32];
     __shared__ float best_v[32];
@@ -357,7 +357,7 @@ sample_cluster_kernel(const float* __restrict__ logits, int ld, int vocab, int c
                       unsigned char* __restrict__ seen_mask, const int* __restrict__ seen_rows,
                       const long long* __restrict__ seed, const long long* __restrict__ offset,
                       int* __restrict__ out) {
-    pdl_wait();
+    logits = pdl_after(logits, pdl_wait());   // written by the kernel before
     cg::cluster_group cluster = cg::this_cluster();
     extern __shared__ __align__(16) unsigned char cs_smem[];
     float* sv = reinterpret_cast<float*>(cs_smem);                  // penalised logits [chunk]
@@ -605,7 +605,7 @@ MSTAR_API int mstar_sample(const float* logits, int ld, int rows, int vocab,
 // Greedy only: argmax of each row (smallest index among equal maxima).
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out) {
-    pdl_wait();
+    logits = pdl_after(logits, pdl_wait());   // written by the kernel before
     __shared__ float best_v[32];
     __shared__ int best_i[32];
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;

@@ -384,11 +384,7 @@ def _gemm_smallm(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, gated
     else:
         code = lib.get("gemm_smallm").mstar_gemm_smallm_bf16(
             x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), w.stride(0),
-            out.stride(0), int(gated), _dt(out), 0, _stream())
-        # the comparison kernel is not given the promise of static weights: with it (weights
-        # read before the wait for the kernel before) decode steps of the engine came out
-        # wrong under programmatic dependent launch, while the kernel alone and in short
-        # chains did not; the cause was not found, and this kernel is not on the product path
+            out.stride(0), int(gated), _dt(out), int(static_weights), _stream())
         what = "gemm_smallm"
     if code == -1:
         raise KernelError(f"small-M GEMM refuses M={m}, N={n}, K={k}")
