@@ -156,3 +156,26 @@ def test_long_request_in_portions_then_decoded(long_request, dtype):
     print(f"long request [{dtype}]: worst abs error {worst:.3e}")
     del model
     torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("switch", [("MSTAR_SMALLM", "registers"), ("MSTAR_FUSED_ROPE", "0"),
+                                    ("MSTAR_DECODE_ATTENTION", "per_item")])
+def test_measurement_switches_at_these_sizes(big, switch, monkeypatch):
+    """The kernels a measurement switch selects instead of the default ones (register-load
+    small-M products, the first product and the rotary kernel apart, decode attention with
+    one CTA per item), on the mixed trace in bfloat16, within the same tolerances."""
+    from mstar_b200.engine.model import load_model
+    from mstar_b200.engine.step import make_stepper
+
+    monkeypatch.setenv(*switch)
+    size, cfg, tensors, reqs, want = big
+    tol, mean_tol = TOLS[size]["bfloat16"]
+    model = load_model(None, dtype="bfloat16", device="cuda:0", config=cfg, tensors=tensors)
+    steps = only_wanted(H.mixed(reqs, seed=1, prompt_frac=0.8), want)
+    pages = H.max_tokens_of(steps, 16) // 16
+    stepper = make_stepper(model, page_size=16, num_pages=pages, num_slots=4)
+    got = H.run_steps_in_process(stepper, steps)
+    assert set(got) == set(want)
+    H.compare(got, want, "bfloat16", f"{size}-sized layers, {switch[0]}", tol=tol, mean_tol=mean_tol)
+    del model
+    torch.cuda.empty_cache()

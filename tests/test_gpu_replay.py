@@ -176,3 +176,18 @@ def test_decode_steps_replay_cuda_graphs_with_the_same_logits(model_folders, dty
         tol = 1e-6 if dtype == "float32" else H.TOL["bfloat16"]
         for key, row in outs[False].items():
             assert (row - outs[True][key]).abs().max().item() <= tol, key
+
+
+@pytest.mark.parametrize("switch", [("MSTAR_SMALLM", "registers"), ("MSTAR_FUSED_ROPE", "0"),
+                                    ("MSTAR_DECODE_ATTENTION", "per_item")])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_other_kernels_of_a_measurement_switch_give_the_same_model(model_folders, name, switch,
+                                                                  monkeypatch):
+    """The kernels that the measurement switches select instead of the default ones run the
+    same requests within the same tolerances: decode steps (single tokens, where the
+    small-M products, the fused first product and the decode attention are chosen) and a
+    mixed batch, in bfloat16."""
+    monkeypatch.setenv(*switch)
+    reqs, _ = get_requests(model_folders, name)
+    run(model_folders, name, "bfloat16", H.prefill_then_decode(reqs, 32), f"{switch[0]}: decode")
+    run(model_folders, name, "bfloat16", H.mixed(reqs, seed=0), f"{switch[0]}: mixed")
