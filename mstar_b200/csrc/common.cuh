@@ -105,7 +105,9 @@ static inline int launch_status() { return (int)cudaGetLastError(); }
 // 2.12 ms); the norm kernel leaves it to its end (calling it at its top lets the product
 // after it crowd in on the product before it: 2.37 ms).  Calling it at the top of every kernel lets waiting successors
 // pile up on the SMs and was slower than no overlap at all (2.93 ms).  Every kernel calls
-// pdl_wait() before it touches global memory.  MSTAR_PDL=0 launches everything with full
+// pdl_wait() before it touches what the kernel before it wrote; what that kernel did not
+// write (model weights, the step's index arrays, keys of earlier steps, the residual when the
+// caller says so) may be read before.  MSTAR_PDL=0 launches everything with full
 // serialization (the calls in the kernels are then no-ops).
 __device__ __forceinline__ void pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
