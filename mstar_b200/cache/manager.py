@@ -21,7 +21,7 @@ import numpy as np
 
 from ..ops.build import build_library
 
-_OK, _NO_SLOT, _DUPLICATE, _UNKNOWN, _NO_PAGES, _BAD_ARG = 0, -1, -2, -3, -4, -5
+_OK, _NO_SLOT, _DUPLICATE, _UNKNOWN, _NO_PAGES, _BAD_ARG, _TOO_LONG = 0, -1, -2, -3, -4, -5, -6
 
 
 class CacheExhausted(RuntimeError):
@@ -33,6 +33,11 @@ class CacheExhausted(RuntimeError):
     def __init__(self, short_by: Sequence[int]):
         self.short_by = list(short_by)
         super().__init__(f"cache pages exhausted: short by {self.short_by} pages per group")
+
+
+class SequenceTooLong(ValueError):
+    """A batch would give a token a position beyond what the model was built for
+    (``max_position_embeddings``); nothing was changed."""
 
 
 class NoFreeSlot(RuntimeError):
@@ -92,6 +97,14 @@ def _host_lib():
     lib.cm_reserve.argtypes = [vp, i32, pi64, pi32, pi64]
     lib.cm_commit.restype = i32
     lib.cm_commit.argtypes = [vp, i64, i32]
+    lib.cm_commit_positions.restype = i32
+    lib.cm_commit_positions.argtypes = [vp, i64, i32, i64]
+    lib.cm_position.restype = i64
+    lib.cm_position.argtypes = [vp, i64]
+    lib.cm_set_position.restype = i32
+    lib.cm_set_position.argtypes = [vp, i64, i64]
+    lib.cm_set_max_positions.restype = i32
+    lib.cm_set_max_positions.argtypes = [vp, i64]
     lib.cm_len.restype = i64
     lib.cm_len.argtypes = [vp, i64]
     lib.cm_slot.restype = i32
@@ -143,6 +156,16 @@ class CacheManager:
             raise ValueError("cache manager rejected its configuration")
         self._ids: dict[Hashable, int] = {}
         self._next = 1
+        self.max_positions: Optional[int] = None
+
+    def set_max_positions(self, max_positions: Optional[int]) -> None:
+        """No token may get a position id >= ``max_positions`` (None: no limit): ``reserve``
+        refuses such a batch with ``SequenceTooLong``.  The reference sizes its sequences by
+        the model's max_position_embeddings (mstar/model/orpheus/orpheus_model.py:88-95)."""
+        rc = self._lib.cm_set_max_positions(self._h, int(max_positions or 0))
+        if rc != _OK:
+            raise ValueError(f"bad position limit {max_positions}")
+        self.max_positions = int(max_positions) if max_positions else None
 
     def __del__(self):
         h, self._h = getattr(self, "_h", None), None
@@ -201,13 +224,25 @@ class CacheManager:
         rc = self._lib.cm_reserve(self._h, len(requests), rids, _i32(list(n_new)), short)
         if rc == _NO_PAGES:
             raise CacheExhausted([int(short[i]) for i in range(len(self.groups))])
+        if rc == _TOO_LONG:
+            who = requests[int(short[0])]
+            raise SequenceTooLong(
+                f"request {who!r} would pass position {self.max_positions}, the most the model "
+                f"was built for (it is at {self.position(who)} and brings "
+                f"{list(n_new)[int(short[0])]} tokens)")
         if rc == _BAD_ARG:
             raise ValueError("a request appears twice in the batch, or a token count is negative")
         if rc != _OK:
             raise RuntimeError(f"cm_reserve failed with {rc}")
 
-    def commit(self, request: Hashable, n_new: int) -> None:
-        rc = self._lib.cm_commit(self._h, self._rid(request), int(n_new))
+    def commit(self, request: Hashable, n_new: int, pos_advance: Optional[int] = None) -> None:
+        """The forward pass over ``n_new`` tokens is done: the length advances by ``n_new``,
+        the position counter by ``pos_advance`` (None: by ``n_new`` as well; the reference
+        lets a model advance positions on its own, mstar/engine/cache_manager.py:777-808)."""
+        if pos_advance is not None and pos_advance < 0:
+            raise ValueError("pos_advance must be >= 0")
+        rc = self._lib.cm_commit_positions(self._h, self._rid(request), int(n_new),
+                                           -1 if pos_advance is None else int(pos_advance))
         if rc == _BAD_ARG:
             raise ValueError(f"commit of {n_new} tokens for {request!r} without reserved pages")
         if rc != _OK:
@@ -216,6 +251,16 @@ class CacheManager:
     # -- queries ----------------------------------------------------------
     def length(self, request: Hashable) -> int:
         return int(self._lib.cm_len(self._h, self._rid(request)))
+
+    def position(self, request: Hashable) -> int:
+        """Position id of the request's next token; equal to ``length`` unless a commit
+        advanced the two differently or ``set_position`` moved it."""
+        return int(self._lib.cm_position(self._h, self._rid(request)))
+
+    def set_position(self, request: Hashable, position: int) -> None:
+        rc = self._lib.cm_set_position(self._h, self._rid(request), int(position))
+        if rc != _OK:
+            raise ValueError(f"cannot set the position counter of {request!r} to {position}")
 
     def slot(self, request: Hashable) -> int:
         return int(self._lib.cm_slot(self._h, self._rid(request)))

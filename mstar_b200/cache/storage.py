@@ -40,6 +40,19 @@ def plan_groups(needs: Sequence[CacheNeed]):
     return windows, group_of
 
 
+def group_page_sizes(page_size, num_groups: int) -> list:
+    """One page size per group from one int for all, or a sequence with one per group."""
+    if isinstance(page_size, int):
+        sizes = [page_size] * num_groups
+    else:
+        sizes = [int(p) for p in page_size]
+        if len(sizes) != num_groups:
+            raise ValueError(f"{num_groups} cache groups but {len(sizes)} page sizes")
+    if any(p <= 0 for p in sizes):
+        raise ValueError(f"page sizes must be positive, got {sizes}")
+    return sizes
+
+
 def bytes_per_page(needs: Sequence[CacheNeed], group_of, group: int, page_size: int,
                    dtype: torch.dtype) -> int:
     item = torch.empty((), dtype=dtype).element_size()
@@ -52,20 +65,22 @@ def bytes_per_page(needs: Sequence[CacheNeed], group_of, group: int, page_size: 
 
 class CacheStorage:
     def __init__(self, needs: Sequence[Optional[CacheNeed]], dtype: torch.dtype,
-                 device: torch.device, page_size: int, num_pages, num_slots: int):
-        """``num_pages``: one int for every group, or a list with one per group."""
+                 device: torch.device, page_size, num_pages, num_slots: int):
+        """``page_size`` and ``num_pages``: one int for every group, or a list with one per
+        group (a group of windowed layers may want smaller pages than one that keeps every
+        key: it gives them back sooner)."""
         self.needs = list(needs)
         self.dtype = dtype
         self.device = device
-        self.page_size = int(page_size)
         self.num_slots = int(num_slots)
         self.windows, self.group_of = plan_groups(self.needs)
+        self.page_sizes = group_page_sizes(page_size, len(self.windows))
         if isinstance(num_pages, int):
             num_pages = [num_pages] * len(self.windows)
         if len(num_pages) != len(self.windows):
             raise ValueError(f"{len(self.windows)} cache groups but {len(num_pages)} page counts")
-        self.group_configs = [GroupConfig(self.page_size, int(n), w)
-                              for n, w in zip(num_pages, self.windows)]
+        self.group_configs = [GroupConfig(p, int(n), w)
+                              for p, n, w in zip(self.page_sizes, num_pages, self.windows)]
         self.manager = CacheManager(self.group_configs, self.num_slots)
         self.kv: list = []
         self.state: list = []
@@ -77,7 +92,7 @@ class CacheStorage:
                 # fixed-shape (CUDA graph) batches write their keys there
                 n = self.group_configs[g].num_pages + 1
                 self.kv.append(torch.zeros(
-                    (n, 2, need.kv.num_kv_heads, self.page_size, need.kv.head_dim),
+                    (n, 2, need.kv.num_kv_heads, self.page_sizes[g], need.kv.head_dim),
                     dtype=dtype, device=device))
             if need is not None and need.state is not None:
                 self.state.append(torch.zeros((self.num_slots + 1,) + tuple(need.state.shape),
@@ -105,6 +120,7 @@ class CacheStorage:
 
     def layer_cache(self, cache_id: int, block_tables: Sequence[torch.Tensor]) -> LayerCache:
         g = self.group_of[cache_id]
-        return LayerCache(kv=self.kv[cache_id], page_size=self.page_size,
+        return LayerCache(kv=self.kv[cache_id],
+                          page_size=0 if g is None else self.page_sizes[g],
                           block_table=None if g is None else block_tables[g],
                           state=self.state[cache_id])

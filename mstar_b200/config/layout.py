@@ -91,6 +91,28 @@ class GatedMLPSpec:
 
 
 @dataclass(frozen=True)
+class EmbeddingSpec:
+    """kind "table": the residual starts as ``table[token] * multiplier`` in float."""
+
+    kind: str = "table"
+    vocab_size: int = 0
+    hidden_size: int = 0
+    multiplier: float = 1.0
+
+
+@dataclass(frozen=True)
+class HeadSpec:
+    """kind "linear": ``logits = x W^T * logit_scale``, then ``softcap * tanh(logits /
+    softcap)`` when a soft cap is given; float logits."""
+
+    kind: str = "linear"
+    vocab_size: int = 0
+    hidden_size: int = 0
+    logit_scale: float = 1.0
+    softcap: Optional[float] = None
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One set of layer weights and how its parts are wired.
 
@@ -128,6 +150,19 @@ class ModelLayout:
     order: Sequence[RunEntry]
     final_norm: NormSpec
     tie_word_embeddings: bool = False
+    # position ids run over [0, max_positions); None: no limit is known
+    max_positions: Optional[int] = None
+    # what turns token ids into the residual and normed rows into logits; None: a plain
+    # table and a plain linear head of the layout's sizes
+    embedding: Optional[object] = None
+    head: Optional[object] = None
+
+    def embedding_spec(self):
+        return self.embedding or EmbeddingSpec(vocab_size=self.vocab_size,
+                                               hidden_size=self.hidden_size)
+
+    def head_spec(self):
+        return self.head or HeadSpec(vocab_size=self.vocab_size, hidden_size=self.hidden_size)
 
     def num_caches(self) -> int:
         return 1 + max((e.cache for e in self.order), default=-1)

@@ -155,7 +155,8 @@ class LlamaConfig(ModelConfig):
         order = [RunEntry(block=i, cache=i) for i in range(self.num_hidden_layers)]
         layout = ModelLayout(vocab_size=self.vocab_size, hidden_size=self.hidden_size,
                              blocks=blocks, order=order, final_norm=norm,
-                             tie_word_embeddings=self.tie_word_embeddings)
+                             tie_word_embeddings=self.tie_word_embeddings,
+                             max_positions=self.max_position_embeddings)
         layout.validate()
         return layout
 

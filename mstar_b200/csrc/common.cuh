@@ -126,6 +126,21 @@ template <typename T> __device__ __forceinline__ T* pdl_after(T* p, unsigned lon
     return reinterpret_cast<T*>(reinterpret_cast<unsigned long long>(p) + zero_of_wait);
 }
 
+// Number of SMs of the current device, asked once per device (grids are sized from it).
+static inline int device_sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 0;
+    if (cached[dev] <= 0) {
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess ||
+            sms <= 0)
+            return 1;
+        cached[dev] = sms;
+    }
+    return cached[dev];
+}
+
 static inline int pdl_enabled() {
     static int v = -1;
     if (v < 0) {

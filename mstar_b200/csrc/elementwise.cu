@@ -17,7 +17,7 @@
 template <typename W>
 __global__ void embed_rows_kernel(const W* __restrict__ table, const int* __restrict__ ids,
                                   const int* __restrict__ src, const int* __restrict__ prev,
-                                  float* __restrict__ out, int vocab, int hidden) {
+                                  float* __restrict__ out, int vocab, int hidden, float scale) {
     prev = pdl_after(prev, pdl_wait());       // sampled by the step before
     const int t = blockIdx.x;
     int id = ids[t];
@@ -31,24 +31,27 @@ __global__ void embed_rows_kernel(const W* __restrict__ table, const int* __rest
         return;
     }
     const W* row = table + (size_t)id * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(row[i]);
+    if (scale == 1.f)
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(row[i]);
+    else
+        for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = to_float(row[i]) * scale;
 }
 
 // `src` and `prev` are both null or both given (src: [num_tokens] ints, -1 where ids holds
-// the token; prev: int tokens on the device).
+// the token; prev: int tokens on the device).  Rows are multiplied by `scale` in float.
 MSTAR_API int mstar_embed_rows(const void* table, int table_dtype, const int* ids, const int* src,
                                const int* prev, float* out, int num_tokens, int vocab, int hidden,
-                               void* stream) {
+                               float scale, void* stream) {
     if (num_tokens <= 0) return 0;
     if ((src == nullptr) != (prev == nullptr)) return -1;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (table_dtype == MSTAR_F32)
         mstar_launch((embed_rows_kernel<float>), dim3(num_tokens), dim3(threads), 0, s, (const float*)table, ids,
-                     src, prev, out, vocab, hidden);
+                     src, prev, out, vocab, hidden, scale);
     else
         mstar_launch((embed_rows_kernel<bf16>), dim3(num_tokens), dim3(threads), 0, s, (const bf16*)table, ids,
-                     src, prev, out, vocab, hidden);
+                     src, prev, out, vocab, hidden, scale);
     return launch_status();
 }
 
@@ -259,11 +262,35 @@ MSTAR_API int mstar_silu_mul(const void* gate_up, void* out, int act_dtype, int 
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = 256;
     size_t blocks = (total + threads - 1) / threads;
-    if (blocks > 148 * 32) blocks = 148 * 32;
+    const size_t most = (size_t)device_sm_count() * 32;   // a grid-stride loop takes the rest
+    if (blocks > most) blocks = most;
     if (act_dtype == MSTAR_F32)
         mstar_launch((silu_mul_kernel<float>), dim3((int)blocks), dim3(threads), 0, s, (const float*)gate_up, (float*)out, inter, total);
     else
         mstar_launch((silu_mul_kernel<bf16>), dim3((int)blocks), dim3(threads), 0, s, (const bf16*)gate_up, (bf16*)out, inter, total);
+    return launch_status();
+}
+
+// ------------------------------------------------- logit scale and soft cap
+// x = x * scale, then x = cap * tanh(x / cap) when cap > 0; float, in place.
+__global__ void scale_softcap_kernel(float* __restrict__ x, size_t n, float scale, float cap) {
+    x = pdl_after(x, pdl_wait());
+    const float inv_cap = cap > 0.f ? 1.f / cap : 0.f;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+         i += (size_t)gridDim.x * blockDim.x) {
+        float v = x[i] * scale;
+        if (cap > 0.f) v = cap * tanhf(v * inv_cap);
+        x[i] = v;
+    }
+}
+
+MSTAR_API int mstar_scale_softcap(float* x, long long n, float scale, float cap, void* stream) {
+    if (n <= 0) return 0;
+    size_t blocks = ((size_t)n + 255) / 256;
+    const size_t most = (size_t)device_sm_count() * 32;
+    if (blocks > most) blocks = most;
+    mstar_launch(scale_softcap_kernel, dim3((int)blocks), dim3(256), 0, (cudaStream_t)stream, x,
+                 (size_t)n, scale, cap);
     return launch_status();
 }
 
@@ -280,7 +307,8 @@ MSTAR_API int mstar_convert(const void* src, int src_dtype, void* dst, int dst_d
     if (n <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     size_t blocks = ((size_t)n + 255) / 256;
-    if (blocks > 148 * 32) blocks = 148 * 32;
+    const size_t most = (size_t)device_sm_count() * 32;   // a grid-stride loop takes the rest
+    if (blocks > most) blocks = most;
     if (src_dtype == MSTAR_F32 && dst_dtype == MSTAR_BF16)
         convert_kernel<float, bf16><<<(int)blocks, 256, 0, s>>>((const float*)src, (bf16*)dst, (size_t)n);
     else if (src_dtype == MSTAR_BF16 && dst_dtype == MSTAR_F32)

@@ -8,7 +8,10 @@
 // (cache_manager.py:278-285, 811-838); everything a request holds returns to the
 // pool when it is removed (kv_store.py:606-614).
 // What it adds: several groups of layers, each with a pool, a page size and an
-// optional window of its own; pages that a window has passed are given back while
+// optional window of its own; a position counter per request that is kept apart from
+// the number of cached tokens (the reference's position_id_start beside seq_len,
+// kv_store.py:112-116, advanced on its own by set_custom_pos_advance,
+// cache_manager.py:777-808); pages that a window has passed are given back while
 // the request is still running; reservation of a whole batch is all-or-nothing
 // (the reference leaves earlier requests of a failed batch extended,
 // kv_store.py:463-482); a pool of fixed-size state slots, one per live request.
@@ -29,6 +32,7 @@ constexpr int kDuplicate = -2;
 constexpr int kUnknown = -3;
 constexpr int kNoPages = -4;
 constexpr int kBadArg = -5;
+constexpr int kTooLong = -6;
 
 struct Group {
     int page_size = 0;
@@ -40,7 +44,8 @@ struct Group {
 
 struct Request {
     int slot = -1;
-    int64_t len = 0;                       // committed tokens
+    int64_t len = 0;                       // committed tokens (keys in the cache)
+    int64_t pos = 0;                       // position id of the next token
     std::vector<std::vector<int>> table;   // [group][logical page] -> page id or -1
 };
 
@@ -49,6 +54,7 @@ struct Manager {
     std::deque<int> free_slots;
     std::vector<int64_t> slot_owner;
     std::unordered_map<int64_t, Request> requests;
+    int64_t max_positions = 0;  // 0: no limit; else no token gets a position id >= this
     std::mutex mu;
 };
 
@@ -111,6 +117,18 @@ MSTAR_API void* cm_create(int n_groups, const int* page_sizes, const int* num_pa
 }
 
 MSTAR_API void cm_destroy(void* h) { delete static_cast<Manager*>(h); }
+
+// The number of positions the model was built for (the reference derives max_seq_len
+// from max_position_embeddings, mstar/model/orpheus/orpheus_model.py:88-95): a
+// reservation that would give a token a position id at or beyond it is refused with
+// kTooLong.  0 lifts the limit.
+MSTAR_API int cm_set_max_positions(void* h, int64_t max_positions) {
+    auto& m = *static_cast<Manager*>(h);
+    std::lock_guard<std::mutex> lock(m.mu);
+    if (max_positions < 0) return kBadArg;
+    m.max_positions = max_positions;
+    return kOk;
+}
 
 MSTAR_API int cm_add_request(void* h, int64_t rid) {
     auto& m = *static_cast<Manager*>(h);
@@ -181,6 +199,10 @@ MSTAR_API int cm_reserve(void* h, int n, const int64_t* rids, const int* n_new,
         if (it == m.requests.end()) return kUnknown;
         for (int j = 0; j < i; ++j)
             if (rids[j] == rids[i]) return kBadArg;
+        if (m.max_positions > 0 && it->second.pos + n_new[i] > m.max_positions) {
+            if (short_by) short_by[0] = i;  // which entry of the batch is too long
+            return kTooLong;
+        }
         reqs[i] = &it->second;
         for (size_t gi = 0; gi < ng; ++gi)
             need[gi] += new_pages_needed(m.groups[gi], it->second, (int)gi, n_new[i]);
@@ -208,9 +230,10 @@ MSTAR_API int cm_reserve(void* h, int n, const int64_t* rids, const int* n_new,
     return kOk;
 }
 
-// The forward pass over n_new tokens is done: advance the length and give back the
+// The forward pass over n_new tokens is done: advance the length by n_new and the
+// position counter by pos_advance (negative: by n_new as well), and give back the
 // pages of windowed groups that no later token can see.
-MSTAR_API int cm_commit(void* h, int64_t rid, int n_new) {
+MSTAR_API int cm_commit_positions(void* h, int64_t rid, int n_new, int64_t pos_advance) {
     auto& m = *static_cast<Manager*>(h);
     std::lock_guard<std::mutex> lock(m.mu);
     auto it = m.requests.find(rid);
@@ -222,7 +245,31 @@ MSTAR_API int cm_commit(void* h, int64_t rid, int n_new) {
         if (r.len + n_new > cap) return kBadArg;  // commit without reserve
     }
     r.len += n_new;
+    r.pos += pos_advance < 0 ? n_new : pos_advance;
     release_passed(m, rid, r);
+    return kOk;
+}
+
+MSTAR_API int cm_commit(void* h, int64_t rid, int n_new) {
+    return cm_commit_positions(h, rid, n_new, -1);
+}
+
+// The position id that the request's next token gets (equal to its length unless a
+// commit advanced the two differently or cm_set_position moved it).
+MSTAR_API int64_t cm_position(void* h, int64_t rid) {
+    auto& m = *static_cast<Manager*>(h);
+    std::lock_guard<std::mutex> lock(m.mu);
+    auto it = m.requests.find(rid);
+    return it == m.requests.end() ? (int64_t)kUnknown : it->second.pos;
+}
+
+MSTAR_API int cm_set_position(void* h, int64_t rid, int64_t pos) {
+    auto& m = *static_cast<Manager*>(h);
+    std::lock_guard<std::mutex> lock(m.mu);
+    auto it = m.requests.find(rid);
+    if (it == m.requests.end()) return kUnknown;
+    if (pos < 0) return kBadArg;
+    it->second.pos = pos;
     return kOk;
 }
 
@@ -291,8 +338,9 @@ MSTAR_API int cm_batch_widths(void* h, int n, const int64_t* rids, int* widths) 
 
 // Per-step index arrays for a reserved batch, written into caller memory (int32):
 //   token_req[T]  entry of the batch each token belongs to
-//   positions[T]  position id of each token (committed length + offset in portion)
+//   positions[T]  position id of each token (position counter + offset in portion)
 //   cache_pos[T]  index of the token's key in the request's key sequence
+//                 (committed length + offset in portion)
 //   qo_indptr[n+1], kv_len[n] (length after this step), slots[n]
 //   tables[g]     [n, widths[g]] block tables, -1 where no page is held
 MSTAR_API int cm_fill_batch(void* h, int n, const int64_t* rids, const int* n_new,
@@ -308,7 +356,7 @@ MSTAR_API int cm_fill_batch(void* h, int n, const int64_t* rids, const int* n_ne
         const Request& r = it->second;
         for (int k = 0; k < n_new[i]; ++k, ++t) {
             token_req[t] = i;
-            positions[t] = (int)(r.len + k);
+            positions[t] = (int)(r.pos + k);
             cache_pos[t] = (int)(r.len + k);
         }
         qo_indptr[i + 1] = t;

@@ -18,7 +18,8 @@ from typing import Hashable, Optional, Sequence
 
 import torch
 
-from ..cache.storage import CacheStorage, bytes_per_page, plan_groups
+from .. import ops
+from ..cache.storage import CacheStorage, bytes_per_page, group_page_sizes, plan_groups
 from ..config.base import GenerationDefaults
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler
@@ -53,8 +54,9 @@ class LLM:
                  max_concurrent_requests: Optional[int] = 64, max_batch_size: int = 64,
                  log_stats: bool = False):
         """``model``: a folder with config.json and safetensors, or a built ``Model``.
-        ``max_num_pages``: pages of ``page_size`` tokens per cache group; None sizes
-        the pool from ``kv_cache_memory_fraction`` of the memory free after loading."""
+        ``page_size`` and ``max_num_pages``: tokens per page and pages of a cache group, one
+        number for all groups or a list with one per group; ``max_num_pages`` None sizes the
+        pools from ``kv_cache_memory_fraction`` of the memory free after loading."""
         self.model: Model = model if isinstance(model, Model) else load_model(
             model, dtype=dtype, device=device)
         self.device = self.model.runtime.device
@@ -70,7 +72,8 @@ class LLM:
         self.scheduler = Scheduler(
             SchedulerConfig(max_num_batched_tokens=max_num_batched_tokens,
                             max_concurrent_requests=max_concurrent_requests,
-                            max_batch_size=max_batch_size),
+                            max_batch_size=max_batch_size,
+                            max_seq_len=self.model.max_positions),
             storage.manager, stops, admit=self.stepper.add_request,
             release=self._release)
         self.log_stats = log_stats
@@ -83,20 +86,23 @@ class LLM:
         self.pipelined_steps = 0
         self._reported = 0              # finished requests handed to the caller so far
         # pinned landing places of the sampled tokens: two steps can be under way
-        self._host_tokens = [torch.empty(max(max_batch_size, 1), dtype=torch.int32, pin_memory=True)
-                             for _ in range(3)]
+        # (one more element than tokens: the device's error word travels with them)
+        self._host_tokens = [torch.empty(max(max_batch_size, 1) + 1, dtype=torch.int32,
+                                         pin_memory=True) for _ in range(3)]
+        self._error_word = ops.tcgen05_error_word(self.device)
         self._turn = 0
         self._copy_stream = torch.cuda.Stream(device=self.device)
 
-    def _pages_from_memory(self, page_size: int, fraction: float) -> list:
+    def _pages_from_memory(self, page_size, fraction: float) -> list:
         free, _ = torch.cuda.mem_get_info(self.device)
         windows, group_of = plan_groups(self.model.cache_needs)
         if not windows:
             return []
+        sizes = group_page_sizes(page_size, len(windows))
         per_group = int(free * fraction) // len(windows)
         pages = []
         for g in range(len(windows)):
-            b = bytes_per_page(self.model.cache_needs, group_of, g, page_size,
+            b = bytes_per_page(self.model.cache_needs, group_of, g, sizes[g],
                                self.model.runtime.dtype)
             pages.append(max(per_group // max(b, 1), 1))
         return pages
@@ -167,16 +173,19 @@ class LLM:
         # their copy to the host is queued now, before the next step is: reading it later
         # waits for this step only
         turn = self._turn = (self._turn + 1) % len(self._host_tokens)
-        if self._host_tokens[turn].numel() < len(sampling):
-            self._host_tokens[turn] = torch.empty(len(sampling), dtype=torch.int32, pin_memory=True)
-        host = self._host_tokens[turn][:len(sampling)]
+        if self._host_tokens[turn].numel() < len(sampling) + 1:
+            self._host_tokens[turn] = torch.empty(len(sampling) + 1, dtype=torch.int32,
+                                                  pin_memory=True)
+        host = self._host_tokens[turn][:len(sampling) + 1]
         # on a stream of its own, so that the next step's input copy and kernels do not
         # queue behind it (``tokens`` stays referenced until it has arrived)
         sampled = torch.cuda.Event()
         sampled.record()
         with torch.cuda.stream(self._copy_stream):
             self._copy_stream.wait_event(sampled)
-            host.copy_(tokens, non_blocking=True)
+            host[:-1].copy_(tokens, non_blocking=True)
+            # with the tokens comes the word that kernels set when a bounded wait ran out
+            host[-1:].copy_(self._error_word, non_blocking=True)
             arrived = torch.cuda.Event()
             arrived.record()
         return plan, sampling, tokens, host, arrived
@@ -218,7 +227,12 @@ class LLM:
         if prev is not None:
             old_plan, old_sampling, _, host, arrived = prev
             arrived.synchronize()
-            sampled = dict(zip(old_sampling, host.tolist()))
+            values = host.tolist()
+            if values[-1]:
+                # a kernel returned with partial output: these tokens are not to be trusted
+                self._error_word.zero_()
+                ops.raise_on_wait_code(values[-1])
+            sampled = dict(zip(old_sampling, values[:-1]))
             self.scheduler.resolve(old_plan, sampled)
             self.stats.generated_tokens += len(sampled)
         if self.log_stats:

@@ -3,7 +3,9 @@
 Built from a ``ModelLayout`` alone; which architecture produced the layout is
 not known here.  The forward pass follows the reference's language model
 (mstar/model/orpheus/components/language_model.py:72-83: embed, every layer, final
-norm) with the row selection moved before the final norm: only rows whose logits
+norm); the two ends, token ids to residual and normed rows to logits, are parts of their
+own, so that a scaled embedding or a capped head is a spec and not an edit here.  The row
+selection is moved before the final norm: only rows whose logits
 are wanted are normalised and multiplied by the head (the reference norms all rows
 and then selects the last one of each request, mstar/model/orpheus/submodules.py:
 225-231).
@@ -27,14 +29,19 @@ from ..weights.names import ParamSpec
 
 def model_param_specs(layout: ModelLayout) -> dict:
     """Engine parameter names and shapes of a layout (no GPU needed)."""
-    specs = {"embed.weight": ParamSpec((layout.vocab_size, layout.hidden_size), role="table")}
+    specs = {}
+    embedding = layout.embedding_spec()
+    for local, ps in part_class("embedding", embedding).param_specs(embedding).items():
+        specs[f"embed.{local}"] = ps
     for i, block in enumerate(layout.blocks):
         for local, ps in part_class("block", block).param_specs(block).items():
             specs[f"blocks.{i}.{local}"] = ps
     norm_cls = part_class("norm", layout.final_norm)
     for local, ps in norm_cls.param_specs(layout.final_norm).items():
         specs[f"final_norm.{local}"] = ps
-    specs["head.weight"] = ParamSpec((layout.vocab_size, layout.hidden_size))
+    head = layout.head_spec()
+    for local, ps in part_class("head", head).param_specs(head).items():
+        specs[f"head.{local}"] = ps
     return specs
 
 
@@ -63,21 +70,28 @@ class Model:
         self.layout = layout
         self.runtime = runtime
         self.params = params
-        self.embed = params["embed.weight"]
-        self.head = params["head.weight"]
+        self.embedding = build_part("embedding", layout.embedding_spec(), _sub(params, "embed"),
+                                    runtime)
+        self.head = build_part("head", layout.head_spec(), _sub(params, "head"), runtime)
         self.blocks = [build_part("block", spec, _sub(params, f"blocks.{i}"), runtime)
                        for i, spec in enumerate(layout.blocks)]
         self.final_norm = build_part("norm", layout.final_norm, _sub(params, "final_norm"),
                                      runtime)
         self.cache_needs = cache_needs(layout)
-        # a decode step may be captured as a CUDA graph only if every mixer says its
-        # forward pass reads nothing per-step from the host
-        self.graph_safe = all(getattr(b.mixer, "graph_safe", False) for b in self.blocks
-                              if hasattr(b, "mixer"))
+        # a decode step may be captured as a CUDA graph only if every block says that its
+        # forward pass reads nothing per-step from the host; a block that says nothing is
+        # taken as unsafe
+        self.graph_safe = all(getattr(p, "graph_safe", False) is True
+                              for p in (self.embedding, self.head, self.final_norm, *self.blocks))
 
     @property
     def vocab_size(self) -> int:
         return self.layout.vocab_size
+
+    @property
+    def max_positions(self) -> Optional[int]:
+        """Positions the model was built for (its layout says; None: no limit known)."""
+        return self.layout.max_positions
 
     def parameter_bytes(self) -> int:
         seen, total = set(), 0
@@ -91,7 +105,7 @@ class Model:
                 block_tables: Sequence[torch.Tensor],
                 want_rows: Optional[torch.Tensor]) -> torch.Tensor:
         """Run the tokens of one step; return float logits [len(want_rows), vocab]."""
-        stream = ResidualStream(ops.embed_rows(self.embed, token_ids, source=ctx.token_source))
+        stream = ResidualStream(self.embedding.forward(token_ids, ctx))
         for entry in self.layout.order:
             self.blocks[entry.block].forward(stream, ctx, storage.layer_cache(entry.cache,
                                                                                block_tables))
@@ -100,7 +114,7 @@ class Model:
                                device=self.runtime.device)
         rows = ops.gather_add_rows(stream.h, stream.take_delta(), want_rows)
         x = self.final_norm.norm_rows(rows)
-        return ops.linear(x, self.head, out_dtype=torch.float32, static_weights=True)
+        return self.head.forward(x)
 
 
 def resolve_dtype(dtype) -> torch.dtype:

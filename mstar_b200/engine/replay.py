@@ -45,6 +45,7 @@ def main(argv=None) -> int:
     import numpy as np
     import torch
 
+    from .. import ops
     from .model import load_model
     from .step import StepEntry, make_stepper
 
@@ -71,11 +72,13 @@ def main(argv=None) -> int:
                 stepper.add_request(e["id"])
             entries.append(StepEntry(e["id"], e["tokens"], e.get("want", [])))
         logits = stepper.step(entries)
+        host = None
         if logits.shape[0] > 0:
             host = logits.to("cpu", torch.float32).contiguous().numpy().astype("<f4", copy=False)
+        # a kernel whose bounded wait ran out has left partial output: fail, do not write on
+        ops.check_error_word(model.runtime.device)
+        if host is not None:
             host.tofile(out_dir / f"{step_id}.f32")
-        else:
-            torch.cuda.synchronize()
         for rid in record.get("end", []):
             if stepper.has_request(rid):
                 stepper.free_request(rid)

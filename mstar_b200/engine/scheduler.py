@@ -37,6 +37,9 @@ class SchedulerConfig:
     max_num_batched_tokens: int = 2048
     max_concurrent_requests: Optional[int] = None   # None: as many as there are slots
     max_batch_size: int = 64                        # requests per step
+    # positions the model was built for (max_position_embeddings; the reference's
+    # max_seq_len, mstar/model/orpheus/orpheus_model.py:88-95); None: no limit
+    max_seq_len: Optional[int] = None
 
     def validate(self) -> None:
         if self.max_num_batched_tokens < 1:
@@ -45,6 +48,8 @@ class SchedulerConfig:
             raise ValueError("max_batch_size must be >= 1")
         if self.max_concurrent_requests is not None and self.max_concurrent_requests < 1:
             raise ValueError("max_concurrent_requests must be >= 1")
+        if self.max_seq_len is not None and self.max_seq_len < 2:
+            raise ValueError("max_seq_len must be >= 2")
 
 
 @dataclass
@@ -58,6 +63,9 @@ class Request:
     finish_reason: Optional[str] = None
     slot: int = -1
     preemptions: int = 0
+    # most tokens it may generate: max_output_tokens, cut to what the model's positions
+    # leave after the prompt (set when the request is added)
+    output_limit: Optional[int] = None
 
     def all_tokens(self) -> list:
         return self.prompt + self.output
@@ -103,6 +111,17 @@ class Scheduler:
         if not request.prompt:
             raise ValueError(f"request {request.request_id!r} has an empty prompt")
         request.params.validate()
+        limit = request.params.max_output_tokens
+        longest = self.config.max_seq_len
+        if longest is not None:
+            if len(request.prompt) >= longest:
+                raise ValueError(
+                    f"request {request.request_id!r} has a prompt of {len(request.prompt)} "
+                    f"tokens; the model takes sequences of up to {longest} (prompt and "
+                    "generated tokens together)")
+            # it then finishes with reason "length" where the positions end
+            limit = min(limit, longest - len(request.prompt))
+        request.output_limit = limit
         request.status = "waiting"
         self.waiting.append(request)
 
@@ -323,7 +342,8 @@ class Scheduler:
             if not e.samples:
                 continue
             r.output.append(None)
-            if len(r.output) >= r.params.max_output_tokens and r.status == "running":
+            limit = r.params.max_output_tokens if r.output_limit is None else r.output_limit
+            if len(r.output) >= limit and r.status == "running":
                 self._finish(r, "length", held=True)
 
     def resolve(self, plan: StepPlan, sampled: dict) -> list:

@@ -158,6 +158,10 @@ class Stepper:
         self.model = model
         self.storage = storage
         self.manager = storage.manager
+        # sequences are as long as the model's positions reach (the reference derives
+        # max_seq_len from max_position_embeddings, mstar/model/orpheus/orpheus_model.py:
+        # 88-95): a step that would pass them raises SequenceTooLong, nothing changed
+        self.manager.set_max_positions(getattr(model, "max_positions", None))
         self.device = model.runtime.device
         self.steps = 0
         self.last_h2d_bytes = 0
@@ -191,7 +195,11 @@ class Stepper:
              device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Run one batch; returns float32 logits [number of wanted places, vocab] on
         the device, in the order of ``entries`` and of each entry's ``want``.
-        Raises ``CacheExhausted`` (nothing changed) if the pages do not suffice.
+        Raises ``CacheExhausted`` (nothing changed) if the pages do not suffice, and
+        ``SequenceTooLong`` (nothing changed) if a request would pass the model's positions.
+        The tensor returned by a step of single tokens may be a view of a captured graph's
+        output buffer: the next such step of the same shape overwrites it, so a caller that
+        keeps logits across steps copies them (``clone()``) first.
 
         ``pending``: entry index -> index into ``device_tokens`` (int32 on the device, the
         tokens the step before sampled).  Such an entry brings one token whose value the
@@ -309,15 +317,19 @@ class Stepper:
         return logits[torch.tensor(wanted, dtype=torch.long, device=self.device)]
 
 
-def make_stepper(model: Model, *, page_size: int = 16, num_pages: Optional[int] = None,
+def make_stepper(model: Model, *, page_size=16, num_pages=None,
                  max_tokens: Optional[int] = None, num_slots: int = 64,
                  cuda_graphs: bool = True) -> Stepper:
     """A stepper with a cache pool of ``num_pages`` pages per group, or enough pages
-    for ``max_tokens`` cached tokens."""
+    for ``max_tokens`` cached tokens.  ``page_size`` and ``num_pages``: one number for
+    every cache group, or a list with one per group."""
     if num_pages is None:
         if max_tokens is None:
             raise ValueError("give num_pages or max_tokens")
-        num_pages = -(-int(max_tokens) // page_size)
+        sizes = [page_size] if isinstance(page_size, int) else list(page_size)
+        num_pages = [-(-int(max_tokens) // p) for p in sizes]
+        if isinstance(page_size, int):
+            num_pages = num_pages[0]
     storage = CacheStorage(model.cache_needs, model.runtime.dtype, model.runtime.device,
-                           page_size, int(num_pages), num_slots)
+                           page_size, num_pages, num_slots)
     return Stepper(model, storage, cuda_graphs=cuda_graphs)

@@ -46,8 +46,8 @@ def _ptr(t) -> int:
 
 
 def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None,
-               source=None):
-    """out[t] = float(table[ids[t]]); the residual stream is float in both dtypes.
+               source=None, scale: float = 1.0):
+    """out[t] = float(table[ids[t]]) * scale; the residual stream is float in both dtypes.
     ``source`` = (src, prev): where src[t] >= 0 the token is prev[src[t]] instead, a token
     that is on the device only (int32 tensors, src as long as ids)."""
     _need_cuda(table, ids)
@@ -62,8 +62,17 @@ def embed_rows(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None 
         assert src.dtype == torch.int32 and prev.dtype == torch.int32 and src.numel() == n
     check(lib.get("elementwise").mstar_embed_rows(
         table.data_ptr(), _dt(table), ids.data_ptr(), _ptr(src), _ptr(prev), out.data_ptr(), n,
-        vocab, hidden, _stream()), "embed_rows")
+        vocab, hidden, float(scale), _stream()), "embed_rows")
     return out
+
+
+def scale_softcap(x: torch.Tensor, scale: float = 1.0, cap: float | None = None):
+    """In place on float ``x``: x *= scale, then x = cap * tanh(x / cap) if ``cap``."""
+    _need_cuda(x)
+    assert x.dtype == torch.float32 and x.is_contiguous()
+    check(lib.get("elementwise").mstar_scale_softcap(
+        x.data_ptr(), x.numel(), float(scale), float(cap or 0.0), _stream()), "scale_softcap")
+    return x
 
 
 def add_rmsnorm(resid: torch.Tensor, delta, weight: torch.Tensor, eps: float,
@@ -171,7 +180,17 @@ def paged_attention_generic(q: torch.Tensor, q_stride: int, out: torch.Tensor, k
 
 
 FAST_ATTENTION_HEAD_DIMS = (16, 32, 64, 128, 256)
-NUM_SMS = 148
+
+_sm_counts: dict = {}
+
+
+def num_sms(device=None) -> int:
+    """SMs of ``device`` (default: the current CUDA device), asked once per device."""
+    index = torch.cuda.current_device() if device is None else (
+        torch.device(device).index or 0)
+    if index not in _sm_counts:
+        _sm_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _sm_counts[index]
 
 
 def fast_attention_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int,
@@ -188,20 +207,22 @@ DECODE_FILL = 6
 RING_CTAS_PER_SM = 2
 
 
-def decode_split(tokens: int, num_kv_heads: int, max_len: int, ring: bool = False) -> tuple:
+def decode_split(tokens: int, num_kv_heads: int, max_len: int, ring: bool = False,
+                 sms: int | None = None) -> tuple:
     """(chunk, splits) of the keys for split-K decode attention, chunks in whole tiles of 64
     keys.  One CTA per work item (token, kv head, split): enough items to fill the GPU a
     few times over.  Persistent ring kernel: as many items as CTAs are resident or fewer
-    (each CTA then streams one item of equal size), of at least 128 keys."""
-    import os
-
+    (each CTA then streams one item of equal size), of at least 128 keys.  ``sms``: the
+    device's SM count (default: asked of the current device)."""
+    if sms is None:
+        sms = num_sms()
     pairs = max(tokens * num_kv_heads, 1)
     if ring:
-        want = max(1, (NUM_SMS * RING_CTAS_PER_SM) // pairs)
+        want = max(1, (sms * RING_CTAS_PER_SM) // pairs)
         chunk = max(128, -(-(-(-max_len // want)) // 64) * 64)
     else:
         fill = int(os.environ.get("MSTAR_DECODE_FILL", DECODE_FILL))
-        want = max(1, -(-NUM_SMS * fill // pairs))
+        want = max(1, -(-sms * fill // pairs))
         want = min(want, 256)                   # the merge kernel takes up to 256 splits
         chunk = max(64, -(-(-(-max_len // want)) // 64) * 64)
     splits = max(1, -(-max_len // chunk))
@@ -258,7 +279,8 @@ def paged_decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
     ring = kv_map is not None and os.environ.get("MSTAR_DECODE_ATTENTION") != "per_item"
     if not ring and page_size > 64:
         kv_map = None                       # the per-item TMA kernel copies whole pages
-    chunk, splits = decode_split(tokens, num_kv_heads, max(max_len, 1), ring=ring)
+    chunk, splits = decode_split(tokens, num_kv_heads, max(max_len, 1), ring=ring,
+                                 sms=num_sms(q.device))
     scratch = None
     if splits > 1:
         scratch = torch.empty(tokens * num_heads * splits * (head_dim + 2), dtype=torch.float32,
@@ -437,6 +459,42 @@ def tcgen05_error_word(device) -> torch.Tensor:
     if key not in _tc_error_words:
         _tc_error_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
     return _tc_error_words[key]
+
+
+WAIT_CODES = {
+    1: "tcgen05 GEMM: the producer waited for a free operand stage",
+    2: "tcgen05 GEMM: the MMA issuer waited for operand tiles",
+    3: "tcgen05 GEMM: the epilogue waited for an accumulator",
+    4: "decode attention: a wait for a key/value tile",
+    5: "attention: a wait for the query tile or a key/value tile copied by TMA",
+    13: "bulk-copy small-M GEMM: the producer waited for a free stage",
+    14: "bulk-copy small-M GEMM: a consumer waited for weights",
+}
+WAIT_CODES.update({c: "tcgen05 prefill attention: a wait on one of its barriers ran out"
+                   for c in range(6, 13)})
+
+
+def raise_on_wait_code(code: int) -> None:
+    """``code``: a value read from ``tcgen05_error_word``.  Non-zero means that a bounded
+    wait inside a kernel ran out and the kernel returned with partial output, so whatever
+    was computed since the word was last zero must not be used."""
+    code = int(code)
+    if code == 0:
+        return
+    what = WAIT_CODES.get(code, "an unknown kernel")
+    raise KernelError(f"a kernel gave up a bounded wait (code {code}: {what}); the results "
+                      "of the steps since the last check are not valid")
+
+
+def check_error_word(device) -> None:
+    """Read the device's error word (this waits for the work queued so far), zero it if it
+    is set, and raise ``KernelError`` naming the code.  The engine's entry points call this
+    (or read the word along with a step's results) before they hand results out."""
+    word = tcgen05_error_word(device)
+    code = int(word.item())
+    if code:
+        word.zero_()
+        raise_on_wait_code(code)
 
 
 def gemm_tcgen05(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,

@@ -19,7 +19,8 @@ _vp, _i, _f, _ll = _c.c_void_p, _c.c_int, _c.c_float, _c.c_longlong
 # library -> {function: argtypes}
 _SIGNATURES = {
     "elementwise": {
-        "mstar_embed_rows": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _vp],
+        "mstar_embed_rows": [_vp, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _f, _vp],
+        "mstar_scale_softcap": [_vp, _ll, _f, _f, _vp],
         "mstar_add_rmsnorm": [_vp, _vp, _vp, _i, _vp, _i, _i, _i, _f, _f, _i, _vp],
         "mstar_gather_add_rows": [_vp, _vp, _i, _vp, _vp, _i, _i, _vp],
         "mstar_silu_mul": [_vp, _vp, _i, _i, _i, _vp],

@@ -38,6 +38,9 @@ class PreNormBlock:
         self.mixer = build_part("mixer", spec.mixer, _sub(params, "mixer"), runtime)
         self.norm2 = build_part("norm", spec.norm2, _sub(params, "norm2"), runtime)
         self.ffn = build_part("ffn", spec.ffn, _sub(params, "ffn"), runtime)
+        # replayable as part of a captured decode step only if every sub-part says so itself
+        self.graph_safe = all(getattr(p, "graph_safe", False) is True
+                              for p in (self.norm1, self.mixer, self.norm2, self.ffn))
 
     def forward(self, stream: ResidualStream, ctx, cache) -> None:
         x = self.norm1.add_norm(stream)

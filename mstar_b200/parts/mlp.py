@@ -9,6 +9,8 @@ from .registry import register_part
 
 
 class GatedMLP:
+    graph_safe = True       # nothing per-step is read from the host
+
     @classmethod
     def param_specs(cls, spec) -> dict:
         return {

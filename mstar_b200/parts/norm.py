@@ -18,6 +18,8 @@ from .registry import register_part
 
 
 class RMSNorm:
+    graph_safe = True       # nothing per-step is read from the host
+
     @classmethod
     def param_specs(cls, spec) -> dict:
         return {"weight": ParamSpec(shape=(spec.size,), role="vector", init="ones")}

@@ -1,6 +1,7 @@
 """Registry of layer parts: (category, kind) -> class.
 
-Categories: "mixer", "ffn", "norm", "position", "block".  A part class offers
+Categories: "mixer", "ffn", "norm", "position", "block", "embedding", "head".  A part
+class offers
 
     param_specs(spec) -> {local name: ParamSpec}        (classmethod; no GPU needed)
     __init__(spec, params, runtime)                      params: {local name: tensor}
@@ -13,13 +14,18 @@ and, by category,
     mixer     cache_need(spec) -> CacheNeed              (classmethod)
               forward(x, ctx, cache) -> y
     block     sub-parts named by the spec; forward(stream, ctx, cache)
+    embedding forward(token_ids, ctx) -> float residual [tokens, hidden]
+    head      forward(normed rows) -> float logits [rows, vocab]
+
+A part that may run inside a captured decode step says so with ``graph_safe = True``
+(nothing per-step is read from the host); saying nothing means no.
 
 A part never learns which model it is in: it sees its spec, its own parameters
 and the step context.
 """
 from __future__ import annotations
 
-CATEGORIES = ("mixer", "ffn", "norm", "position", "block")
+CATEGORIES = ("mixer", "ffn", "norm", "position", "block", "embedding", "head")
 
 _PARTS: dict = {}
 
@@ -64,4 +70,4 @@ def _builtin() -> None:
     if _done:
         return
     _done = True
-    from . import attention, block, mlp, norm, rope  # noqa: F401  (they register themselves)
+    from . import attention, block, embedding, mlp, norm, rope  # noqa: F401  (they register themselves)

@@ -164,3 +164,64 @@ def test_random_orders_lose_nothing(seed, window, page):
         cm.free_request(rid)
     assert cm.free_pages(0) == 40 and cm.free_pages(1) == 25 and cm.free_slots() == 4
     assert cm.check() == 0
+
+
+def test_position_counter_is_kept_apart_from_the_length():
+    """Positions advance with the cached length unless a commit says otherwise (the
+    reference keeps position_id_start beside seq_len, mstar/engine/kv_store.py:112-116)."""
+    cm = CacheManager([GroupConfig(page_size=4, num_pages=8)], num_slots=2)
+    cm.add_request("a")
+    cm.reserve(["a"], [5])
+    cm.commit("a", 5)                                  # default: both by 5
+    assert (cm.length("a"), cm.position("a")) == (5, 5)
+    cm.reserve(["a"], [3])
+    b = cm.fill_batch(["a"], [3])
+    assert b.positions.tolist() == [5, 6, 7] and b.cache_pos.tolist() == [5, 6, 7]
+    cm.commit("a", 3, pos_advance=1)                   # three keys, one position
+    assert (cm.length("a"), cm.position("a")) == (8, 6)
+    cm.reserve(["a"], [2])
+    b = cm.fill_batch(["a"], [2])
+    assert b.positions.tolist() == [6, 7] and b.cache_pos.tolist() == [8, 9]
+    assert b.kv_len.tolist() == [10]
+    cm.commit("a", 2)
+    cm.set_position("a", 100)
+    cm.reserve(["a"], [1])
+    b = cm.fill_batch(["a"], [1])
+    assert b.positions.tolist() == [100] and b.cache_pos.tolist() == [10]
+    with pytest.raises(ValueError):
+        cm.set_position("a", -1)
+    with pytest.raises(ValueError):
+        cm.commit("a", 1, pos_advance=-2)
+    cm.free_request("a")
+    cm.add_request("b")                                # a new request starts at zero again
+    assert cm.position("b") == 0 and cm.check() == 0
+
+
+def test_storage_gives_each_group_its_own_page_size():
+    """Two groups (every key / a window of 6) with pages of 8 and of 2 tokens: tensors,
+    block tables and the layer caches handed to mixers follow their group's size."""
+    import torch
+
+    from mstar_b200.cache.storage import CacheStorage
+    from mstar_b200.parts.base import CacheNeed, KVNeed
+
+    needs = [CacheNeed(kv=KVNeed(2, 16)), CacheNeed(kv=KVNeed(1, 32, window=6)),
+             CacheNeed(kv=KVNeed(2, 16))]
+    st_ = CacheStorage(needs, torch.float32, torch.device("cpu"), [8, 2], [5, 9], num_slots=2)
+    assert st_.page_sizes == [8, 2] and st_.group_of == [0, 1, 0]
+    assert [tuple(t.shape) for t in st_.kv] == [(6, 2, 2, 8, 16), (10, 2, 1, 2, 32),
+                                                (6, 2, 2, 8, 16)]
+    cm = st_.manager
+    assert [g.page_size for g in cm.groups] == [8, 2]
+    cm.add_request("a")
+    cm.reserve(["a"], [11])
+    assert len(cm.block_table("a", 0)) == 2 and len(cm.block_table("a", 1)) == 6
+    idx = cm.fill_batch(["a"], [11])
+    tables = [torch.from_numpy(t) for t in idx.tables]
+    assert st_.layer_cache(0, tables).page_size == 8
+    assert st_.layer_cache(1, tables).page_size == 2
+    assert st_.layer_cache(1, tables).block_table.shape == (1, 6)
+    cm.commit("a", 11)                                 # the window has passed keys 0..5
+    assert cm.block_table("a", 1)[:3] == [-1, -1, -1] and cm.check() == 0
+    with pytest.raises(ValueError):
+        CacheStorage(needs, torch.float32, torch.device("cpu"), [8, 2, 4], 5, num_slots=2)

@@ -340,3 +340,45 @@ def test_abort_while_a_step_is_under_way():
     assert not done and a.finish_reason == "abort" and None not in a.output
     assert [e.request.request_id for e in p2.entries] == ["b"]
     assert not sch.abort("a") and not sch.abort("nobody")
+
+
+def test_sequences_end_where_the_models_positions_end():
+    """max_seq_len (the model's max_position_embeddings; the reference's max_seq_len,
+    mstar/model/orpheus/orpheus_model.py:88-95): a prompt that fills it is refused, and
+    generation finishes with "length" where the positions end, whatever max_output_tokens
+    says."""
+    cm = CacheManager([GroupConfig(4, 100)], num_slots=4)
+    cm.set_max_positions(12)
+    sch = Scheduler(SchedulerConfig(max_num_batched_tokens=64, max_seq_len=12), cm, (99,))
+    with pytest.raises(ValueError, match="sequences of up to 12"):
+        sch.add(req("long", 12))
+    with pytest.raises(ValueError):
+        sch.add(req("longer", 30))
+    sch.add(req("a", 9, max_out=50))                   # 9 + 3 = 12: three tokens, no more
+    sch.add(req("b", 3, max_out=2))                    # its own limit is the smaller one
+    outputs = {}
+    for _ in range(8):
+        if not sch.has_work():
+            break
+        _, done = run_step(cm, sch)
+        for r in done:
+            outputs[r.request_id] = (len(r.output), r.finish_reason)
+    assert outputs == {"a": (3, "length"), "b": (2, "length")}
+    assert cm.num_requests() == 0 and cm.check() == 0
+
+
+def test_the_manager_refuses_a_step_beyond_the_positions():
+    from mstar_b200.cache import SequenceTooLong
+
+    cm = CacheManager([GroupConfig(4, 100)], num_slots=2)
+    cm.set_max_positions(10)
+    cm.add_request("a")
+    cm.add_request("b")
+    cm.reserve(["a"], [10])                            # positions 0..9: allowed
+    cm.commit("a", 10)
+    free = cm.free_pages()
+    with pytest.raises(SequenceTooLong, match="'a'"):
+        cm.reserve(["b", "a"], [4, 1])                 # a would get position 10
+    assert cm.free_pages() == free and cm.block_table("b") == [] and cm.check() == 0
+    cm.set_max_positions(None)
+    cm.reserve(["b", "a"], [4, 1])
