@@ -100,6 +100,42 @@ def mixed(reqs: dict, seed: int = 0, max_live: int = 4, prompt_frac: float = 0.6
     return steps
 
 
+def serving(reqs: dict, prompt_len: dict, max_live: int, budget: int, order=None) -> list:
+    """The steps a continuous-batching server would run: requests are admitted in order
+    while fewer than ``max_live`` are live; every live request whose prompt is in brings one
+    token, then prompt portions fill what is left of ``budget`` tokens (cut anywhere, down
+    to one token); a request leaves after its last token, and its pages go to whoever
+    comes next.  ``prompt_len[rid]`` tokens of a request are prompt, the rest are fed one
+    by one as if they had been sampled."""
+    pending = list(order or reqs)
+    live: dict = {}
+    steps = []
+    while pending or live:
+        while pending and len(live) < max_live:
+            rid = pending.pop(0)
+            live[rid] = 0
+        left = budget
+        entries, end = [], []
+        for phase in ("decode", "prompt"):
+            for rid in list(live):
+                toks, pos = reqs[rid], live[rid]
+                decoding = pos >= prompt_len[rid]
+                if decoding != (phase == "decode") or left <= 0:
+                    continue
+                n = 1 if decoding else min(prompt_len[rid] - pos, left)
+                entries.append({"id": rid, "tokens": toks[pos:pos + n],
+                                "want": list(range(n))})
+                left -= n
+                live[rid] = pos + n
+        for rid in list(live):
+            if live[rid] == len(reqs[rid]):
+                end.append(rid)
+                del live[rid]
+        assert entries, "budget too small for any progress"
+        steps.append({"entries": entries, "end": end})
+    return steps
+
+
 def max_tokens_of(steps: list, page: int = 64) -> int:
     """The --max-tokens a trace needs: the most tokens live requests hold at any time,
     each request's count rounded up to a multiple of ``page``."""
@@ -114,27 +150,53 @@ def max_tokens_of(steps: list, page: int = 64) -> int:
     return worst
 
 
-def run_steps_in_process(stepper, steps: list) -> dict:
-    """Feed ``steps`` to a Stepper; returns {(request, position): logits row (cpu, f32)}."""
+def run_steps_in_process(stepper, steps: list, device_fed_seed=None, keep=None) -> dict:
+    """Feed ``steps`` to a Stepper; returns {(request, position): logits row (cpu, f32)}.
+    ``device_fed_seed``: about half of the single tokens (chosen by this seed) are not
+    given to the step as values but left on the device, in a tensor that also holds other
+    numbers, as the engine feeds the tokens a step sampled to the step after it.
+    ``keep``: a set of (request, position); the engine still computes every wanted row,
+    but only these are brought back."""
     from mstar_b200.engine.step import StepEntry
 
     out = {}
     pos = {}
+    rng = None if device_fed_seed is None else np.random.default_rng(device_fed_seed)
+    vocab = stepper.model.vocab_size
     for st in steps:
-        entries = []
+        entries, pending, fed = [], {}, []
         for e in st["entries"]:
             if not stepper.has_request(e["id"]):
                 stepper.add_request(e["id"])
-            entries.append(StepEntry(e["id"], e["tokens"], e["want"]))
-        logits = stepper.step(entries).float().cpu()
-        row = 0
+            tokens = e["tokens"]
+            if rng is not None and len(tokens) == 1 and rng.random() < 0.5:
+                pending[len(entries)] = len(fed)
+                fed.append(tokens[0])
+                tokens = [(tokens[0] + 1) % vocab]          # a wrong value: it must not be used
+            entries.append(StepEntry(e["id"], tokens, e["want"]))
+        if pending:
+            perm = rng.permutation(len(fed) + 3)              # shuffled, among strangers
+            place = {j: int(perm[j]) for j in range(len(fed))}
+            values = [0] * (len(fed) + 3)
+            for j, tok in enumerate(fed):
+                values[place[j]] = tok
+            dev_tokens = torch.tensor(values, dtype=torch.int32, device=stepper.device)
+            logits = stepper.step(entries, {i: place[j] for i, j in pending.items()}, dev_tokens)
+        else:
+            logits = stepper.step(entries)
+        keys = []
         for e in st["entries"]:
             base = pos.get(e["id"], 0)
-            for w in e["want"]:
-                out[(e["id"], base + w)] = logits[row]
-                row += 1
+            keys.extend((e["id"], base + w) for w in e["want"])
             pos[e["id"]] = base + len(e["tokens"])
-        assert row == logits.shape[0]
+        assert len(keys) == logits.shape[0]
+        rows = [i for i, k in enumerate(keys) if keep is None or k in keep]
+        if rows:
+            if len(rows) < len(keys):
+                logits = logits[torch.tensor(rows, device=logits.device)]
+            host = logits.float().cpu()
+            for j, i in enumerate(rows):
+                out[keys[i]] = host[j]
         for rid in st["end"]:
             stepper.free_request(rid)
             pos.pop(rid, None)

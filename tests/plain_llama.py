@@ -12,7 +12,16 @@ rotation angles are 32-bit; sine and cosine of that angle are then taken in
 double precision.
 
 Weights are a dict of checkpoint-named tensors (model.layers.N.self_attn.q_proj.weight
-and so on); ``cfg`` is the dict of config.json keys.
+and so on); ``cfg`` is the dict of config.json keys.  Everything is computed where the
+weights live (the large-size tests keep them on the GPU to have the float64 products
+done there; the arithmetic is the same).
+
+``act``: an optional function applied to every activation at the places where the engine
+stores one in its compute dtype (normed rows; q, k, v; rotated q and k; the attention
+output; each projection's output; gate, up and their product).  With ``round_bf16`` it
+gives the second oracle of the bfloat16 tests: the same float64 arithmetic on activations
+that were rounded where the engine rounds them, so that what remains between it and the
+engine is the order of the sums and the attention kernels' internal roundings.
 """
 from __future__ import annotations
 
@@ -21,6 +30,15 @@ import math
 import torch
 
 DT = torch.float64
+
+
+def _keep(x):
+    return x
+
+
+def round_bf16(x: torch.Tensor) -> torch.Tensor:
+    """Round to bfloat16 (nearest even) and return to float64."""
+    return x.to(torch.bfloat16).to(DT)
 
 
 def plain_rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
@@ -62,27 +80,32 @@ def plain_apply_rope(x: torch.Tensor, positions: torch.Tensor, inv_freq: torch.T
     the same rotate-half form in test/modular/test_fused_rmsnorm.py:12-45).  Angles are
     rounded to float32 (see the module docstring)."""
     hd = x.shape[-1]
-    ang32 = positions.to(torch.float32)[:, None] * inv_freq.to(torch.float32)[None, :]
+    ang32 = (positions.to(torch.float32)[:, None]
+             * inv_freq.to(positions.device, torch.float32)[None, :])
     ang = ang32.to(DT)
     cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
     x1, x2 = x[..., : hd // 2].to(DT), x[..., hd // 2:].to(DT)
     return torch.cat([x1 * cos - x2 * sin, x2 * cos + x1 * sin], dim=-1)
 
 
-def plain_attention(q, k, v, scale=None, window=None):
+def plain_attention(q, k, v, scale=None, window=None, round_probs=None):
     """Causal grouped-query attention of a whole sequence.  q [T, nh, hd], k, v
     [T, nkv, hd]; query head i uses kv head i // (nh/nkv); scores * hd^-0.5 (the
     reference passes no scale, i.e. the library default; its own kernels and tests use
     hd^-0.5: mstar/utils/attention.py:116-117, test/modular/
     test_pi05_reference_equivalence.py:692); causal mask (mstar/model/orpheus/
     submodules.py:122); softmax; P.V (mstar/engine/cache_manager.py:653-701).
-    ``window`` W lets token p see keys p-W+1..p (not used by Llama)."""
+    ``window`` W lets token p see keys p-W+1..p (not used by Llama).
+    ``round_probs``: a function applied to the unnormalised probabilities exp(s - max)
+    before they multiply V (tensor-core attention kernels hold them in bfloat16 there);
+    the normaliser is the sum of the unrounded ones.  Only the tests' yardstick for what
+    such a kernel-internal rounding can do uses it."""
     T, nh, hd = q.shape
     nkv = k.shape[1]
     group = nh // nkv
     scale = hd ** -0.5 if scale is None else scale
-    out = torch.empty(T, nh, hd, dtype=DT)
-    idx = torch.arange(T)
+    out = torch.empty(T, nh, hd, dtype=DT, device=q.device)
+    idx = torch.arange(T, device=q.device)
     mask = idx[None, :] <= idx[:, None]
     if window is not None:
         mask &= idx[None, :] > idx[:, None] - window
@@ -90,21 +113,26 @@ def plain_attention(q, k, v, scale=None, window=None):
         kh, vh = k[:, h // group].to(DT), v[:, h // group].to(DT)
         s = (q[:, h].to(DT) @ kh.T) * scale
         s = s.masked_fill(~mask, float("-inf"))
-        out[:, h] = torch.softmax(s, dim=-1) @ vh
+        if round_probs is None:
+            out[:, h] = torch.softmax(s, dim=-1) @ vh
+        else:
+            e = torch.exp(s - s.max(dim=-1, keepdim=True).values)
+            out[:, h] = (round_probs(e) @ vh) / e.sum(dim=-1, keepdim=True)
     return out
 
 
-def plain_swiglu(x, w_gate, w_up, w_down):
+def plain_swiglu(x, w_gate, w_up, w_down, act=_keep):
     """down(silu(gate(x)) * up(x)), no bias (mstar/model/components/distributed/
     mlp.py:78-81; activation "silu" fixed at mstar/model/orpheus/components/
     language_model.py:48)."""
     x = x.to(DT)
-    g = x @ w_gate.to(DT).T
-    u = x @ w_up.to(DT).T
-    return ((g * torch.sigmoid(g)) * u) @ w_down.to(DT).T
+    g = act(x @ w_gate.to(DT).T)
+    u = act(x @ w_up.to(DT).T)
+    return act(act((g * torch.sigmoid(g)) * u) @ w_down.to(DT).T)
 
 
-def plain_self_attention(x, w, prefix, cfg, positions, inv_freq, window=None):
+def plain_self_attention(x, w, prefix, cfg, positions, inv_freq, window=None, act=_keep,
+                         round_probs=None):
     """q/k/v projections, view as heads, rotary on q and k, attention, output
     projection (mstar/model/components/distributed/attention.py:98-110, 138-149)."""
     nh, nkv = cfg["num_attention_heads"], cfg.get("num_key_value_heads") or cfg[
@@ -112,46 +140,49 @@ def plain_self_attention(x, w, prefix, cfg, positions, inv_freq, window=None):
     hd = cfg.get("head_dim") or cfg["hidden_size"] // nh
     T = x.shape[0]
     x = x.to(DT)
-    q = (x @ w[f"{prefix}.q_proj.weight"].to(DT).T).view(T, nh, hd)
-    k = (x @ w[f"{prefix}.k_proj.weight"].to(DT).T).view(T, nkv, hd)
-    v = (x @ w[f"{prefix}.v_proj.weight"].to(DT).T).view(T, nkv, hd)
-    q = plain_apply_rope(q, positions, inv_freq)
-    k = plain_apply_rope(k, positions, inv_freq)
-    a = plain_attention(q, k, v, window=window).reshape(T, nh * hd)
-    return a @ w[f"{prefix}.o_proj.weight"].to(DT).T
+    q = act((x @ w[f"{prefix}.q_proj.weight"].to(DT).T)).view(T, nh, hd)
+    k = act((x @ w[f"{prefix}.k_proj.weight"].to(DT).T)).view(T, nkv, hd)
+    v = act((x @ w[f"{prefix}.v_proj.weight"].to(DT).T)).view(T, nkv, hd)
+    q = act(plain_apply_rope(q, positions, inv_freq))
+    k = act(plain_apply_rope(k, positions, inv_freq))
+    a = act(plain_attention(q, k, v, window=window, round_probs=round_probs).reshape(T, nh * hd))
+    return act(a @ w[f"{prefix}.o_proj.weight"].to(DT).T)
 
 
-def plain_decoder_layer(h, w, i, cfg, positions, inv_freq):
+def plain_decoder_layer(h, w, i, cfg, positions, inv_freq, act=_keep, round_probs=None):
     """Pre-norm block with plain residual adds
     (mstar/model/components/decoder_layer.py:58-71)."""
     p = f"model.layers.{i}"
     eps = cfg["rms_norm_eps"]
-    x = plain_rms_norm(h, w[f"{p}.input_layernorm.weight"], eps)
-    h = h + plain_self_attention(x, w, f"{p}.self_attn", cfg, positions, inv_freq)
-    y = plain_rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], eps)
+    x = act(plain_rms_norm(h, w[f"{p}.input_layernorm.weight"], eps))
+    h = h + plain_self_attention(x, w, f"{p}.self_attn", cfg, positions, inv_freq, act=act,
+                                 round_probs=round_probs)
+    y = act(plain_rms_norm(h, w[f"{p}.post_attention_layernorm.weight"], eps))
     return h + plain_swiglu(y, w[f"{p}.mlp.gate_proj.weight"], w[f"{p}.mlp.up_proj.weight"],
-                            w[f"{p}.mlp.down_proj.weight"])
+                            w[f"{p}.mlp.down_proj.weight"], act=act)
 
 
-def plain_hidden_states(w: dict, cfg: dict, token_ids) -> torch.Tensor:
+def plain_hidden_states(w: dict, cfg: dict, token_ids, act=_keep, round_probs=None) -> torch.Tensor:
     """embed -> layers -> final norm (mstar/model/orpheus/components/
     language_model.py:72-83; embedding lookup without scaling, mstar/model/components/
     distributed/embedding.py:98-99)."""
-    ids = torch.as_tensor(token_ids, dtype=torch.long)
-    positions = torch.arange(ids.numel())
+    table = w["model.embed_tokens.weight"]
+    ids = torch.as_tensor(token_ids, dtype=torch.long, device=table.device)
+    positions = torch.arange(ids.numel(), device=table.device)
     inv_freq = plain_rope_frequencies(cfg)
-    h = w["model.embed_tokens.weight"].to(DT)[ids]
+    h = table[ids].to(DT)
     for i in range(cfg["num_hidden_layers"]):
-        h = plain_decoder_layer(h, w, i, cfg, positions, inv_freq)
-    return plain_rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"])
+        h = plain_decoder_layer(h, w, i, cfg, positions, inv_freq, act=act,
+                                round_probs=round_probs)
+    return act(plain_rms_norm(h, w["model.norm.weight"], cfg["rms_norm_eps"]))
 
 
-def plain_logits(w: dict, cfg: dict, token_ids) -> torch.Tensor:
+def plain_logits(w: dict, cfg: dict, token_ids, act=_keep, round_probs=None) -> torch.Tensor:
     """Logits at every position, [T, vocab], float64.  The head is lm_head.weight, or
     the embedding table when the configuration ties them (the reference has no tying
     code: mstar/model/orpheus/components/language_model.py:95-101; tying is this
     engine's reading of config.json's tie_word_embeddings)."""
-    hidden = plain_hidden_states(w, cfg, token_ids)
+    hidden = plain_hidden_states(w, cfg, token_ids, act=act, round_probs=round_probs)
     head = w.get("lm_head.weight")
     if head is None or cfg.get("tie_word_embeddings"):
         head = w["model.embed_tokens.weight"]

@@ -12,18 +12,23 @@ import plain_llama as P
 pytestmark = pytest.mark.gpu
 
 
+def check_greedy_chain(prompt, token_ids, tensors, raw, dtype):
+    """Every token is the plain model's greedy choice after the tokens before it; only a
+    near-tie may be decided differently, and only in bfloat16."""
+    ids = list(prompt)
+    for k, tok in enumerate(token_ids):
+        logits = P.plain_logits(tensors, raw, ids)[-1]
+        best = int(logits.argmax())
+        if tok != best:
+            assert dtype == "bfloat16", (prompt, k, tok, best)
+            assert (logits[best] - logits[tok]).item() < 2 * H.TOL["bfloat16"], (k, tok, best)
+        ids.append(tok)
+
+
 def check_greedy(results, prompts, tensors, raw, dtype, n_new):
     for prompt, res in zip(prompts, results):
         assert res.finish_reason == "length" and len(res.token_ids) == n_new
-        ids = list(prompt)
-        for k, tok in enumerate(res.token_ids):
-            logits = P.plain_logits(tensors, raw, ids)[-1]
-            best = int(logits.argmax())
-            if tok != best:
-                # only a near-tie may be decided differently, and only in bfloat16
-                assert dtype == "bfloat16", (prompt, k, tok, best)
-                assert (logits[best] - logits[tok]).item() < 2 * H.TOL["bfloat16"], (k, tok, best)
-            ids.append(tok)
+        check_greedy_chain(prompt, res.token_ids, tensors, raw, dtype)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -43,18 +48,26 @@ def test_greedy_generation_matches_the_plain_model(model_folders, name, dtype):
     assert llm.stepper.manager.num_requests() == 0 and llm.stepper.manager.check() == 0
 
 
-def test_preemption_does_not_change_greedy_tokens(model_folders):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_preemption_does_not_change_greedy_tokens(model_folders, dtype):
+    """A pre-empted request computes its prompt and what it had generated again, as one
+    prompt; in float32 the tokens are those of a run with room for everyone, in bfloat16
+    (where the second computation goes through other kernels than the first) they are the
+    plain model's greedy tokens up to near-ties."""
     from mstar_b200 import LLM, SamplingParams
 
     folder, raw, tensors = model_folders["tiny_b"]
     prompts = [H.request_tokens(raw["vocab_size"], n, seed=300 + n) for n in (20, 22, 24)]
     params = SamplingParams(temperature=0.0, max_output_tokens=24, ignore_eos=True)
-    roomy = LLM(folder, dtype="float32", page_size=8, max_num_pages=64).generate(prompts, params)
-    tight_llm = LLM(folder, dtype="float32", page_size=8, max_num_pages=12)
+    roomy = LLM(folder, dtype=dtype, page_size=8, max_num_pages=64).generate(prompts, params)
+    tight_llm = LLM(folder, dtype=dtype, page_size=8, max_num_pages=12)
     tight = tight_llm.generate(prompts, params)
     assert tight_llm.stats.preemptions > 0
-    assert [r.token_ids for r in tight] == [r.token_ids for r in roomy]
+    if dtype == "float32":
+        assert [r.token_ids for r in tight] == [r.token_ids for r in roomy]
+    check_greedy(tight, prompts, tensors, raw, dtype, 24)
     assert sum(r.preemptions for r in tight) == tight_llm.stats.preemptions
+    assert tight_llm.stepper.manager.num_requests() == 0 and tight_llm.stepper.manager.check() == 0
 
 
 def test_sampling_options_through_the_entry_point(model_folders):
@@ -162,7 +175,8 @@ def test_tokens_taken_from_the_device_give_the_same_logits(model_folders, graphs
         assert torch.equal(a, b)
 
 
-def test_stop_and_length_through_the_pipelined_entry_point(model_folders, tmp_path):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_stop_and_length_through_the_pipelined_entry_point(model_folders, tmp_path, dtype):
     """Steps are launched before the tokens of the step before are read: a request that
     stops is cut at its stop token although one more token was computed for it, and the
     other requests of the batch are not disturbed."""
@@ -171,7 +185,9 @@ def test_stop_and_length_through_the_pipelined_entry_point(model_folders, tmp_pa
     folder, raw, tensors = model_folders["tiny_a"]
     prompts = [H.request_tokens(raw["vocab_size"], n, seed=600 + n) for n in (4, 9, 13, 6)]
     free = SamplingParams(temperature=0.0, max_output_tokens=12, ignore_eos=True)
-    ref = LLM(folder, dtype="float32", page_size=4, max_num_pages=64).generate(prompts, free)
+    ref = LLM(folder, dtype=dtype, page_size=4, max_num_pages=64).generate(prompts, free)
+    for prompt, r in zip(prompts, ref):
+        check_greedy_chain(prompt, r.token_ids, tensors, raw, dtype)
     # declare the 5th token of request 1 a stop token: config.json's eos_token_id
     stop = ref[1].token_ids[4]
     from mstar_b200.config.registry import config_from_dict
@@ -179,7 +195,7 @@ def test_stop_and_length_through_the_pipelined_entry_point(model_folders, tmp_pa
 
     alt = tmp_path / "with_stop"
     write_model_folder(alt, config_from_dict({**raw, "eos_token_id": int(stop)}), 0, tensors=tensors)
-    llm = LLM(alt, dtype="float32", page_size=4, max_num_pages=64)
+    llm = LLM(alt, dtype=dtype, page_size=4, max_num_pages=64)
     got = llm.generate(prompts, SamplingParams(temperature=0.0, max_output_tokens=12))
     for r, g in zip(ref, got):
         cut = r.token_ids.index(stop) + 1 if stop in r.token_ids else len(r.token_ids)
@@ -189,14 +205,17 @@ def test_stop_and_length_through_the_pipelined_entry_point(model_folders, tmp_pa
     assert llm.stepper.manager.num_requests() == 0 and llm.stepper.manager.check() == 0
 
 
-def test_abort_through_the_entry_point(model_folders):
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_abort_through_the_entry_point(model_folders, dtype):
     from mstar_b200 import LLM, SamplingParams
 
     folder, raw, tensors = model_folders["tiny_a"]
     prompts = [H.request_tokens(raw["vocab_size"], n, seed=700 + n) for n in (5, 8, 11)]
     params = SamplingParams(temperature=0.0, max_output_tokens=10, ignore_eos=True)
-    ref = LLM(folder, dtype="float32", page_size=4, max_num_pages=64).generate(prompts, params)
-    llm = LLM(folder, dtype="float32", page_size=4, max_num_pages=64)
+    ref = LLM(folder, dtype=dtype, page_size=4, max_num_pages=64).generate(prompts, params)
+    for prompt, r in zip(prompts, ref):
+        check_greedy_chain(prompt, r.token_ids, tensors, raw, dtype)
+    llm = LLM(folder, dtype=dtype, page_size=4, max_num_pages=64)
     ids = [llm.add_request(p, params) for p in prompts]
     done = {}
     for _ in range(4):                                  # a few steps, one always under way
@@ -211,3 +230,65 @@ def test_abort_through_the_entry_point(model_folders):
     for k in (0, 2):                                    # the others are not disturbed
         assert done[ids[k]].output == ref[k].token_ids and done[ids[k]].finish_reason == "length"
     assert llm.stepper.manager.num_requests() == 0 and llm.stepper.manager.check() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_temperature_beside_greedy_with_portions_of_16(model_folders, dtype):
+    """Four requests with prompts of 1, 7, 33 and 40 tokens, two greedy and two at
+    temperature 0.8, prompts cut into portions of 16 at most, pages of 8: the greedy ones
+    follow the plain model; every token drawn at a temperature is the inverse-CDF draw of the
+    plain distribution for that request's seed and step (within what the dtype's logit
+    error moves the CDF's steps)."""
+    from mstar_b200 import LLM, SamplingParams
+
+    folder, raw, tensors = model_folders["tiny_b"]
+    lengths = [1, 7, 33, 40]
+    prompts = [H.request_tokens(raw["vocab_size"], n, seed=900 + n) for n in lengths]
+    n_new = 10
+    params = [SamplingParams(temperature=0.0, max_output_tokens=n_new, ignore_eos=True),
+              SamplingParams(temperature=0.8, max_output_tokens=n_new, ignore_eos=True, seed=41),
+              SamplingParams(temperature=0.0, max_output_tokens=n_new, ignore_eos=True),
+              SamplingParams(temperature=0.8, max_output_tokens=n_new, ignore_eos=True, seed=42)]
+    llm = LLM(folder, dtype=dtype, page_size=8, max_num_pages=64, max_num_batched_tokens=16)
+    results = llm.generate(prompts, params)
+    assert llm.stats.steps > n_new + 2                  # the prompts did not fit one step
+    # how far a logit error of the dtype's tolerance can move a cumulative probability:
+    # d(softmax)/d(logit) <= 1/4 per unit of logit/temperature, summed over a CDF at most 1
+    slack = {"float32": 1e-4, "bfloat16": H.TOL["bfloat16"] / 0.8}[dtype]
+    for prompt, sp, res in zip(prompts, params, results):
+        assert res.finish_reason == "length" and len(res.token_ids) == n_new
+        if sp.temperature == 0:
+            check_greedy_chain(prompt, res.token_ids, tensors, raw, dtype)
+            continue
+        ids = list(prompt)
+        for step, tok in enumerate(res.token_ids):
+            p = P.plain_sampling_distribution(P.plain_logits(tensors, raw, ids)[-1], 0.8)
+            cdf = torch.cumsum(p, 0)
+            u = P.plain_uniform(sp.seed, step)
+            lo = cdf[tok - 1].item() if tok else 0.0
+            assert lo - slack <= u <= cdf[tok].item() + slack, (lengths, step, tok, u)
+            ids.append(tok)
+    assert llm.stepper.manager.num_requests() == 0 and llm.stepper.manager.check() == 0
+
+
+def test_a_wait_that_ran_out_stops_the_entry_point(model_folders):
+    """Kernels with bounded waits report into a device word and return with partial
+    output; the entry point reads that word with every step's tokens and raises instead
+    of handing tokens out.  The word is set by hand here: no kernel is made to hang."""
+    from mstar_b200 import LLM, SamplingParams, ops
+
+    folder, raw, _ = model_folders["tiny_a"]
+    llm = LLM(folder, dtype="bfloat16", page_size=4, max_num_pages=32)
+    llm.add_request(H.request_tokens(raw["vocab_size"], 6, seed=1),
+                    SamplingParams(temperature=0.0, max_output_tokens=8, ignore_eos=True))
+    llm.step()
+    llm.step()
+    ops.tcgen05_error_word(llm.device).fill_(4)
+    with pytest.raises(ops.KernelError, match="code 4"):
+        for _ in range(3):
+            llm.step()
+    assert int(ops.tcgen05_error_word(llm.device).item()) == 0     # cleared for what follows
+    with pytest.raises(ops.KernelError):
+        ops.tcgen05_error_word(llm.device).fill_(13)
+        ops.check_error_word(llm.device)
+    ops.check_error_word(llm.device)                               # zero again: silent
