@@ -18,7 +18,9 @@
 // Behaviour to know about:
 //   * The first call on a device looks up the array's device address
 //     (cudaGetSymbolAddress) and keeps it.  Make that first call outside of any CUDA
-//     stream capture.
+//     stream capture.  The kept address is stored without a lock: two host threads that
+//     make their first calls on a device at the same time both look the address up and
+//     both store the same value, which is harmless.
 //   * No call allocates or frees: no cudaMalloc, cudaFree or allocating library routine.
 //   * All calls on a device share the one array.  It still holds the previous call's
 //     partial results when the next one starts; that is harmless, because every partial

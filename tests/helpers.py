@@ -241,6 +241,42 @@ def run_steps_with_trace_run(model_dir, dtype: str, steps: list, out_dir, vocab:
     return out
 
 
+def spread(a: dict, b: dict) -> tuple:
+    """(largest, mean over rows of the mean) absolute difference of two sets of rows."""
+    worst, total = 0.0, 0.0
+    for key, row in a.items():
+        err = (row.double() - b[key].double()).abs()
+        worst = max(worst, err.max().item())
+        total += err.mean().item()
+    return worst, total / len(a)
+
+
+def in_float32(fn):
+    """``fn()`` with the plain model's sums in float32 (its roundings stay where they are)."""
+    P.DT = torch.float32
+    try:
+        return fn()
+    finally:
+        P.DT = torch.float64
+
+
+def kernel_rounding_yardstick(tensors: dict, raw_cfg: dict, reqs: dict) -> tuple:
+    """How far the logits move through what a bfloat16 kernel does differently from the
+    plain model beyond rounding its stored activations: the plain model with activations
+    rounded to bfloat16 (``act=P.round_bf16``) against the same with its products summed in
+    float32 and its attention probabilities rounded to bfloat16 before they multiply V.
+    Nothing the engine computes enters.  Returns (max, mean) over all positions of
+    ``reqs``."""
+    a, b = {}, {}
+    for rid, toks in reqs.items():
+        x = P.plain_logits(tensors, raw_cfg, toks, act=P.round_bf16)
+        y = in_float32(lambda: P.plain_logits(tensors, raw_cfg, toks, act=P.round_bf16,
+                                              round_probs=P.round_bf16))
+        for i in range(len(toks)):
+            a[(rid, i)], b[(rid, i)] = x[i], y[i].double()
+    return spread(a, b)
+
+
 def plain_rows(tensors: dict, raw_cfg: dict, reqs: dict) -> dict:
     out = {}
     for rid, toks in reqs.items():

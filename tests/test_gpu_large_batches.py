@@ -44,22 +44,7 @@ def make_requests(vocab: int, count: int, lo: int, hi: int, seed: int):
 # probabilities rounded to bfloat16 before they multiply V differs from itself (by 0.07 at
 # most at the benchmark sizes); the tolerance is twice that.  Neither figure depends on
 # anything the engine computes.
-def spread(a: dict, b: dict) -> tuple:
-    worst, total = 0.0, 0.0
-    for key, row in a.items():
-        err = (row.double() - b[key].double()).abs()
-        worst = max(worst, err.max().item())
-        total += err.mean().item()
-    return worst, total / len(a)
-
-
-def in_float32(fn):
-    """``fn()`` with the plain model's sums in float32 (its roundings stay where they are)."""
-    P.DT = torch.float32
-    try:
-        return fn()
-    finally:
-        P.DT = torch.float64
+spread, in_float32 = H.spread, H.in_float32
 
 
 _tiny: dict = {}

@@ -78,21 +78,27 @@ def test_gated_mlp_part(dtype):
                    {"gate_up.weight": gu, "down.weight": dn}, runtime(dtype))
 
 
-def test_rope_part_frequencies_match_the_plain_rule():
+def test_rope_part_holds_the_hand_computed_frequencies_on_the_device():
+    """The position part's table, as the kernels read it (float on the device), against
+    values worked out by hand from the llama3 rule (tests/test_plain.py; the rule itself is
+    compared with the library call the reference makes in tests/test_gpu_library_anchor.py),
+    and against the plain rule for a head size and base without scaling."""
+    from test_plain import ORPHEUS_FREQS, TINY_B_FREQS
+
     from mstar_b200.config.layout import PositionSpec, RopeScalingSpec
     from mstar_b200.parts import build_part
 
-    for hd, theta, sc in ((48, 10000.0, None), (128, 500000.0, (32.0, 1.0, 4.0, 8192)),
-                          (32, 500000.0, (8.0, 1.0, 4.0, 32))):
+    for hd, theta, sc, pins in ((128, 500000.0, (32.0, 1.0, 4.0, 8192), ORPHEUS_FREQS),
+                                (32, 500000.0, (8.0, 1.0, 4.0, 32), TINY_B_FREQS),
+                                (48, 10000.0, None, {0: 1.0, 12: 0.01, 23: 10000.0 ** (-46 / 48)})):
         scaling = None if sc is None else RopeScalingSpec("llama3", *sc)
         part = build_part("position", PositionSpec("rope", hd, hd, theta, scaling), {},
                           runtime(torch.float32))
-        cfg = dict(head_dim=hd, rope_theta=theta, hidden_size=hd, num_attention_heads=1,
-                   rope_scaling=None if sc is None else dict(
-                       rope_type="llama3", factor=sc[0], low_freq_factor=sc[1],
-                       high_freq_factor=sc[2], original_max_position_embeddings=sc[3]))
-        want = P.plain_rope_frequencies(cfg).float()
-        assert torch.allclose(part.inv_freq.cpu(), want, rtol=2e-7, atol=0)
+        assert part.inv_freq.is_cuda and part.inv_freq.dtype == torch.float32
+        table = part.inv_freq.cpu().double()
+        assert table.numel() == hd // 2
+        for j, value in pins.items():
+            assert abs(table[j].item() / value - 1) < 1e-7, (hd, j, table[j].item(), value)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -95,8 +95,11 @@ class TestCuttings:
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_cuttings_agree_with_each_other(model_folders, dtype):
-    """Beyond agreeing with the plain model, different cuttings agree with each other
-    far more tightly in float32: the same row goes through the same arithmetic."""
+    """Beyond agreeing with the plain model, different cuttings agree with each other:
+    in float32 to 1e-6, the same row going through the same arithmetic; in bfloat16, where
+    a portion and a single token go through different attention kernels, within what such
+    kernel-internal differences (the order of float sums, probabilities held in bfloat16)
+    move the plain model's own logits on these requests (``kernel_rounding_yardstick``)."""
     from mstar_b200.engine.step import make_stepper
 
     name = "tiny_b"
@@ -106,10 +109,17 @@ def test_cuttings_agree_with_each_other(model_folders, dtype):
     for steps in (H.whole(reqs), H.portions(reqs), H.mixed(reqs, seed=3)):
         stepper = make_stepper(model, page_size=8, num_pages=200, num_slots=8)
         outs.append(H.run_steps_in_process(stepper, steps))
-    tol = 1e-6 if dtype == "float32" else H.TOL["bfloat16"]
+    if dtype == "float32":
+        tol = 1e-6
+    else:
+        _, raw, tensors = model_folders[name]
+        tol = H.kernel_rounding_yardstick(tensors, raw, reqs)[0]
+    worst = 0.0
     for other in outs[1:]:
         for key, row in outs[0].items():
-            assert (row - other[key]).abs().max().item() <= tol, key
+            worst = max(worst, (row - other[key]).abs().max().item())
+            assert worst <= tol, (key, worst, tol)
+    print(f"cuttings differ from each other by {worst:.3e} at most [{dtype}] (allowed {tol:.3e})")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -173,7 +183,9 @@ def test_decode_steps_replay_cuda_graphs_with_the_same_logits(model_folders, dty
             assert (stepper.graph_replays > 0) == graphs
             assert stepper.manager.check() == 0 and stepper.manager.free_pages(0) == 200
         H.compare(outs[True], want, dtype, what)
-        tol = 1e-6 if dtype == "float32" else H.TOL["bfloat16"]
+        # a replayed step runs the kernels of the eager step; only the number of key
+        # splits may differ with the padded batch (bfloat16: sums in another order)
+        tol = 1e-6 if dtype == "float32" else 4e-3
         for key, row in outs[False].items():
             assert (row - outs[True][key]).abs().max().item() <= tol, key
 

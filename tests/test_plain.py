@@ -82,3 +82,76 @@ def test_sampling_distribution_filters():
     seen = torch.tensor([0, 0, 0, 0, 1])
     p = P.plain_sampling_distribution(logits, 1.0, penalty=100.0, seen=seen)
     assert p.argmax().item() == 0
+
+
+# ---- pins that do not rest on plain_llama's own formulas: numbers worked out by hand from
+# the llama3 rule as published (wavelength 2*pi/f; shorter than C/high: kept; longer than
+# C/low: f/factor; between: s = (C/wavelength - low)/(high - low), (1-s)*f/factor + s*f).
+# The same rule is compared with the library call that the reference makes in
+# tests/test_gpu_library_anchor.py; here it is pinned without a GPU, for the plain
+# implementation and for the product's table alike.
+ORPHEUS_ROPE = dict(head_dim=128, hidden_size=3072, num_attention_heads=24, rope_theta=500000.0,
+                    rope_scaling={"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                                  "high_freq_factor": 4.0,
+                                  "original_max_position_embeddings": 8192})
+# frequency index -> scaled inverse frequency (theta 5e5, head size 128, factor 32, C 8192).
+# Index 32 by hand: f = 500000^(-1/2) = 1.4142136e-3, C*f/(2*pi) = 1.843862,
+# s = 0.843862/3 = 0.281287, f' = f*(0.718713/32 + 0.281287) = 4.295568e-4.
+ORPHEUS_FREQS = {0: 1.0, 1: 0.8146172338565447, 28: 0.003211445994752591,      # kept
+                 29: 0.002118406996779608, 31: 0.0007625412033563571,          # smoothed
+                 32: 0.00042955679655936815, 34: 9.70828780262767e-05,
+                 35: 2.3890530884911708e-05, 63: 7.672314972286278e-08}        # divided by 32
+TINY_B_ROPE = dict(head_dim=32, hidden_size=96, num_attention_heads=3, rope_theta=500000.0,
+                   rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                 "high_freq_factor": 4.0, "original_max_position_embeddings": 32})
+TINY_B_FREQS = {0: 1.0, 1: 0.2146673579985814, 2: 0.02424034309358572,
+                15: 5.677088100759837e-07}
+
+
+def test_llama3_frequencies_against_hand_computed_values():
+    from mstar_b200.config.llama import LlamaConfig  # noqa: F401  (the product's table too)
+    from mstar_b200.config.layout import PositionSpec, RopeScalingSpec
+    from mstar_b200.parts.rope import rope_inverse_frequencies
+
+    for cfg, pins in ((ORPHEUS_ROPE, ORPHEUS_FREQS), (TINY_B_ROPE, TINY_B_FREQS)):
+        plain = P.plain_rope_frequencies(cfg)
+        rs = cfg["rope_scaling"]
+        spec = PositionSpec(kind="rope", head_dim=cfg["head_dim"], rotary_dim=cfg["head_dim"],
+                            theta=cfg["rope_theta"], scaling=RopeScalingSpec(
+                                rs["rope_type"], rs["factor"], rs["low_freq_factor"],
+                                rs["high_freq_factor"], rs["original_max_position_embeddings"]))
+        product = rope_inverse_frequencies(spec)
+        for j, value in pins.items():
+            assert abs(plain[j].item() / value - 1) < 1e-12, (j, plain[j].item(), value)
+            assert abs(product[j] / value - 1) < 1e-12, (j, product[j], value)
+
+
+def test_split_half_rotation_of_one_hand_rotated_vector():
+    """Head size 4, theta 10000 (frequencies 1 and 0.01), position 3: the pairs are
+    (x0, x2) and (x1, x3).  x = (1, 2, 3, 4):
+    x0' = cos 3 - 3 sin 3, x2' = 3 cos 3 + sin 3; x1' = 2 cos .03 - 4 sin .03, x3' = 4 cos .03 + 2 sin .03."""
+    cfg = dict(head_dim=4, hidden_size=4, num_attention_heads=1, rope_theta=10000.0)
+    x = torch.tensor([[[1.0, 2.0, 3.0, 4.0]]], dtype=torch.float64)
+    out = P.plain_apply_rope(x, torch.tensor([3]), P.plain_rope_frequencies(cfg))[0, 0]
+    want = [-1.413352520780047, 1.8791180666879925, -2.828857481741469, 4.058191135400942]
+    for got, w in zip(out.tolist(), want):
+        assert abs(got - w) < 1e-6, (out.tolist(), want)      # float32 angle: 0.03 is rounded
+
+
+def test_attention_of_three_tokens_by_explicit_softmax():
+    """One head of size 2, no position encoding: token t sees keys 0..t, scores scaled by
+    2^-0.5, weights by explicit exponentials."""
+    import math
+
+    q = torch.tensor([[[1.0, 0.0]], [[0.0, 2.0]], [[1.0, 1.0]]], dtype=torch.float64)
+    k = torch.tensor([[[1.0, 1.0]], [[2.0, 0.0]], [[0.0, 3.0]]], dtype=torch.float64)
+    v = torch.tensor([[[1.0, 10.0]], [[2.0, 20.0]], [[4.0, 40.0]]], dtype=torch.float64)
+    out = P.plain_attention(q, k, v)[:, 0]
+    s = 2 ** -0.5
+    rows = [[1.0],                                             # token 0: its own key only
+            [math.exp(2 * s), math.exp(0.0)],                  # q1.k0 = 2, q1.k1 = 0
+            [math.exp(2 * s), math.exp(2 * s), math.exp(3 * s)]]
+    for t, weights in enumerate(rows):
+        z = sum(weights)
+        want0 = sum(w * v[j, 0, 0].item() for j, w in enumerate(weights)) / z
+        assert abs(out[t, 0].item() - want0) < 1e-12 and abs(out[t, 1].item() - 10 * want0) < 1e-11
