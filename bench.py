@@ -1,16 +1,23 @@
 #!/usr/bin/env python3
 """Headline benchmark: decode tokens/s of the Orpheus-3B-sized Llama decoder (random
-weights, bfloat16) at batch 8 with 2,048-token cached prompts, on one B200.
+weights, bfloat16) at batch 8 with 2,048-token cached prompts and pages of 16 tokens, on
+one B200.
 
-    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--rounds R] [--page-size P]
+                    [--impl ours|reference] [--workloads all|none|mixed64|long8]
 
 One JSON line on stdout.  ``value``: decoded tokens per second of the engine's step
-function plus greedy sampling, timed on the device with CUDA events.  ``e2e``: the same
-through the Python entry point (``LLM.step``), host token ids in and out.  ``prefill``:
-one 2,048-token prompt in one step.  ``roofline``: bytes a decode step has to read (every
-weight once, and the cache of the live requests) over its time, against the measured
-copy bandwidth.  ``points``: decode at batch 1 and 64.  A step is one decode step; every
-step reads all weights (6.6 GB), far more than the 126 MB L2, so no L2 flush is needed.
+function plus greedy sampling, timed on the device with CUDA events: W warm-up steps, then
+R rounds of exactly K steps each; ``ms_per_step`` is the median round, the fastest and
+slowest are beside it.  ``e2e``: the same through the Python entry point (``LLM.step``),
+host token ids in and out.  ``prefill``: one 2,048-token prompt in one step.
+``roofline``: bytes a decode step has to read (every weight once, and the cache of the
+live requests) over its time, against the measured copy bandwidth.  ``points``: decode at
+batch 1 and 64, batch 8 with pages of 64 tokens, and two serving workloads through the
+entry point at other sizes of the architecture (64 mixed requests at the Llama 3.2 1B
+sizes, 8 long prompts in portions at the Llama 3.1 8B sizes), each as generated tokens per
+second and median time to the first token.  A step is one decode step; every step reads
+all weights (6.6 GB), far more than the 126 MB L2, so no L2 flush is needed.
 """
 from __future__ import annotations
 
@@ -27,7 +34,8 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-# Layer sizes of the benchmark model: Orpheus 3B / Llama 3.2 3B (BASELINE configs[2]).
+# Layer sizes of the benchmark model: Orpheus 3B / Llama 3.2 3B
+# (mstar/model/orpheus/config.py:4-23).
 ORPHEUS_3B = dict(
     architectures=["LlamaForCausalLM"], num_hidden_layers=28, hidden_size=3072,
     num_attention_heads=24, num_key_value_heads=8, head_dim=128, intermediate_size=8192,
@@ -47,7 +55,7 @@ SIZES = {"orpheus-3b": ("Orpheus 3B / Llama 3.2 3B", ORPHEUS_3B),
          "llama-1b": ("Llama 3.2 1B", LLAMA_1B), "llama-8b": ("Llama 3.1 8B", LLAMA_8B)}
 PROMPT_LEN = 2048
 CONTEXT = 4096
-PAGE_SIZE = 64
+PAGE_SIZE = 16          # the default of --page-size; kernel_bench reads the global
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -91,7 +99,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._stop.wait(0.2)
+            self._stop.wait(0.05)
 
     def __enter__(self):
         self._thread = threading.Thread(target=self._run, daemon=True)
@@ -149,9 +157,10 @@ def prompts(batch: int, vocab: int, length: int, seed: int = 1) -> list:
     return torch.randint(0, vocab, (batch, length), generator=g).tolist()
 
 
-def time_decode(stepper, batch: int, cfg: dict, steps: int, warmup: int) -> dict:
-    """B requests with PROMPT_LEN cached tokens each; W + K decode steps of the step
-    function plus greedy sampling, K of them timed with CUDA events."""
+def time_decode(stepper, batch: int, cfg: dict, steps: int, warmup: int, rounds: int = 1) -> dict:
+    """B requests with PROMPT_LEN cached tokens each; W warm-up decode steps of the step
+    function plus greedy sampling, then ``rounds`` rounds of exactly K steps, each round timed
+    with CUDA events.  The median round is the result; fastest and slowest are reported."""
     import torch
 
     from mstar_b200 import ops
@@ -159,7 +168,8 @@ def time_decode(stepper, batch: int, cfg: dict, steps: int, warmup: int) -> dict
     from mstar_b200.ops import lib
 
     ids = [f"d{batch}-{i}" for i in range(batch)]
-    toks = prompts(batch, cfg["vocab_size"], PROMPT_LEN + warmup + steps + 1, seed=batch)
+    total = warmup + rounds * steps
+    toks = prompts(batch, cfg["vocab_size"], PROMPT_LEN + total + 1, seed=batch)
     for rid, t in zip(ids, toks):
         stepper.add_request(rid)
         stepper.step([StepEntry(rid, t[:PROMPT_LEN], ())])
@@ -173,23 +183,27 @@ def time_decode(stepper, batch: int, cfg: dict, steps: int, warmup: int) -> dict
     for k in range(warmup):
         one(k)
     torch.cuda.synchronize()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches0 = lib.launch_count()
-    start.record()
-    for k in range(warmup, warmup + steps):
-        one(k)
-    end.record()
-    torch.cuda.synchronize()
-    ms = start.elapsed_time(end) / steps
-    launches = lib.launch_count() - launches0
-    kv_lens = [PROMPT_LEN + warmup + steps // 2] * batch
+    times, launches = [], 0
+    for r in range(rounds):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        launches0 = lib.launch_count()
+        start.record()
+        for k in range(warmup + r * steps, warmup + (r + 1) * steps):
+            one(k)
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end) / steps)
+        launches = lib.launch_count() - launches0
+    ops.check_error_word(stepper.device)
+    ms = statistics.median(times)
+    kv_lens = [PROMPT_LEN + warmup + (rounds * steps) // 2] * batch
     for rid in ids:
         stepper.free_request(rid)
-    return {"ms_per_step": ms, "tokens_per_s": batch / (ms / 1e3), "launches": launches,
-            "kv_lens": kv_lens}
+    return {"ms_per_step": ms, "ms_min": min(times), "ms_max": max(times),
+            "tokens_per_s": batch / (ms / 1e3), "launches": launches, "kv_lens": kv_lens}
 
 
-def time_prefill(stepper, cfg: dict, reps: int = 3) -> dict:
+def time_prefill(stepper, cfg: dict, reps: int = 5) -> dict:
     import torch
 
     from mstar_b200.engine.step import StepEntry
@@ -213,35 +227,107 @@ def time_prefill(stepper, cfg: dict, reps: int = 3) -> dict:
             "flops": flops_of_step(cfg, [PROMPT_LEN], [PROMPT_LEN], 1)}
 
 
-def time_e2e(model, batch: int, cfg: dict, steps: int, warmup: int, num_pages: int) -> dict:
+def time_e2e(model, batch: int, cfg: dict, steps: int, warmup: int, num_pages: int,
+             page_size: int, rounds: int = 1) -> dict:
     """The same decode steps through the public entry point: host token ids in (pinned
-    index buffer copied to the device every step) and sampled token ids read back."""
+    index buffer copied to the device every step) and sampled token ids read back; wall
+    clock around ``rounds`` rounds of K steps, the median round reported."""
     import torch
 
     from mstar_b200 import LLM, SamplingParams
 
-    llm = LLM(model, page_size=PAGE_SIZE, max_num_pages=num_pages,
+    llm = LLM(model, page_size=page_size, max_num_pages=num_pages,
               max_num_batched_tokens=PROMPT_LEN, max_concurrent_requests=max(batch, 1),
               max_batch_size=max(batch, 1))
     params = SamplingParams(temperature=0.0, ignore_eos=True,
-                            max_output_tokens=warmup + steps + batch + 8)
+                            max_output_tokens=warmup + rounds * steps + batch + 8)
     for i, t in enumerate(prompts(batch, cfg["vocab_size"], PROMPT_LEN, seed=7 + batch)):
         llm.add_request(t, params, request_id=f"e{i}")
     while any(r.num_pending() > 1 for r in llm.scheduler.running) or llm.scheduler.waiting:
         llm.step()                                   # prompts, one per step
     for _ in range(warmup):
         llm.step()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        llm.step()
-    torch.cuda.synchronize()
-    seconds = time.perf_counter() - t0
+    times = []
+    for _ in range(rounds):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            llm.step()
+        torch.cuda.synchronize()
+        times.append((time.perf_counter() - t0) / steps * 1e3)
+    ms = statistics.median(times)
     h2d = llm.stepper.last_h2d_bytes
     for r in list(llm.scheduler.running):
         llm.scheduler.abort(r.request_id)
-    return {"tokens_per_s": batch * steps / seconds, "ms_per_step": seconds / steps * 1e3,
-            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch}
+    # tokens out: 4 bytes a request, and the 4-byte word kernels report a given-up wait in
+    return {"tokens_per_s": batch / (ms / 1e3), "ms_per_step": ms, "ms_min": min(times),
+            "ms_max": max(times), "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": 4 * batch + 4}
+
+
+# ------------------------------------------------------------------ serving workloads
+WORKLOADS = {
+    # 64 requests at once, prompts of 16 to 2,048 tokens, 256 new tokens each
+    "mixed64": dict(sizes="llama-1b", requests=64, prompt=(16, 2048), new_tokens=256,
+                    budget=2048),
+    # 8 prompts of 8,192 tokens, computed in portions of 2,048, 128 new tokens each
+    "long8": dict(sizes="llama-8b", requests=8, prompt=(8192, 8192), new_tokens=128,
+                  budget=2048),
+}
+
+
+def run_workload(name: str, page_size: int) -> dict:
+    """A whole serving run through the entry point: all requests are handed over at time
+    zero, the scheduler admits, cuts prompts into portions under its token budget, decodes
+    and frees.  Run twice (the first run captures the decode graphs and compiles nothing
+    else); the second is timed by the wall clock.  Greedy sampling, no stop token."""
+    import numpy as np
+    import torch
+
+    from mstar_b200 import LLM, SamplingParams
+
+    w = WORKLOADS[name]
+    model_name, cfg = SIZES[w["sizes"]]
+    print(f"[bench] workload {name}: {w['requests']} requests at the {model_name} sizes ...",
+          file=sys.stderr, flush=True)
+    model = build_model(dict(cfg), seed=2)
+    rng = np.random.default_rng(5)
+    lens = rng.integers(w["prompt"][0], w["prompt"][1] + 1, size=w["requests"]).tolist()
+    g = torch.Generator().manual_seed(11)
+    prompt_ids = [torch.randint(0, cfg["vocab_size"], (n,), generator=g).tolist() for n in lens]
+    pages = sum(-(-(n + w["new_tokens"]) // page_size) for n in lens) + 64
+    llm = LLM(model, page_size=page_size, max_num_pages=pages,
+              max_num_batched_tokens=w["budget"], max_concurrent_requests=w["requests"],
+              max_batch_size=w["requests"])
+    params = SamplingParams(temperature=0.0, ignore_eos=True, max_output_tokens=w["new_tokens"])
+    result = {}
+    for run in ("warm-up", "timed"):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        ids = [llm.add_request(p, params, request_id=f"{name}-{run}-{i}")
+               for i, p in enumerate(prompt_ids)]
+        waiting = {r.request_id: r for r in llm.scheduler.waiting}
+        first: dict = {}
+        done = 0
+        while llm.has_unfinished():
+            done += len(llm.step())
+            if len(first) < len(ids):
+                now = time.perf_counter() - t0
+                for rid, r in waiting.items():
+                    if rid not in first and r.output and r.output[0] is not None:
+                        first[rid] = now
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - t0
+        assert done == len(ids) and len(first) == len(ids)
+        generated = w["requests"] * w["new_tokens"]
+        result = {"tokens_per_s": generated / seconds, "seconds": seconds,
+                  "ttft_ms_median": statistics.median(first.values()) * 1e3,
+                  "ttft_ms_max": max(first.values()) * 1e3,
+                  "prompt_tokens": sum(lens), "generated_tokens": generated,
+                  "steps": llm.stats.steps, "preemptions": llm.stats.preemptions}
+        llm.stats.steps = 0
+    del llm, model
+    torch.cuda.empty_cache()
+    return result
 
 
 # --------------------------------------------------------------- single kernels
@@ -391,25 +477,43 @@ def kernel_bench(name: str, batch: int, ctx: int, small: bool, cfg: dict) -> int
     return 0
 
 
-def reference_arm() -> int:
-    print(json.dumps({
-        "impl": "reference",
-        "unavailable": "t-avil/mstar installs offline with --no-deps, but its stock path "
-                       "(mstar serve orpheus) fetches the checkpoint, its tokenizer and the SNAC "
-                       "codec from the Hugging Face hub and needs the mooncake and snac "
-                       "packages; there is no network and neither package is installed"}))
+def reference_arm(args) -> int:
+    """The reference's own engine on the same workload, in a process of its own that
+    imports nothing of this package (baseline/run_reference.py); its JSON line is passed
+    on.  If that process dies without a line, the reason is printed as ``unavailable``."""
+    cmd = [sys.executable, str(ROOT / "baseline" / "run_reference.py"), "--steps", str(args.steps),
+           "--warmup", str(args.warmup), "--rounds", str(args.rounds), "--batch", str(args.batch),
+           "--page-size", str(args.page_size)]
+    if args.layers:
+        cmd += ["--layers", str(args.layers)]
+    try:
+        proc = subprocess.run(cmd, stdout=subprocess.PIPE, text=True, timeout=3000)
+        lines = [ln for ln in proc.stdout.splitlines() if ln.startswith("{")]
+        if lines:
+            print(lines[-1])
+            return 0
+        why = f"baseline/run_reference.py exited with {proc.returncode} and printed no record"
+    except subprocess.TimeoutExpired:
+        why = "baseline/run_reference.py did not finish within 3000 s"
+    print(json.dumps({"impl": "reference", "unavailable": why}))
     return 0
 
 
 def main() -> int:
+    global PAGE_SIZE
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--rounds", type=int, default=5,
+                    help="rounds of --steps timed steps; the median round is reported")
+    ap.add_argument("--page-size", type=int, default=PAGE_SIZE, help="tokens per cache page")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the model has (named in the record)")
+    ap.add_argument("--workloads", default="all", choices=["all", "none", *sorted(WORKLOADS)],
+                    help="serving workloads through the entry point, reported under points")
     ap.add_argument("--kernel", default=None,
                     help="time one kernel alone (decode_attention, prefill_attention, gemm_qkv, "
                          "gemm_o, gemm_gate_up, gemm_down, gemm_lm_head, qkv_rope, add_rmsnorm, "
@@ -420,14 +524,16 @@ def main() -> int:
                     help="layer sizes; the default is the benchmark model")
     args = ap.parse_args()
     model_name, sizes = SIZES[args.sizes]
-    if args.kernel:
-        return kernel_bench(args.kernel, args.batch, args.ctx, args.small, sizes)
-    if args.impl == "reference":
-        return reference_arm()
+    PAGE_SIZE = page = args.page_size
     if args.gpus != 1:
         print(f"bench.py measures a single-GPU engine: --gpus {args.gpus} is not supported")
         return 2
+    if args.kernel:
+        return kernel_bench(args.kernel, args.batch, args.ctx, args.small, sizes)
+    if args.impl == "reference":
+        return reference_arm(args)
     warmup = max(args.warmup, 3)
+    rounds = max(args.rounds, 1)
 
     import torch
 
@@ -442,34 +548,58 @@ def main() -> int:
     print("[bench] building the random-weight model ...", file=sys.stderr, flush=True)
     model = build_model(cfg)
     max_batch = max(64, args.batch)
-    pages = max_batch * (CONTEXT // PAGE_SIZE) + 64
-    stepper = make_stepper(model, page_size=PAGE_SIZE, num_pages=pages, num_slots=max_batch + 4)
+    pages = max_batch * (CONTEXT // page) + 64
+    stepper = make_stepper(model, page_size=page, num_pages=pages, num_slots=max_batch + 4)
 
     print("[bench] prefill ...", file=sys.stderr, flush=True)
     pre = time_prefill(stepper, cfg)
     print("[bench] decode ...", file=sys.stderr, flush=True)
     with ClockSampler() as clocks:
-        head = time_decode(stepper, args.batch, cfg, args.steps, warmup)
+        head = time_decode(stepper, args.batch, cfg, args.steps, warmup, rounds)
     # the same steps through the entry point, directly after the device-timed ones (the
     # long batch-64 run below leaves the GPU under its power cap)
     print("[bench] end to end ...", file=sys.stderr, flush=True)
     e2e = time_e2e(model, args.batch, cfg, args.steps, warmup,
-                   args.batch * (CONTEXT // PAGE_SIZE) + 64)
+                   args.batch * (CONTEXT // page) + 64, page, rounds)
     print("[bench] decode at batch 1 and 64 ...", file=sys.stderr, flush=True)
     points = {}
     for b in (1, 64):
-        r = time_decode(stepper, b, cfg, max(args.steps // 2, 8), warmup)
+        r = time_decode(stepper, b, cfg, max(args.steps // 2, 8), warmup, min(rounds, 3))
         points[f"decode_b{b}"] = round(r["tokens_per_s"], 1)
+    del stepper
+    torch.cuda.empty_cache()
+    other = 64 if page != 64 else 16
+    print(f"[bench] decode with pages of {other} ...", file=sys.stderr, flush=True)
+    stepper = make_stepper(model, page_size=other,
+                           num_pages=args.batch * (CONTEXT // other) + 64,
+                           num_slots=args.batch + 4)
+    r = time_decode(stepper, args.batch, cfg, args.steps, warmup, min(rounds, 3))
+    points[f"decode_b{args.batch}_page{other}"] = round(r["tokens_per_s"], 1)
     del stepper
     torch.cuda.empty_cache()
 
     step_bytes = bytes_of_decode_step(cfg, model, head["kv_lens"])
     achieved = step_bytes / (head["ms_per_step"] / 1e3) / 1e9
+    parameter_gb = model.parameter_bytes() / 1e9
+    del model
+    torch.cuda.empty_cache()
+    chosen = sorted(WORKLOADS) if args.workloads == "all" else (
+        [] if args.workloads == "none" else [args.workloads])
+    for name in chosen:
+        w = run_workload(name, page)
+        tag = f"{name}_{WORKLOADS[name]['sizes'].replace('-', '')}"
+        points[f"{tag}_tok_s"] = round(w["tokens_per_s"], 1)
+        points[f"{tag}_ttft_ms"] = round(w["ttft_ms_median"], 1)
+        points[f"{tag}_seconds"] = round(w["seconds"], 3)
+        print(f"[bench] {name}: {json.dumps(w)}", file=sys.stderr, flush=True)
+
     record = {
         "metric": f"decode tok/s at batch {args.batch} ({model_name.split(' / ')[0]} bf16, "
                   "2,048-token cached prompts)",
         "value": round(head["tokens_per_s"], 1), "unit": "tokens/s", "n_gpus": 1,
         "steps": args.steps, "warmup": warmup, "ms_per_step": round(head["ms_per_step"], 4),
+        "rounds": rounds, "ms_per_step_min": round(head["ms_min"], 4),
+        "ms_per_step_max": round(head["ms_max"], 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic token ids, random-init weights N(0, 0.02)",
         "config": {
@@ -481,13 +611,15 @@ def main() -> int:
             "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
             "tied_embeddings": cfg["tie_word_embeddings"],
             "rope": f"theta 5e5, llama3 x{cfg['rope_scaling']['factor']:g} (1, 4, 8192)",
-            "rms_eps": cfg["rms_norm_eps"], "page_size": PAGE_SIZE,
-            "l2": f"inputs larger than L2 (weights {model.parameter_bytes() / 1e9:.1f} GB per step)",
+            "rms_eps": cfg["rms_norm_eps"], "page_size": page,
+            "l2": f"inputs larger than L2 (weights {parameter_gb:.1f} GB per step)",
             "peaks": pk["source"]},
         "e2e": {"value": round(e2e["tokens_per_s"], 1), "unit": "tokens/s",
                 "h2d_bytes_per_step": e2e["h2d_bytes_per_step"],
                 "d2h_bytes_per_step": e2e["d2h_bytes_per_step"],
-                "ms_per_step": round(e2e["ms_per_step"], 4)},
+                "ms_per_step": round(e2e["ms_per_step"], 4),
+                "ms_per_step_min": round(e2e["ms_min"], 4),
+                "ms_per_step_max": round(e2e["ms_max"], 4)},
         "gpu_launches": head["launches"],
         "clocks": clocks.summary(),
         "prefill": {"value": round(pre["tokens_per_s"], 1), "tokens": PROMPT_LEN,
