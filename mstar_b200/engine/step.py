@@ -14,6 +14,7 @@ nothing changed (the reference reports allocation_failed, kv_cache_engine.py:693
 """
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 from typing import Hashable, Optional, Sequence
 
@@ -67,7 +68,11 @@ class DecodeGraph:
     RING = 3
 
     def __init__(self, stepper: "Stepper", bucket: int, widths: list):
-        self.stepper = stepper
+        # no reference back to the stepper: a stepper and its graphs must not form a cycle,
+        # or they would be freed by the cyclic collector at a moment of its choosing, which
+        # may be the middle of another graph's capture (freeing device memory there
+        # invalidates that capture)
+        self.manager, self.storage = stepper.manager, stepper.storage
         self.bucket = bucket
         self.widths = list(widths)
         mgr, storage = stepper.manager, stepper.storage
@@ -108,9 +113,16 @@ class DecodeGraph:
         torch.cuda.synchronize(stepper.device)
         self.graph = torch.cuda.CUDAGraph()
         before = ops_lib.launch_count()
-        with torch.cuda.graph(self.graph):
-            self.logits = model.forward(self.token_ids, self.ctx, storage, self.tables,
-                                        self.want_rows)
+        # and no collection of other garbage while the capture is under way
+        collecting = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph):
+                self.logits = model.forward(self.token_ids, self.ctx, storage, self.tables,
+                                            self.want_rows)
+        finally:
+            if collecting:
+                gc.enable()
         self.launches = ops_lib.launch_count() - before   # own kernels in one replay
 
     def _stage(self, requests: list, tokens: list, sources) -> int:
@@ -123,10 +135,10 @@ class DecodeGraph:
             self.events[turn].synchronize()               # its last copy has been read
         pinned = self.pinned[turn]
         n = len(requests)
-        index = self.stepper.manager.fill_batch(
+        index = self.manager.fill_batch(
             requests, [1] * n, extra=self.extra, alloc=lambda size: pinned.numpy(),
             widths=self.widths, pad_entries=self.bucket - n, pad_page=self.pad_pages,
-            pad_slot=self.stepper.storage.pad_slot)
+            pad_slot=self.storage.pad_slot)
         off, length = index.offsets["token_ids"]
         index.packed[off:off + n] = tokens
         index.packed[off + n:off + length] = 0
@@ -146,8 +158,7 @@ class DecodeGraph:
         """``sources``: per request, the index into the stepper's device tokens (the
         sampler's output of the step before) that replaces ``tokens[i]`` without the host
         ever seeing the value, or -1."""
-        nbytes = self._stage(requests, tokens, sources)
-        self.stepper.last_h2d_bytes = nbytes
+        self._stage(requests, tokens, sources)
         self.graph.replay()
         ops_lib.add_launches(self.launches)
         return self.logits[:len(requests)]
@@ -305,6 +316,7 @@ class Stepper:
         if pending:
             sources = [pending.get(i, -1) for i in range(len(entries))]
         logits = graph.run(requests, [e.tokens[0] for e in entries], sources)
+        self.last_h2d_bytes = graph.size * 4
         for request in requests:
             self.manager.commit(request, 1)
         self.steps += 1

@@ -414,6 +414,51 @@ def _gemm_smallm(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, gated
     return out
 
 
+# Rows up to which the swapped-operand tcgen05 kernel is used (tokens are the MMA's N
+# dimension: 32, 64 or 128), the rows of W to one of its tiles, and the tiles per SM from
+# which on it is used: each CTA takes one tile and all of K, so only a matrix of many tiles
+# (a vocabulary-wide head) fills the GPU several times over; with few tiles the library's
+# cut along K wins.
+SKINNY_MAX = 128
+SKINNY_ROWS = 128
+SKINNY_TILES_PER_SM = 4
+
+
+def _skinny_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Whether the product of ``SMALL_M`` < M <= ``SKINNY_MAX`` bfloat16 rows goes to the
+    swapped-operand tcgen05 kernel (MSTAR_SKINNY=0: nowhere, 1: for every width)."""
+    if not (SMALL_M < x.shape[0] <= SKINNY_MAX and _tc_ok(x, w)):
+        return False
+    forced = os.environ.get("MSTAR_SKINNY")
+    if forced is not None:
+        return forced != "0"
+    return -(-w.shape[0] // SKINNY_ROWS) >= SKINNY_TILES_PER_SM * num_sms(x.device)
+
+
+def gemm_skinny(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
+                static_weights: bool = False):
+    """x[M,K] @ w[N,K]^T for up to 128 bfloat16 rows on the tcgen05 tensor cores with the
+    operands swapped (rows of W are the MMA's M dimension, the tokens its N dimension)."""
+    _need_cuda(x, w)
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16
+    assert x.stride(1) == 1 and w.stride(1) == 1 and x.shape[1] == w.shape[1]
+    m, k = x.shape
+    n = w.shape[0]
+    out_dtype = out_dtype or torch.bfloat16
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+    code = lib.get("gemm_skinny").mstar_gemm_skinny_bf16(
+        x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), w.stride(0),
+        out.stride(0), _dt(out), int(static_weights),
+        tcgen05_error_word(x.device).data_ptr(), _stream())
+    if code == -1:
+        raise KernelError(f"skinny GEMM refuses M={m}, N={n}, K={k} (at most {SKINNY_MAX} rows, "
+                          "K and row strides multiples of 8, operands 16-byte aligned)")
+    if code in (-3, -4):
+        raise KernelError(f"skinny GEMM could not make its TMA tensor map (code {code})")
+    check(code, "gemm_skinny")
+    return out
+
+
 def qkv_rope_write(x: torch.Tensor, w_qkv: torch.Tensor, positions, cache_pos, token_req,
                    block_table, inv_freq, kv_cache, num_heads: int, num_kv_heads: int,
                    head_dim: int, page_size: int, static_weights: bool = False):
@@ -454,7 +499,8 @@ _tc_error_words: dict = {}
 def tcgen05_error_word(device) -> torch.Tensor:
     """Device int32 that a kernel with bounded mbarrier waits sets when one of them ran out:
     1-3 tcgen05 GEMM (producer, MMA issuer, epilogue), 4 decode attention copies, 6-12 tcgen05
-    prefill attention, 13-14 bulk-copy small-M GEMM; zero otherwise."""
+    prefill attention, 13-14 bulk-copy small-M GEMM, 15-17 swapped-operand tcgen05 GEMM; zero
+    otherwise."""
     key = torch.device(device).index or 0
     if key not in _tc_error_words:
         _tc_error_words[key] = torch.zeros(1, dtype=torch.int32, device=device)
@@ -470,6 +516,9 @@ WAIT_CODES = {
     13: "bulk-copy small-M GEMM: the producer waited for a free stage",
     14: "bulk-copy small-M GEMM: a consumer waited for weights",
 }
+WAIT_CODES.update({15: "swapped-operand tcgen05 GEMM: the producer waited for a free stage",
+                   16: "swapped-operand tcgen05 GEMM: the MMA issuer waited for operand tiles",
+                   17: "swapped-operand tcgen05 GEMM: the epilogue waited for the accumulator"})
 WAIT_CODES.update({c: "tcgen05 prefill attention: a wait on one of its barriers ran out"
                    for c in range(6, 13)})
 
@@ -547,21 +596,24 @@ def _tc_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
             and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def tcgen05_tile(m: int, n: int) -> int | None:
-    """Which tcgen05 kernel takes an [m, K] x [n, K]^T product, or None for the library
-    GEMM: 256 = lone CTAs with 128 x 256 tiles, 1024 = persistent CTA pairs with 256 x 256
-    tiles (512: the same pairs, one tile each).
-    The hand-written kernels are used where their grid fills the GPU: very wide
-    matrices (the LM head) at any row count, and wide ones (gate/up) at prompt size.
+def tcgen05_tile(m: int, n: int, sms: int | None = None) -> int | None:
+    """Which tcgen05 kernel takes an [m, K] x [n, K]^T product of more than ``SKINNY_MAX``
+    rows, or None for the library GEMM: 256 = lone CTAs with 128 x 256 tiles, 1024 =
+    persistent CTA pairs with 256 x 256 tiles (512: the same pairs, one tile each).
+    The hand-written kernels are used where their tiles fill the GPU: up to 256 rows when
+    there is a 128 x 256 tile or more for every SM (a vocabulary-wide head), beyond when the
+    256 x 256 tiles make three waves or more over the CTA pairs (below, the library's finer
+    tiles win: measured at 96 to 160 tiles on 74 pairs).
     ``MSTAR_GEMM=tcgen05`` forces them everywhere, ``MSTAR_GEMM=library`` nowhere."""
-    import os
-
     forced = os.environ.get("MSTAR_GEMM", "")
     if forced == "library":
         return None
-    if n >= 32768:
-        return 256 if m <= 256 else 1024
-    if m >= 1024 and n >= 8192:
+    if sms is None:
+        sms = num_sms()
+    if m <= 256:
+        if -(-n // 256) >= sms:
+            return 256
+    elif -(-m // 256) * -(-n // 256) >= 3 * (sms // 2):
         return 1024
     if forced == "tcgen05":
         return 1024 if m > 128 else 256
@@ -570,16 +622,15 @@ def tcgen05_tile(m: int, n: int) -> int | None:
 
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = None,
            static_weights: bool = False):
-    """x[M,K] @ w[N,K]^T.  bfloat16 with at most ``SMALL_M`` rows: this package's
-    weight-streaming kernel; more rows: this package's tcgen05 kernels where
-    ``tcgen05_tile`` says so, else the library GEMM; anything involving a float32
-    operand runs in true float32.  ``static_weights`` promises that no kernel earlier on
-    the stream writes ``w`` (model parameters): the weight-streaming kernel then starts
-    its copies while the kernel before it is still draining."""
+    """x[M,K] @ w[N,K]^T.  bfloat16: this package's weight-streaming kernel for at most
+    ``SMALL_M`` rows, its swapped-operand tcgen05 kernel up to ``SKINNY_MAX`` rows, its
+    tiled tcgen05 kernels where ``tcgen05_tile`` says so, else the library GEMM; anything
+    involving a float32 operand runs in true float32.  ``static_weights`` promises that no
+    kernel earlier on the stream writes ``w`` (model parameters): the kernels for few rows
+    then start their weight copies while the kernel before them is still draining."""
     bf16 = x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_cuda and w.is_cuda
     m, n = x.shape[0], w.shape[0]
-    if (bf16 and out_dtype is None and m > SMALL_M and n < 8192
-            and os.environ.get("MSTAR_GEMM") is None):
+    if bf16 and out_dtype is None and m > SKINNY_MAX and tcgen05_tile(m, n) is None:
         # the common case of a prompt portion on a narrow projection, decided first: this
         # function runs a hundred times in a step that the host has to get launched
         return torch.mm(x, w.t())
@@ -587,6 +638,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype | None = Non
     out_dtype = out_dtype or x.dtype
     if out_dtype in (torch.bfloat16, torch.float32) and _smallm_ok(x, w):
         return _gemm_smallm(x, w, out_dtype, gated=False, static_weights=static_weights)
+    if out_dtype in (torch.bfloat16, torch.float32) and _skinny_ok(x, w):
+        return gemm_skinny(x, w, out_dtype, static_weights=static_weights)
     if out_dtype in (torch.bfloat16, torch.float32) and _tc_ok(x, w):
         tile = tcgen05_tile(x.shape[0], w.shape[0])
         if tile is not None:

@@ -40,6 +40,7 @@ LIBRARIES = {
     "gemm_smallm": ("cuda", ["gemm_smallm.cu"], []),
     "gemm_smallm_bulk": ("cuda", ["gemm_smallm_bulk.cu"], []),
     "gemm_tcgen05": ("cuda", ["gemm_tcgen05.cu"], []),
+    "gemm_skinny": ("cuda", ["gemm_skinny.cu"], []),
     "sampling": ("cuda", ["sampling.cu"], []),
     "host": ("host", ["host/cache_manager.cpp"], []),
 }

@@ -62,6 +62,9 @@ _SIGNATURES = {
         "mstar_gemm_tcgen05_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
         "mstar_gemm_tcgen05_gated_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp, _vp],
     },
+    "gemm_skinny": {
+        "mstar_gemm_skinny_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
+    },
     "sampling": {
         "mstar_sample": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
         "mstar_argmax": [_vp, _i, _i, _i, _vp, _vp],

@@ -756,3 +756,48 @@ def test_tcgen05_refusals_and_dispatch(monkeypatch):
     assert ops.tcgen05_tile(2048, 3072) == 1024
     monkeypatch.setenv("MSTAR_GEMM", "library")
     assert ops.tcgen05_tile(2048, 16384) is None
+
+
+# ------------------------------------------------------------ swapped-operand tcgen05 GEMM
+@pytest.mark.parametrize("m", [17, 32, 33, 64, 100, 128])
+@pytest.mark.parametrize("n,k", [(300, 136), (130, 4096), (5120, 3072), (1000, 776), (33001, 64)])
+def test_skinny_gemm(m, n, k):
+    """17 to 128 rows with W as the MMA's M operand: row counts on both sides of the three
+    token widths, output widths and K that are no multiples of the tiles."""
+    from mstar_b200 import ops
+
+    x = rnd(m, k, dtype=torch.bfloat16, seed=m + k)
+    w = rnd(n, k, dtype=torch.bfloat16, seed=n, scale=0.1)
+    want = x.double() @ w.double().T
+    y = ops.gemm_skinny(x, w, torch.bfloat16)
+    y32 = ops.gemm_skinny(x, w, torch.float32, static_weights=True)
+    assert tc_clean() == 0
+    assert (y32.double() - want).abs().max() < 2e-4 * math.sqrt(k) * max(1.0, want.abs().max().item() / 8)
+    assert (y.double() - want).abs().max() < 0.01 * want.abs().max() + 1e-3
+    # a view into a wider buffer: the row stride goes into the tensor map
+    wide = torch.zeros(m, k + 64, dtype=torch.bfloat16, device=DEV)
+    wide[:, :k] = x
+    assert torch.equal(ops.gemm_skinny(wide[:, :k], w, torch.bfloat16), y)
+    assert tc_clean() == 0
+
+
+def test_skinny_gemm_refusals_and_dispatch(monkeypatch):
+    from mstar_b200 import ops
+
+    x = rnd(129, 64, dtype=torch.bfloat16)
+    w = rnd(64, 64, dtype=torch.bfloat16)
+    with pytest.raises(ops.KernelError, match="refuses"):
+        ops.gemm_skinny(x, w)
+    with pytest.raises(ops.KernelError, match="refuses"):
+        ops.gemm_skinny(rnd(20, 20, dtype=torch.bfloat16), rnd(64, 20, dtype=torch.bfloat16))
+    assert ops.linear(x, w).shape == (129, 64)             # the library product takes it
+    # chosen for a matrix of several tiles per SM only (a vocabulary-wide head)
+    wide = torch.empty(ops.SKINNY_TILES_PER_SM * ops.num_sms() * 128, 64, dtype=torch.bfloat16,
+                       device=DEV)
+    assert ops._skinny_ok(x[:64], wide) and not ops._skinny_ok(x[:64], w)
+    assert not ops._skinny_ok(x[:16], wide) and not ops._skinny_ok(x, wide)
+    monkeypatch.setenv("MSTAR_SKINNY", "0")
+    assert not ops._skinny_ok(x[:64], wide)
+    monkeypatch.setenv("MSTAR_SKINNY", "1")
+    assert ops._skinny_ok(x[:64], w)
+    assert torch.equal(ops.linear(x[:64], w), ops.gemm_skinny(x[:64], w))

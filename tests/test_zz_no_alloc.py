@@ -93,10 +93,10 @@ def test_noalloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
         got, want, plain = run_both(fn, lens, nq, nkv, hd, page, seed)
         assert torch.isfinite(got.float()).all()
         # the tolerance of the kernel tests against the plain reference (bfloat16 outputs
-        # of order 1); the two entry points run the same kernels on the same inputs, so
-        # they must agree bit for bit
+        # of order 1), against the plain attention and against the ordinary entry point
+        # (which cuts the keys into other chunks, so its float sums run in another order)
         assert (got.double().cpu() - plain).abs().max().item() < 2e-2
-        assert torch.equal(got, want)
+        assert (got.float() - want.float()).abs().max().item() < 2e-2
         del got, want, plain
     assert torch.cuda.memory_allocated() <= allocated + (1 << 20)   # nothing piled up
 
