@@ -112,6 +112,29 @@ class CacheStorage:
     def state_bytes_per_request(self) -> int:
         return sum(0 if s is None else s[0].numel() * s.element_size() for s in self.state)
 
+    @property
+    def has_state(self) -> bool:
+        return any(s is not None for s in self.state)
+
+    def snapshot_state(self, slots) -> Optional[tuple]:
+        """Copies of the state rows of ``slots`` (None when no mixer keeps state).  Mixers
+        update their state in place during the forward pass; the step function takes this
+        copy before the pass and puts it back if the pass fails, so that state, like the
+        lengths, moves only with a step that completed (the reference advances its sequence
+        state after the forward pass, mstar/engine/cache_manager.py:811-838)."""
+        if not self.has_state:
+            return None
+        index = torch.as_tensor(list(slots), dtype=torch.long, device=self.device)
+        return index, [None if s is None else s.index_select(0, index) for s in self.state]
+
+    def restore_state(self, snapshot) -> None:
+        if snapshot is None:
+            return
+        index, rows = snapshot
+        for s, saved in zip(self.state, rows):
+            if s is not None:
+                s.index_copy_(0, index, saved)
+
     def reset_slot(self, slot: int) -> None:
         """A request takes the slot: its state starts at zero."""
         for s in self.state:

@@ -291,8 +291,15 @@ class Stepper:
             token_source=(view("token_src"), self.device_tokens) if pending else None)
         tables = [view(f"table{g}").view(len(ordered), -1)
                   for g in range(len(self.manager.groups))]
-        logits = self.model.forward(view("token_ids"), ctx, self.storage, tables,
-                                    view("want_rows"))
+        # per-request state is written in place by the mixers that keep some: it is put back
+        # if the pass fails, so that state and lengths move together or not at all
+        saved = self.storage.snapshot_state(index.slots.tolist())
+        try:
+            logits = self.model.forward(view("token_ids"), ctx, self.storage, tables,
+                                        view("want_rows"))
+        except BaseException:
+            self.storage.restore_state(saved)
+            raise
         for request, count in zip(requests, counts):
             self.manager.commit(request, count)
         self.steps += 1
@@ -315,7 +322,14 @@ class Stepper:
         sources = None
         if pending:
             sources = [pending.get(i, -1) for i in range(len(entries))]
-        logits = graph.run(requests, [e.tokens[0] for e in entries], sources)
+        saved = None
+        if self.storage.has_state:
+            saved = self.storage.snapshot_state([self.manager.slot(r) for r in requests])
+        try:
+            logits = graph.run(requests, [e.tokens[0] for e in entries], sources)
+        except BaseException:
+            self.storage.restore_state(saved)
+            raise
         self.last_h2d_bytes = graph.size * 4
         for request in requests:
             self.manager.commit(request, 1)

@@ -178,16 +178,31 @@ def load_parameters(source, param_specs: Mapping[str, ParamSpec],
         raise WeightsError(ckpt.where, sorted(missing), unexpected, wrong_shape, other)
 
     params: dict = {}
+    kept_wide: list = []
     for param, spec in param_specs.items():
         if param in aliased:
             continue
         sources = by_param[param]
         stored = [ckpt.shape_dtype(s.name)[1] for s in sources]
         target = _target_dtype(spec, stored, dtype)
+        if target == torch.float32 and dtype != torch.float32 and len(spec.shape) > 1:
+            kept_wide.append(param)
         out = torch.empty(tuple(spec.shape), dtype=target, device=device)
         for s in sources:
             out.narrow(0, s.row_start, s.rows).copy_(ckpt.tensor(s.name))
         params[param] = out
+    if kept_wide:
+        # a tensor stored in 32 bits stays so; for a matrix that has a price worth saying
+        import warnings
+
+        shown = ", ".join(kept_wide[:4]) + (f" and {len(kept_wide) - 4} more" if len(kept_wide) > 4
+                                            else "")
+        warnings.warn(
+            f"{len(kept_wide)} matrices of {ckpt.where} are stored in 32 bits and stay float32 "
+            f"although the model runs in {str(dtype).replace('torch.', '')} ({shown}): they take "
+            "twice the memory, and their products run in the true-32-bit kernel instead of the "
+            "bfloat16 tensor-core kernels.  Convert the checkpoint to bfloat16 to avoid this.",
+            stacklevel=2)
     for param, target_name in aliased.items():
         if target_name not in params:
             raise WeightsError(ckpt.where, [], [], [],

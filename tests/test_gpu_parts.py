@@ -235,6 +235,7 @@ class QueryGrowth:
 class ToyConfig:
     architecture = "ToyMixedForCausalLM"
     EXPERTS, EXPERT_SIZE, RATE = 3, 40, 0.02
+    EMBED_MULT, LOGIT_SCALE, SOFTCAP = 1.5, 0.5, 4.0     # a scaled embedding, a capped head
     H, NH, NKV, HD, INTER, VOCAB, WINDOW, EPS = 64, 4, 2, 16, 96, 128, 8, 1e-5
 
     def to_dict(self):
@@ -248,8 +249,9 @@ class ToyConfig:
         return ()
 
     def layout(self):
-        from mstar_b200.config.layout import (AttentionSpec, BlockSpec, GatedMLPSpec,
-                                              ModelLayout, NormSpec, PositionSpec, RunEntry)
+        from mstar_b200.config.layout import (AttentionSpec, BlockSpec, EmbeddingSpec,
+                                              GatedMLPSpec, HeadSpec, ModelLayout, NormSpec,
+                                              PositionSpec, RunEntry)
         pos = PositionSpec("rope", self.HD, self.HD, 10000.0)
         norm = NormSpec(size=self.H, eps=self.EPS)
         ffn = GatedMLPSpec(hidden_size=self.H, intermediate_size=self.INTER)
@@ -273,7 +275,11 @@ class ToyConfig:
         order = [RunEntry(0, 0), RunEntry(1, 1), RunEntry(2, 0), RunEntry(3, 2), RunEntry(1, 3),
                  RunEntry(4, 4)]
         return ModelLayout(vocab_size=self.VOCAB, hidden_size=self.H, blocks=blocks, order=order,
-                           final_norm=norm, tie_word_embeddings=True)
+                           final_norm=norm, tie_word_embeddings=True,
+                           embedding=EmbeddingSpec(vocab_size=self.VOCAB, hidden_size=self.H,
+                                                   multiplier=self.EMBED_MULT),
+                           head=HeadSpec(vocab_size=self.VOCAB, hidden_size=self.H,
+                                         logit_scale=self.LOGIT_SCALE, softcap=self.SOFTCAP))
 
 
 def toy_checkpoint_map(config, layout):
@@ -295,7 +301,7 @@ def toy_plain_logits(w, cfg: ToyConfig, ids, margins=None):
     rope_cfg = dict(head_dim=cfg.HD, rope_theta=10000.0, hidden_size=cfg.H,
                     num_attention_heads=cfg.NH)
     inv = P.plain_rope_frequencies(rope_cfg)
-    h = w["toy.embed.weight"].double()[torch.tensor(ids)]
+    h = w["toy.embed.weight"].double()[torch.tensor(ids)] * cfg.EMBED_MULT
     kv_of_cache = {}
 
     def heads(x, mat, n):
@@ -344,7 +350,8 @@ def toy_plain_logits(w, cfg: ToyConfig, ids, margins=None):
             continue
         gu = w[f"{p}.ffn.gate_up.weight"]
         h = h + P.plain_swiglu(y, gu[:cfg.INTER], gu[cfg.INTER:], w[f"{p}.ffn.down.weight"])
-    return P.plain_rms_norm(h, w["toy.final_norm.weight"], cfg.EPS) @ w["toy.embed.weight"].double().T
+    logits = P.plain_rms_norm(h, w["toy.final_norm.weight"], cfg.EPS) @ w["toy.embed.weight"].double().T
+    return cfg.SOFTCAP * torch.tanh(logits * cfg.LOGIT_SCALE / cfg.SOFTCAP)
 
 
 @pytest.fixture
@@ -406,16 +413,62 @@ def test_toy_architecture_is_registered_built_and_stepped(toy_registered, dtype)
             else:
                 want[(rid, i)] = logits[i]
     assert close <= 0.1 * sum(len(t) for t in reqs.values())
-    for steps, what in ((H.whole(reqs), "toy whole"), (H.portions(reqs), "toy portions"),
-                        (H.prefill_then_decode(reqs, 32), "toy prefill + decode"),
-                        (H.mixed(reqs, seed=2), "toy mixed")):
-        pages = H.max_tokens_of(steps, 4) // 4
-        stepper = make_stepper(model, page_size=4, num_pages=pages, num_slots=4)
+    # the group of windowed layers has pages of its own size (2 tokens) in the last two runs
+    for steps, what, page1 in ((H.whole(reqs), "toy whole", 4), (H.portions(reqs), "toy portions", 4),
+                               (H.prefill_then_decode(reqs, 32), "toy prefill + decode", 2),
+                               (H.mixed(reqs, seed=2), "toy mixed", 2)):
+        pages = [H.max_tokens_of(steps, 4) // 4, H.max_tokens_of(steps, page1) // page1]
+        stepper = make_stepper(model, page_size=[4, page1], num_pages=pages, num_slots=4)
         assert stepper.storage.state_bytes_per_request() == 2 * cfg.H * 4
+        assert not stepper.cuda_graphs        # the toy parts do not say that they may be captured
         got = H.run_steps_in_process(stepper, steps)
         H.compare({k: v for k, v in got.items() if k in want}, want, dtype, what)
         mgr = stepper.manager
-        assert mgr.check() == 0 and mgr.free_pages(0) == pages and mgr.free_pages(1) == pages
+        assert mgr.check() == 0 and mgr.free_pages(0) == pages[0] and mgr.free_pages(1) == pages[1]
+
+
+def test_a_failed_step_leaves_state_and_lengths_as_they_were(toy_registered):
+    """Mixers update their per-request state in place; a forward pass that fails after they
+    did (here: the routed feed-forward of the last block raises) must leave the state, like
+    the lengths, where the step found them, so that the same step can be run again."""
+    import helpers as H
+    from mstar_b200.engine.model import load_model, model_param_specs
+    from mstar_b200.engine.step import StepEntry, make_stepper
+
+    cfg = ToyConfig()
+    g = torch.Generator().manual_seed(6)
+    tensors = {"toy." + name: ((torch.ones(spec.shape) if spec.init == "ones"
+                                else 0.05 * torch.randn(spec.shape, generator=g))).to(torch.bfloat16)
+               for name, spec in model_param_specs(cfg.layout()).items() if name != "head.weight"}
+    model = load_model(None, dtype="float32", device=DEV, config=cfg, tensors=tensors)
+    toks = {r: H.request_tokens(cfg.VOCAB, 12, seed=60 + i) for i, r in enumerate("ab")}
+
+    def run(fail_at_step):
+        stepper = make_stepper(model, page_size=4, num_pages=16, num_slots=2)
+        for r in toks:
+            stepper.add_request(r)
+        outs = []
+        for step, (lo, hi) in enumerate(((0, 5), (5, 6), (6, 12))):
+            entries = [StepEntry(r, toks[r][lo:hi], (hi - lo - 1,)) for r in toks]
+            if step == fail_at_step:
+                before = [s.clone() for s in stepper.storage.state if s is not None]
+                real = TopOneExperts.forward
+                TopOneExperts.forward = lambda *a, **k: (_ for _ in ()).throw(RuntimeError("boom"))
+                try:
+                    with pytest.raises(RuntimeError, match="boom"):
+                        stepper.step(entries)
+                finally:
+                    TopOneExperts.forward = real
+                after = [s for s in stepper.storage.state if s is not None]
+                assert len(before) == 2 and all(torch.equal(x, y) for x, y in zip(before, after))
+                assert [stepper.manager.length(r) for r in toks] == [lo, lo]
+            outs.append(stepper.step(entries).clone())
+        return outs
+
+    clean = run(None)
+    for fail_at in (0, 1, 2):
+        for x, y in zip(clean, run(fail_at)):
+            assert torch.equal(x, y)
 
 
 def test_llama_has_an_empty_state_slot(model_folders):

@@ -77,7 +77,9 @@ def test_dtype_rules(tmp_path):
     # one float32 shard of a fused parameter keeps the whole parameter in 32-bit
     tensors["model.layers.0.self_attn.k_proj.weight"] = tensors[
         "model.layers.0.self_attn.k_proj.weight"].float()
-    assert load(TINY_A, tensors, torch.bfloat16)["blocks.0.mixer.qkv.weight"].dtype == torch.float32
+    with pytest.warns(UserWarning, match="1 matrices .* stay float32 .*blocks.0.mixer.qkv.weight"):
+        kept = load(TINY_A, tensors, torch.bfloat16)
+    assert kept["blocks.0.mixer.qkv.weight"].dtype == torch.float32
 
 
 def test_one_error_lists_missing_unexpected_and_wrong_shapes(tmp_path):
