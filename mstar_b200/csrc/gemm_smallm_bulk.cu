@@ -21,7 +21,8 @@
 // bytes more than a chunk apart, which makes the 16-byte fragment reads free of bank
 // conflicts.  Eight consumer warps take the 32-element blocks of a chunk in turn, read their
 // fragments from shared memory (W rows as the 8-wide N of m16n8k16, the tokens as its M, k
-// assigned to threads as in gemm_smallm.cu) and x from global memory (it is small and stays
+// assigned to threads so that 16 consecutive bytes of a row are one thread's: permuted alike
+// in both operands) and x from global memory (it is small and stays
 // in L1/L2), and are summed through shared memory at the end of a strip.
 //
 // A third form is the attention mixer's first product for decoded tokens: y = x Wqkv^T with

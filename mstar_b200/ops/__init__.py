@@ -384,33 +384,18 @@ def _smallm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def smallm_kernel(m: int, gated: bool) -> str:
-    """"bulk" or "registers": which weight-streaming kernel takes a product of ``m`` rows.
-    The bulk-copy kernel (weights through a shared-memory ring filled by ``cp.async.bulk``)
-    is the faster one in every form; MSTAR_SMALLM=registers selects the other (weights
-    through registers), for measurements."""
-    return "registers" if os.environ.get("MSTAR_SMALLM") == "registers" else "bulk"
-
-
 def _gemm_smallm(x: torch.Tensor, w: torch.Tensor, out_dtype: torch.dtype, gated: bool,
                  static_weights: bool = False):
     m, k = x.shape
     n = w.shape[0]
     out = torch.empty((m, n // 2 if gated else n), dtype=out_dtype, device=x.device)
-    if smallm_kernel(m, gated) == "bulk":
-        code = lib.get("gemm_smallm_bulk").mstar_gemm_smallm_bulk_bf16(
-            x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), w.stride(0),
-            out.stride(0), int(gated), _dt(out), int(static_weights),
-            tcgen05_error_word(x.device).data_ptr(), _stream())
-        what = "gemm_smallm_bulk"
-    else:
-        code = lib.get("gemm_smallm").mstar_gemm_smallm_bf16(
-            x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), w.stride(0),
-            out.stride(0), int(gated), _dt(out), int(static_weights), _stream())
-        what = "gemm_smallm"
+    code = lib.get("gemm_smallm_bulk").mstar_gemm_smallm_bulk_bf16(
+        x.data_ptr(), w.data_ptr(), out.data_ptr(), m, n, k, x.stride(0), w.stride(0),
+        out.stride(0), int(gated), _dt(out), int(static_weights),
+        tcgen05_error_word(x.device).data_ptr(), _stream())
     if code == -1:
         raise KernelError(f"small-M GEMM refuses M={m}, N={n}, K={k}")
-    check(code, what)
+    check(code, "gemm_smallm_bulk")
     return out
 
 
@@ -465,15 +450,13 @@ def qkv_rope_write(x: torch.Tensor, w_qkv: torch.Tensor, positions, cache_pos, t
     """For few bfloat16 rows (decoded tokens): the product x Wqkv^T, the split-half rotary
     encoding of q and k over the whole head, and the write of k and v into their cache
     pages, as one kernel.  Returns q [M, num_heads * head_dim], rotated; or None when this
-    form does not apply (more than ``SMALL_M`` rows, another dtype, no cache to write,
-    MSTAR_SMALLM=registers or MSTAR_FUSED_ROPE=0), and the caller runs ``linear`` and
-    ``rope_kv_write`` instead."""
+    form does not apply (more than ``SMALL_M`` rows, another dtype, no cache to write, or
+    MSTAR_FUSED_ROPE=0), and the caller runs ``linear`` and ``rope_kv_write`` instead."""
     if (kv_cache is None or inv_freq is None or not _smallm_ok(x, w_qkv)
             or kv_cache.dtype != torch.bfloat16 or head_dim % 16
             or inv_freq.numel() != head_dim // 2
             or w_qkv.shape[0] != (num_heads + 2 * num_kv_heads) * head_dim
-            or os.environ.get("MSTAR_FUSED_ROPE") == "0"
-            or os.environ.get("MSTAR_SMALLM") == "registers"):
+            or os.environ.get("MSTAR_FUSED_ROPE") == "0"):
         return None
     _need_cuda(x, w_qkv, positions, cache_pos, token_req, block_table, inv_freq, kv_cache)
     assert kv_cache.is_contiguous() and inv_freq.dtype == torch.float32

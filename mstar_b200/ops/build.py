@@ -37,7 +37,6 @@ LIBRARIES = {
     "attention_prefill_tc": ("cuda", ["attention_prefill_tc.cu"], []),
     "attention_decode_noalloc": ("cuda", ["attention_decode_noalloc.cu"], []),
     "gemm_f32": ("cuda", ["gemm_f32.cu"], []),
-    "gemm_smallm": ("cuda", ["gemm_smallm.cu"], []),
     "gemm_smallm_bulk": ("cuda", ["gemm_smallm_bulk.cu"], []),
     "gemm_tcgen05": ("cuda", ["gemm_tcgen05.cu"], []),
     "gemm_skinny": ("cuda", ["gemm_skinny.cu"], []),

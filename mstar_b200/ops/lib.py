@@ -50,9 +50,6 @@ _SIGNATURES = {
     "gemm_f32": {
         "mstar_sgemm_nt": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],
     },
-    "gemm_smallm": {
-        "mstar_gemm_smallm_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp],
-    },
     "gemm_smallm_bulk": {
         "mstar_gemm_smallm_bulk_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _i, _i, _vp, _vp],
         "mstar_qkv_rope_write_bulk_bf16": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _vp, _vp, _vp, _i,

@@ -524,19 +524,16 @@ def test_repetition_penalty_and_seen_mask():
     assert seen[2, 9] == 1 and seen.sum() == 2      # the sampled token is marked
 
 
-@pytest.mark.parametrize("variant", ["bulk", "registers"])
 @pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("n,k", [(16, 32), (100, 96), (3000, 1024), (157, 3072), (33001, 64),
                                  (1030, 2080)])
-def test_small_m_gemm(m, n, k, variant, monkeypatch):
-    """The weight-streaming products of decode steps, both kernels (weights through a
-    shared-memory ring of bulk copies with strips of 8, 16 and 32 rows; weights through
-    registers): every M up to 16, N that is no multiple of the strip, K from one block of 32
-    up and K that is no multiple of the ring's chunk, both output types."""
+def test_small_m_gemm(m, n, k):
+    """The weight-streaming products of decode steps (weights through a shared-memory ring of
+    bulk copies with strips of 8, 16 and 32 rows): every M up to 16, N that is no multiple of
+    the strip, K from one block of 32 up and K that is no multiple of the ring's chunk, both
+    output types."""
     from mstar_b200 import ops
 
-    monkeypatch.setenv("MSTAR_SMALLM", variant)
-    assert ops.smallm_kernel(m, False) == variant
     x = rnd(m, k, dtype=torch.bfloat16, seed=m)
     w = rnd(n, k, dtype=torch.bfloat16, seed=n, scale=0.1)
     want = x.double() @ w.double().T
@@ -660,24 +657,16 @@ def test_small_m_gemm_refuses_more_rows():
     from mstar_b200 import ops
 
     x, w = rnd(17, 64, dtype=torch.bfloat16), rnd(32, 64, dtype=torch.bfloat16)
-    for variant in ("bulk", "registers"):
-        os.environ["MSTAR_SMALLM"] = variant
-        try:
-            with pytest.raises(ops.KernelError, match="refuses"):
-                ops._gemm_smallm(x, w, torch.bfloat16, gated=False)
-        finally:
-            del os.environ["MSTAR_SMALLM"]
-    assert ops.smallm_kernel(8, True) == "bulk" and ops.smallm_kernel(16, False) == "bulk"
+    with pytest.raises(ops.KernelError, match="refuses"):
+        ops._gemm_smallm(x, w, torch.bfloat16, gated=False)
     assert ops.linear(x, w).shape == (17, 32)             # the library product takes over
 
 
-@pytest.mark.parametrize("variant", ["bulk", "registers"])
 @pytest.mark.parametrize("inter,k", [(200, 96), (1500, 1120)])
 @pytest.mark.parametrize("m", [1, 8, 13, 16, 100])
-def test_gated_up_fused_and_unfused(m, inter, k, variant, monkeypatch):
+def test_gated_up_fused_and_unfused(m, inter, k):
     from mstar_b200 import ops
 
-    monkeypatch.setenv("MSTAR_SMALLM", variant)
     x = rnd(m, k, dtype=torch.bfloat16, seed=1)
     w = rnd(2 * inter, k, dtype=torch.bfloat16, seed=2, scale=0.2)
     got = ops.gated_up(x, w) if m > 16 else ops._gemm_smallm(x, w, torch.bfloat16, gated=True)

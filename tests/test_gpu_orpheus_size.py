@@ -158,12 +158,12 @@ def test_long_request_in_portions_then_decoded(long_request, dtype):
     torch.cuda.empty_cache()
 
 
-@pytest.mark.parametrize("switch", [("MSTAR_SMALLM", "registers"), ("MSTAR_FUSED_ROPE", "0"),
+@pytest.mark.parametrize("switch", [("MSTAR_FUSED_ROPE", "0"),
                                     ("MSTAR_DECODE_ATTENTION", "per_item")])
 def test_measurement_switches_at_these_sizes(big, switch, monkeypatch):
-    """The kernels a measurement switch selects instead of the default ones (register-load
-    small-M products, the first product and the rotary kernel apart, decode attention with
-    one CTA per item), on the mixed trace in bfloat16, within the same tolerances."""
+    """The kernels a measurement switch selects instead of the default ones (the first product
+    and the rotary kernel apart, decode attention with one CTA per item), on the mixed trace
+    in bfloat16, within the same tolerances."""
     from mstar_b200.engine.model import load_model
     from mstar_b200.engine.step import make_stepper
 
