@@ -237,7 +237,6 @@ def run(args) -> dict:
     finish(rids)
     e2e_ms = statistics.median(e2e_rounds)
 
-    flops = 0.0   # left to the reader: the line carries times, the ratio is the driver's
     return {
         "impl": "reference",
         "metric": f"decode tok/s at batch {batch} (Orpheus 3B bf16, 2,048-token cached prompts)",
@@ -275,7 +274,7 @@ def main() -> int:
     if not (REF / "mstar").is_dir():
         print(json.dumps({"impl": "reference", "unavailable":
                           "baseline/_ref holds no install of t-avil/mstar (pip install --no-index "
-                          "--no-deps --target baseline/_ref /root/reference)"}))
+                          "--no-deps --target baseline/_ref <the reference's source tree>)"}))
         return 0
     try:
         record = run(args)
