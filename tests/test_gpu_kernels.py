@@ -36,6 +36,22 @@ def test_embed_rows(table_dtype):
     assert torch.equal(out, table.float()[ids.long()])
 
 
+def test_embed_rows_scaled_and_logit_scale_softcap():
+    """The row multiplier of the embedding kernel and the scale / soft-cap kernel of the
+    head, at widths that are no powers of two."""
+    from mstar_b200 import ops
+
+    table = rnd(77, 200, dtype=torch.bfloat16, seed=1)
+    ids = torch.tensor([3, 76, 0, 3], dtype=torch.int32, device=DEV)
+    out = ops.embed_rows(table, ids, scale=11.5)
+    assert torch.equal(out, table[ids.long()].float() * 11.5)
+    x = rnd(5, 1001, seed=2, scale=20.0)
+    want = 30.0 * torch.tanh(x.double() * 0.25 / 30.0)
+    got = ops.scale_softcap(x.clone(), 0.25, 30.0)
+    assert (got.double() - want).abs().max() < 1e-5
+    assert torch.equal(ops.scale_softcap(x.clone(), 0.5, None), x * 0.5)
+
+
 @pytest.mark.parametrize("act", DTYPES)
 @pytest.mark.parametrize("wdtype", DTYPES)
 @pytest.mark.parametrize("hidden", [100, 3000])

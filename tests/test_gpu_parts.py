@@ -78,6 +78,42 @@ def test_gated_mlp_part(dtype):
                    {"gate_up.weight": gu, "down.weight": dn}, runtime(dtype))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding_and_head_parts(dtype):
+    """The two ends of the residual stream alone: a table with a row multiplier (tokens that
+    only the device holds included), and a linear head with a logit scale and a soft cap."""
+    from mstar_b200.config.layout import EmbeddingSpec, HeadSpec
+    from mstar_b200.parts import build_part
+
+    V, H = 150, 72
+    table = rnd(V, H, dtype=dtype, seed=1)
+    emb = build_part("embedding", EmbeddingSpec(vocab_size=V, hidden_size=H, multiplier=3.0),
+                     {"weight": table}, runtime(dtype))
+    assert emb.graph_safe is True
+    ids = torch.tensor([5, 149, 0, 7], dtype=torch.int32, device=DEV)
+    ctx = simple_ctx([4], [0])
+    h = emb.forward(ids, ctx)
+    assert h.dtype == torch.float32 and torch.equal(h, table[ids.long()].float() * 3.0)
+    # token 1 and 3 come from the device: their ids in `ids` are not to be used
+    ctx.token_source = (torch.tensor([-1, 1, -1, 0], dtype=torch.int32, device=DEV),
+                        torch.tensor([100, 33], dtype=torch.int32, device=DEV))
+    h2 = emb.forward(ids, ctx)
+    want_ids = torch.tensor([5, 33, 0, 100], device=DEV)
+    assert torch.equal(h2, table[want_ids].float() * 3.0)
+
+    w = rnd(V, H, dtype=dtype, seed=2, scale=0.3)
+    x = rnd(6, H, dtype=dtype, seed=3)
+    plain = (x.double() @ w.double().T).cpu()
+    tol = 1e-4 if dtype == torch.float32 else 2e-2
+    head = build_part("head", HeadSpec(vocab_size=V, hidden_size=H), {"weight": w}, runtime(dtype))
+    logits = head.forward(x)
+    assert logits.dtype == torch.float32 and (logits.double().cpu() - plain).abs().max() < tol
+    capped = build_part("head", HeadSpec(vocab_size=V, hidden_size=H, logit_scale=2.0, softcap=3.0),
+                        {"weight": w}, runtime(dtype))
+    want = 3.0 * torch.tanh(plain * 2.0 / 3.0)
+    assert (capped.forward(x).double().cpu() - want).abs().max() < tol
+
+
 def test_rope_part_holds_the_hand_computed_frequencies_on_the_device():
     """The position part's table, as the kernels read it (float on the device), against
     values worked out by hand from the llama3 rule (tests/test_plain.py; the rule itself is
