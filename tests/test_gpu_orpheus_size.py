@@ -44,6 +44,9 @@ TOLS = {"3b": {"float32": (1.3e-4, 1.3e-5), "bfloat16": (0.27, 0.027)},
         "8b": {"float32": (1.2e-4, 1.37e-5), "bfloat16": (0.305, 0.030)}}
 
 
+ROUNDED: dict = {}     # size -> (logits of the rounded plain model, tolerance against them)
+
+
 @pytest.fixture(scope="module", params=["3b", "1b", "8b"])
 def big(request):
     from mstar_b200.config.registry import config_from_dict
@@ -58,16 +61,25 @@ def big(request):
             tensors[key] = (tensors[key].float() * 2.0).to(torch.bfloat16)
     reqs = {f"o{i}": H.request_tokens(CFG["vocab_size"], n, seed=70 + i)
             for i, n in enumerate(LENGTHS)}
-    cpu = {k: v.cpu() for k, v in tensors.items()}
-    want = {}
-    head = cpu["model.embed_tokens.weight" if CFG["tie_word_embeddings"]
-               else "lm_head.weight"].double()
+    # the plain model's float64 products run where the weights are, on the GPU.  Beside the
+    # float64 logits, the second bfloat16 oracle (activations rounded where the engine
+    # stores bfloat16) and the yardstick for what remains between it and a bfloat16 kernel
+    # (tests/helpers.py kernel_rounding_yardstick, here on the compared rows only)
+    want, rounded, rounded32 = {}, {}, {}
+    head = tensors["model.embed_tokens.weight" if CFG["tie_word_embeddings"]
+                   else "lm_head.weight"].double()
     for rid, toks in reqs.items():
-        hidden = P.plain_hidden_states(cpu, CFG, toks)
         rows = sorted({0, 1, 15, 16, 17, len(toks) // 2, len(toks) - 2, len(toks) - 1})
-        logits = hidden[rows] @ head.T
-        want.update({(rid, r): logits[i] for i, r in enumerate(rows)})
+        logits = (P.plain_hidden_states(tensors, CFG, toks)[rows] @ head.T).cpu()
+        bf = (P.plain_hidden_states(tensors, CFG, toks, act=P.round_bf16)[rows] @ head.T).cpu()
+        bf32 = (H.in_float32(lambda: P.plain_hidden_states(
+            tensors, CFG, toks, act=P.round_bf16, round_probs=P.round_bf16))[rows].double()
+            @ head.T).cpu()
+        for i, r in enumerate(rows):
+            want[(rid, r)], rounded[(rid, r)], rounded32[(rid, r)] = logits[i], bf[i], bf32[i]
     del head
+    pushes = H.spread(rounded32, rounded)
+    ROUNDED[size] = (rounded, (2 * pushes[0], 2 * pushes[1]))
     return size, cfg, tensors, reqs, want
 
 
@@ -100,6 +112,11 @@ def test_orpheus_sized_layers_match_the_plain_model(big, dtype):
         assert set(got) == set(want)
         worst = H.compare(got, want, dtype, what, tol=tol, mean_tol=mean_tol)
         print(f"{what} [{dtype}]: worst abs error {worst:.3e}")
+        if dtype == "bfloat16":
+            rounded, (rtol, rmean) = ROUNDED[size]
+            worst = H.compare(got, rounded, dtype, what + ", against the rounded plain model",
+                              tol=rtol, mean_tol=rmean)
+            print(f"{what} [rounded plain model]: worst abs error {worst:.3e} of {rtol:.3e}")
     del model
     torch.cuda.empty_cache()
 
