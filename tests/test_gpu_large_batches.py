@@ -155,12 +155,18 @@ def big():
     return cfg, tensors, reqs, prompt_len, want, rounded, keep, (2 * pushes[0], 2 * pushes[1])
 
 
-@pytest.mark.parametrize("page,live", [(16, 20), (64, 20), (16, 40)])
+@pytest.mark.parametrize("page,live,skinny", [(16, 20, None), (64, 20, None), (16, 40, None),
+                                              (16, 20, "1")])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_many_requests_at_the_benchmark_sizes(big, dtype, page, live):
+def test_many_requests_at_the_benchmark_sizes(big, dtype, page, live, skinny, monkeypatch):
     """The kernels serving runs (tcgen05 prefill attention, the TMA ring decode attention, the
     products for 17 to 40 rows, the swapped-operand LM head, captured graphs of 32 and 64) on
-    pages that earlier requests have held."""
+    pages that earlier requests have held.  ``skinny``: MSTAR_SKINNY=1, the swapped-operand
+    kernel for every projection of 17 to 128 rows instead of the library's."""
+    if skinny is not None:
+        if dtype == "float32":
+            pytest.skip("the switch concerns the bfloat16 products")
+        monkeypatch.setenv("MSTAR_SKINNY", skinny)
     from mstar_b200.engine.model import load_model
     from mstar_b200.engine.step import make_stepper
 

@@ -175,7 +175,7 @@ def test_long_request_in_portions_then_decoded(long_request, dtype):
     torch.cuda.empty_cache()
 
 
-@pytest.mark.parametrize("switch", [("MSTAR_FUSED_ROPE", "0"),
+@pytest.mark.parametrize("switch", [("MSTAR_FUSED_ROPE", "0"), ("MSTAR_SKINNY", "1"),
                                     ("MSTAR_DECODE_ATTENTION", "per_item")])
 def test_measurement_switches_at_these_sizes(big, switch, monkeypatch):
     """The kernels a measurement switch selects instead of the default ones (the first product

@@ -190,7 +190,7 @@ def test_decode_steps_replay_cuda_graphs_with_the_same_logits(model_folders, dty
             assert (row - outs[True][key]).abs().max().item() <= tol, key
 
 
-@pytest.mark.parametrize("switch", [("MSTAR_FUSED_ROPE", "0"),
+@pytest.mark.parametrize("switch", [("MSTAR_FUSED_ROPE", "0"), ("MSTAR_SKINNY", "1"),
                                     ("MSTAR_DECODE_ATTENTION", "per_item")])
 @pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
 def test_other_kernels_of_a_measurement_switch_give_the_same_model(model_folders, name, switch,
