@@ -3,9 +3,13 @@
 // the group) pairs, causal end-aligned mask, float softmax); what differs is where the
 // work runs.
 //
-// One CTA owns 128 rows and one kv head; the CTAs with the most keys are launched first.
+// One CTA owns the rows of 128 / G whole tokens (G query heads per kv head: 128 rows, or
+// 126 where G is 3) and one kv head; the CTAs with the most keys are launched first.  Its
+// query rows come by one TMA copy per 64 features: a box of [tokens x G heads x 64] from the
+// projection's output lands as the K-major swizzled tile that the MMA reads (loads and
+// stores by the softmax threads took 5 to 9 us per CTA before the first product could start).
 // Per tile of 64 keys:
-//   * the producer warp brings the keys and the values by TMA (one box of [page_size x 64]
+//   * two producer warps bring the keys and the values by TMA (one box of [page_size x 64]
 //     per page and 64-feature half, 128-byte swizzle, issued side by side from several
 //     lanes) into two rings of two stages;
 //   * a lane of the S warp issues S = Q K^T as tcgen05.mma (M 128, N 64, K 16 per step) into
@@ -23,6 +27,14 @@
 // S 64, P 2 x 32, O 128), so one CTA's softmax overlaps the other's MMAs; at 64 there is
 // room for more, at 256 (193 KB, 512 columns) for one.
 //
+// With one prompt alone the CTAs are few (a few hundred, of 1 to 32 key tiles) and the
+// longest sets the time.  Sharing the long row tiles between two CTAs was built twice and is
+// not kept: as a cluster of two with the second CTA's part read through distributed shared
+// memory (63 us instead of 42 for 2,048 tokens: launched as clusters the CTAs no longer
+// overlapped on the SMs), and as independent CTAs that leave their parts in scratch memory,
+// the one that comes second adding them up (46 to 56 us against 38: a CTA's start and end
+// cost as much as four key tiles, writing and reading a part as much as seven).
+//
 // Shared-memory descriptors: Q and K are K-major with the 128-byte swizzle (8-row groups
 // 1024 bytes apart); V is MN-major (features contiguous): 8-key groups 1024 bytes apart
 // (stride byte offset), the 64-feature blocks 8192 bytes apart (leading byte offset).
@@ -36,15 +48,14 @@
 
 #define PT_ROWS 128
 #define PT_KEYS 64
-#define PT_THREADS 224  // 4 softmax warps, the S-issuing warp, the TMA warp, the O-issuing warp
+#define PT_THREADS 256  // 4 softmax warps, the S-issuing warp, the key warp, the O-issuing warp, the value warp
 
 struct PrefillTcArgs {
-    const bf16* q;
     const int* block_table;
     const int* qo_indptr;
     const int* kv_len;
     bf16* out;
-    int q_stride, bt_stride, nq, nkv, page_size, first_entry;
+    int bt_stride, nq, nkv, page_size, first_entry;
     float scale_log2e;
 };
 
@@ -100,8 +111,22 @@ __device__ __forceinline__ void pt_st32(uint32_t taddr, const uint32_t (&r)[32])
 }
 __device__ __forceinline__ void pt_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void pt_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// A wait of a whole warp whose outcome all its lanes share: the tcgen05.ld / st that follow
+// are warp-wide instructions and must not be reached by a part of the warp only.
+__device__ __forceinline__ bool pt_wait_warp(uint32_t bar, uint32_t parity) {
+    return __all_sync(0xffffffffu, mbar_wait(bar, parity)) != 0;
+}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void pt_tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
+                                               int c1, int c2, int c3) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, "
+        "%4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+        : "memory");
 }
 
 // descriptor bits common to all operands here: version 1 [46,48), SWIZZLE_128B [61,64)
@@ -139,7 +164,8 @@ __device__ __forceinline__ float pt_ex2(float x) {
 
 template <int HD>
 __global__ void __launch_bounds__(PT_THREADS)
-prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillTcArgs a,
+prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map,
+                            const __grid_constant__ CUtensorMap q_map, PrefillTcArgs a,
                             int* __restrict__ error_word) {
     constexpr int PT_Q_BYTES = pt_q_bytes(HD), PT_KV_TILE = pt_kv_tile(HD);
     constexpr int NB = HD / 64;                     // 64-feature blocks of a row
@@ -161,21 +187,21 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillT
 
     // grid: x the kv head, y the row tile with the longest first (the tiles with the most keys
     // are launched before the short ones), z the entry
-    const int tile = gridDim.y - 1 - blockIdx.y, kvh = blockIdx.x, e = a.first_entry + blockIdx.z;
+    const int tile = gridDim.y - 1 - blockIdx.y, e = a.first_entry + blockIdx.z;
+    const int kvh = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = a.nq / a.nkv;
+    const int TPT = PT_ROWS / G, RPT = TPT * G;      // tokens and rows of a tile
     const int q_start = a.qo_indptr[e];
     const int q_len = a.qo_indptr[e + 1] - q_start;
-    const int rows_total = q_len * G;
-    const int row0 = tile * PT_ROWS;
-    if (row0 >= rows_total) return;
+    const int tok0 = tile * TPT;
+    if (tok0 >= q_len) return;
     if ((tc_smem(smem_dyn) & 1023u) != 0) {         // the swizzled tiles need this alignment
         if (tid == 0) atomicExch(error_word, 6);
         return;
     }
     const int past = a.kv_len[e] - q_len;
-    const int last_row = min(rows_total, row0 + PT_ROWS) - 1;
-    const int hi = past + last_row / G + 1;       // keys 0 .. hi-1 are visible to some row
+    const int hi = past + min(q_len, tok0 + TPT);   // keys 0 .. hi-1 are visible to some row
     const int ntiles = (hi + PT_KEYS - 1) / PT_KEYS;
     const int* bt = a.block_table + (size_t)e * a.bt_stride;
     const int ps = a.page_size;
@@ -183,8 +209,15 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillT
     const uint32_t q_ready = tc_smem(bars + 12);
     if (tid == 0) {
         for (int i = 0; i < 13; ++i)
-            mbar_init(tc_smem(bars + i), i == 8 || i == 9 || i == 11 || i == 12 ? 128 : 1);
+            mbar_init(tc_smem(bars + i), i == 8 || i == 9 || i == 11 ? 128 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (tid >= RPT && tid < PT_ROWS) {
+        // rows of the tile that the copy of the query rows leaves out (128 is no multiple of G)
+        for (int c = 0; c < HD / 8; ++c)
+            *reinterpret_cast<uint4*>(q_s + (c >> 3) * (PT_ROWS * 128) + tid * 128 + (c & 7) * 16) =
+                make_uint4(0u, 0u, 0u, 0u);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 4) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
@@ -201,54 +234,62 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillT
     const uint32_t tmem_p = tmem + 64;    // P: two buffers of 32 columns (64 packed keys each)
     const uint32_t tmem_o = tmem + 128;   // O: head_dim columns from 128 on
 
-    if (warp == 5) {
-        // ------------------------------------------------------------- TMA producer
-        // The whole warp runs the loop: its lanes fetch 32 block-table entries at a time
-        // (one dependent global load per page would cost more than the copies), lane 0
-        // waits for the stages and issues the copies.
-        const int last_page = (hi - 1) / ps;
+    if (warp == 5 || warp == 7) {
+        // ------------------------------------------- TMA producers: warp 5 the keys, 7 the values
+        // All lanes run the loop: they fetch 32 block-table entries at a time (one dependent
+        // global load per page would cost more than the copies); lane NB p + h waits for the
+        // stage and copies block h of page p (at most 8 pages x 4 blocks), side by side with
+        // the others.  Keys and values have a warp each and the loop is kept short (page
+        // sizes are powers of two: shifts; no exchange between the lanes but the page
+        // numbers): one warp doing both, with divisions, took 1,850 cycles per tile, which
+        // was the whole kernel's pace.
+        const int which = warp == 7;
+        const int ps_log = 31 - __clz(ps);
+        const int last_page = (hi - 1) >> ps_log;
         // a tile is 1, 2, 4 or 8 whole pages, or, with pages of 128 or 256 keys, a part of one
-        const int per_tile = ps < PT_KEYS ? PT_KEYS / ps : 1;
+        const int per_tile = ps < PT_KEYS ? PT_KEYS >> ps_log : 1;
         const int box_rows = ps < PT_KEYS ? ps : PT_KEYS;
+        const int p = lane / NB, h = lane % NB;
+        const bool issues = p < per_tile;
+        const uint32_t full0 = which ? v_full : k_full, empty0 = which ? v_empty : k_empty;
+        const uint32_t dst0 = tc_smem(which ? v_s : k_s) + (uint32_t)(h * (PT_KEYS * 128) + p * box_rows * 128);
+        // row of the cache seen as a matrix: ((page * 2 + which) * nkv + kvh) * ps + key in page
+        const int page_rows = 2 * a.nkv * ps, row0 = (which * a.nkv + kvh) * ps;
+        if (which == 0 && lane == 0) {
+            // the query rows: tokens tok0 .. tok0+TPT-1 (past the last row of the batch: zeros)
+            mbar_expect_tx(q_ready, (uint32_t)(NB * RPT * 128));
+            for (int hh = 0; hh < NB; ++hh)
+                pt_tma_load_4d(tc_smem(q_s + hh * (PT_ROWS * 128)), &q_map, q_ready, hh * 64, 0, kvh,
+                               q_start + tok0);
+        }
         int mine = 0, have_from = -1;                 // lanes hold pages have_from .. +31
         bool ok = true;
         for (int j = 0; j < ntiles; ++j) {
             const int s = j & 1;
             const uint32_t free_parity = (((uint32_t)j >> 1) & 1u) ^ 1u;
-            const int base_page = j * PT_KEYS / ps;
-            const int in_page = j * PT_KEYS % ps;     // 0 unless the page is larger than the tile
+            const int key0 = j * PT_KEYS;
+            const int base_page = key0 >> ps_log;
+            const int in_page = key0 & (ps - 1);      // 0 unless the page is larger than the tile
             if (have_from < 0 || base_page + per_tile > have_from + 32) {
                 have_from = base_page;
                 // pages beyond the last are replaced by the last: masked rows stay finite
                 mine = bt[min(base_page + lane, last_page)];
             }
-            // keys, as soon as S of tile j-2 is done
-            if (lane == 0 && !mbar_wait(k_empty + 8 * s, free_parity)) {
-                atomicExch(error_word, 7);
-                ok = false;
-            }
-            if (!__shfl_sync(0xffffffffu, (int)ok, 0)) break;
-            // lane NB p + h copies block h of page p (at most 8 pages x 4 blocks): the copies
-            // are issued side by side
-            const int p = lane / NB, h = lane % NB;
             const int page = __shfl_sync(0xffffffffu, mine, (base_page + p - have_from) & 31);
-            const uint32_t dst_off = (uint32_t)(s * PT_KV_TILE + h * (PT_KEYS * 128) + p * box_rows * 128);
-            if (lane == 0) mbar_expect_tx(k_full + 8 * s, PT_KV_TILE);
-            __syncwarp();
-            if (p < per_tile)
-                tma_load_2d(tc_smem(k_s + dst_off), &kv_map, k_full + 8 * s, h * 64,
-                            ((page * 2) * a.nkv + kvh) * ps + in_page);
-            // values, once O += P V of tile j-2 is done
-            if (lane == 0 && !mbar_wait(v_empty + 8 * s, free_parity)) {
-                atomicExch(error_word, 7);
-                ok = false;
+            if (issues) {
+                // the stage is free once S (keys) or O += P V (values) of tile j-2 is done
+                if (!mbar_wait(empty0 + 8 * s, free_parity)) {
+                    atomicExch(error_word, 7);
+                    ok = false;
+                } else {
+                    // the bytes may land before lane 0 has announced them: the phase cannot
+                    // end before its one arrival
+                    if (lane == 0) mbar_expect_tx(full0 + 8 * s, PT_KV_TILE);
+                    tma_load_2d(dst0 + (uint32_t)(s * PT_KV_TILE), &kv_map, full0 + 8 * s, h * 64,
+                                page * page_rows + row0 + in_page);
+                }
             }
-            if (!__shfl_sync(0xffffffffu, (int)ok, 0)) break;
-            if (lane == 0) mbar_expect_tx(v_full + 8 * s, PT_KV_TILE);
-            __syncwarp();
-            if (p < per_tile)
-                tma_load_2d(tc_smem(v_s + dst_off), &kv_map, v_full + 8 * s, h * 64,
-                            ((page * 2 + 1) * a.nkv + kvh) * ps + in_page);
+            if (!__all_sync(0xffffffffu, ok)) break;
         }
     } else if (warp == 4) {
         // ------------------------------------------------ S = Q K^T, while the softmax works on
@@ -316,45 +357,17 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillT
         }
     } else if (warp < 4) {
         // ------------------------------------------------------ softmax, one row per thread
-        // the 128 query rows -> shared, K-major with the 128-byte swizzle: chunks of 16
-        // bytes, 8 loads per thread in flight before their stores
-        {
-            constexpr int CPR = HD / 8;                 // chunks per row
-#pragma unroll
-            for (int k0 = 0; k0 < CPR; k0 += 8) {
-                uint4 v[8];
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const int i = tid + 128 * (k0 + k), qr = i / CPR, c = i % CPR;
-                    const int qrow = row0 + qr;
-                    v[k] = make_uint4(0u, 0u, 0u, 0u);
-                    if (qrow < rows_total) {
-                        const int tok = q_start + qrow / G, head = kvh * G + qrow % G;
-                        v[k] = *reinterpret_cast<const uint4*>(a.q + (size_t)tok * a.q_stride +
-                                                               (size_t)head * HD + c * 8);
-                    }
-                }
-#pragma unroll
-                for (int k = 0; k < 8; ++k) {
-                    const int i = tid + 128 * (k0 + k), qr = i / CPR, c = i % CPR;
-                    const uint32_t off = (uint32_t)(c >> 3) * (PT_ROWS * 128) + (uint32_t)qr * 128 +
-                                         (uint32_t)(((c & 7) ^ (qr & 7)) << 4);
-                    *reinterpret_cast<uint4*>(q_s + off) = v[k];
-                }
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_arrive(q_ready);
-        }
         const int r = tid;                              // row of the tile = TMEM lane
-        const int row = row0 + r;
-        const int cp = past + min(row, rows_total - 1) / G;   // newest key this row sees
-        const int cp_min = past + row0 / G;                   // ... and any row of this CTA
+        const int tok = tok0 + min(r, RPT - 1) / G;
+        const bool valid = r < RPT && tok < q_len;
+        const int cp = past + min(tok, q_len - 1);      // newest key this row sees
+        const int cp_min = past + tok0;                 // ... and any row of this CTA
         const uint32_t lane_off = (uint32_t)(warp * 32) << 16;
         const float scale = a.scale_log2e;
         float m = -INFINITY, l = 0.f;     // m: the reference maximum, in scaled (log2) units
         bool ok = true;
         for (int j = 0; j < ntiles; ++j) {
-            if (!mbar_wait(s_full, (uint32_t)j & 1u)) {
+            if (!pt_wait_warp(s_full, (uint32_t)j & 1u)) {
                 if (lane == 0) atomicExch(error_word, 10);
                 ok = false;
                 break;
@@ -404,7 +417,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillT
             l = l * alpha + (sum0 + sum1);
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
                 // O += P V of tile j-1 must be done before O is rescaled
-                if (!mbar_wait(v_empty + 8 * ((j - 1) & 1), ((uint32_t)(j - 1) >> 1) & 1u)) {
+                if (!pt_wait_warp(v_empty + 8 * ((j - 1) & 1), ((uint32_t)(j - 1) >> 1) & 1u)) {
                     if (lane == 0) atomicExch(error_word, 11);
                     ok = false;
                     break;
@@ -421,7 +434,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillT
                 }
             }
             // P of tile j-2 lies in this tile's buffer until O += P V of that tile is done
-            if (j >= 2 && !mbar_wait(v_empty + 8 * (j & 1), ((uint32_t)(j - 2) >> 1) & 1u)) {
+            if (j >= 2 && !pt_wait_warp(v_empty + 8 * (j & 1), ((uint32_t)(j - 2) >> 1) & 1u)) {
                 if (lane == 0) atomicExch(error_word, 11);
                 ok = false;
                 break;
@@ -432,19 +445,17 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillT
             pt_fence_before();
             mbar_arrive(p_ready + 8 * (j & 1));
         }
-        if (ok && !mbar_wait(v_empty + 8 * ((ntiles - 1) & 1), ((uint32_t)(ntiles - 1) >> 1) & 1u)) {
+        if (ok && !pt_wait_warp(v_empty + 8 * ((ntiles - 1) & 1), ((uint32_t)(ntiles - 1) >> 1) & 1u)) {
             if (lane == 0) atomicExch(error_word, 12);
             ok = false;
         }
         pt_fence_after();
+        // ---------------------------------------------------------------- epilogue
+        // (`ok` is the same in all lanes of a warp; rows past the entry's last token are read
+        // with the others, the load being a warp's, and not stored)
         if (ok) {
             const float inv = 1.f / l;
-            const bool valid = row < rows_total;
-            bf16* dst = nullptr;
-            if (valid) {
-                const int tok = q_start + row / G, head = kvh * G + row % G;
-                dst = a.out + (size_t)tok * a.nq * HD + (size_t)head * HD;
-            }
+            bf16* dst = a.out + (size_t)(q_start + tok) * a.nq * HD + (size_t)(kvh * G + r % G) * HD;
 #pragma unroll 1
             for (int c0 = 0; c0 < HD; c0 += 32) {
                 uint32_t o[32];
@@ -472,29 +483,32 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, PrefillT
 }
 
 template <int HD>
-static int launch_prefill_tc(const CUtensorMap& map, const PrefillTcArgs& a, dim3 grid, int* error_word,
-                             cudaStream_t stream) {
+static int launch_prefill_tc(const CUtensorMap& map, const CUtensorMap& q_map, const PrefillTcArgs& a,
+                             dim3 grid, int* error_word, cudaStream_t stream) {
+    auto kernel = prefill_attention_tc_kernel<HD>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(prefill_attention_tc_kernel<HD>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, pt_smem_launch(HD));
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             pt_smem_launch(HD));
         if (e != cudaSuccess) return (int)e;
         // several CTAs per SM need nearly all of the SM's shared memory
-        e = cudaFuncSetAttribute(prefill_attention_tc_kernel<HD>, cudaFuncAttributePreferredSharedMemoryCarveout,
+        e = cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
                                  (int)cudaSharedmemCarveoutMaxShared);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    prefill_attention_tc_kernel<HD><<<grid, PT_THREADS, pt_smem_launch(HD), stream>>>(map, a, error_word);
+    kernel<<<grid, PT_THREADS, pt_smem_launch(HD), stream>>>(map, q_map, a, error_word);
     return launch_status();
 }
 
 // Entries [first_entry, first_entry + entries) of the batch.  head_dim must be 64, 128 or
-// 256, the page size 8..64 dividing 64, or 128 or 256, no window.  `kv_map`: the cache's tensor map.
+// 256, the page size 8..64 dividing 64, or 128 or 256, no window, at most 128 query heads per
+// kv head.  `kv_map`: the cache's tensor map.  `q`: `q_rows` rows of `q_stride` elements, of
+// which the first nq * hd are the query heads; 16-byte aligned, the stride a multiple of 8.
 // Returns 0, a CUDA error code or -1 (shape refused).  `error_word` receives 6..12 if a wait
 // ran out (6: the shared memory was not aligned as the swizzle needs).
 MSTAR_API int mstar_paged_prefill_attention_tc(
-    const void* kv_map, const void* q, int q_stride, void* out, const int* block_table, int bt_stride,
+    const void* kv_map, const void* q, int q_stride, int q_rows, void* out, const int* block_table, int bt_stride,
     const int* qo_indptr, const int* kv_len, int first_entry, int entries, int max_q_len, int nq,
     int nkv, int hd, int page_size, float scale, int* error_word, void* stream) {
     if (entries <= 0 || max_q_len <= 0) return 0;
@@ -505,13 +519,31 @@ MSTAR_API int mstar_paged_prefill_attention_tc(
           page_size == 256))
         return -1;
     if (entries > 65535) return -1;
+    const int G = nq / nkv;
+    if (G > PT_ROWS || q == nullptr || q_rows <= 0 || ((uintptr_t)q & 15) != 0 || q_stride % 8 != 0 ||
+        q_stride < nq * hd)
+        return -1;
+    const int per_tile = PT_ROWS / G;                     // tokens of a row tile
+    // the query rows as [token][kv head][head of the group][feature]; a box is a tile's rows
+    // for one kv head and 64 features
+    CUtensorMap q_map;
+    {
+        EncodeTiledFn encode = encode_tiled_fn();
+        if (encode == nullptr) return (int)cudaErrorNotSupported;
+        const cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)G, (cuuint64_t)nkv, (cuuint64_t)q_rows};
+        const cuuint64_t strides[3] = {(cuuint64_t)hd * 2, (cuuint64_t)G * hd * 2, (cuuint64_t)q_stride * 2};
+        const cuuint32_t box[4] = {64, (cuuint32_t)G, 1, (cuuint32_t)per_tile};
+        const cuuint32_t elem[4] = {1, 1, 1, 1};
+        if (encode(&q_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(q), dims, strides, box,
+                   elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return -1;
+    }
     PrefillTcArgs a;
-    a.q = (const bf16*)q;
     a.block_table = block_table;
     a.qo_indptr = qo_indptr;
     a.kv_len = kv_len;
     a.out = (bf16*)out;
-    a.q_stride = q_stride;
     a.bt_stride = bt_stride;
     a.nq = nq;
     a.nkv = nkv;
@@ -520,13 +552,13 @@ MSTAR_API int mstar_paged_prefill_attention_tc(
     a.scale_log2e = scale * 1.4426950408889634f;
     CUtensorMap map;
     memcpy(&map, kv_map, sizeof(map));
-    const int G = nq / nkv;
-    const long long tiles = ((long long)max_q_len * G + PT_ROWS - 1) / PT_ROWS;
+    const long long tiles = ((long long)max_q_len + per_tile - 1) / per_tile;
     if (tiles > 65535) return -1;
     dim3 grid(nkv, (unsigned)tiles, entries);
+    cudaStream_t s = (cudaStream_t)stream;
     switch (hd) {
-        case 64: return launch_prefill_tc<64>(map, a, grid, error_word, (cudaStream_t)stream);
-        case 128: return launch_prefill_tc<128>(map, a, grid, error_word, (cudaStream_t)stream);
-        default: return launch_prefill_tc<256>(map, a, grid, error_word, (cudaStream_t)stream);
+        case 64: return launch_prefill_tc<64>(map, q_map, a, grid, error_word, s);
+        case 128: return launch_prefill_tc<128>(map, q_map, a, grid, error_word, s);
+        default: return launch_prefill_tc<256>(map, q_map, a, grid, error_word, s);
     }
 }

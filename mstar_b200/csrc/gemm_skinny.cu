@@ -151,7 +151,8 @@ gemm_skinny_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         // `out` may be memory that the kernel before still reads: nothing is written before
         // that kernel has ended
         pdl_wait();
-        if (ready && !*(volatile int*)&abort_flag) {
+        // one outcome for the warp: the loads from tensor memory below are warp-wide
+        if (__all_sync(0xffffffffu, ready && !*(volatile int*)&abort_flag)) {
             const int n = n0 + quarter * 32 + lane;
 #pragma unroll 1
             for (int c0 = 0; c0 < TOK; c0 += 32) {

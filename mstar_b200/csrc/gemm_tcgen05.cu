@@ -164,7 +164,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             abort_flag = 1;
         }
         tc_fence_after_sync();
-        if (ready && !*(volatile int*)&abort_flag) {
+        // one outcome for the warp: the loads from tensor memory below are warp-wide
+        if (__all_sync(0xffffffffu, ready && !*(volatile int*)&abort_flag)) {
             const int row = m0 + quarter * 32 + lane;
             const bool vec_ok = (ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
 #pragma unroll 1
@@ -341,7 +342,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
             abort_flag = 1;
         }
         tc_fence_after_sync();
-        if (ready && !*(volatile int*)&abort_flag) {
+        // one outcome for the warp: the loads from tensor memory below are warp-wide
+        if (__all_sync(0xffffffffu, ready && !*(volatile int*)&abort_flag)) {
             const int row = m0 + quarter * 32 + lane;
             const bool vec_ok = (ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(out) & 15) == 0);
 #pragma unroll 1
@@ -539,7 +541,8 @@ gemm_tcgen05_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
         for (int t = pair; t < tiles_total; t += num_pairs, ++j) {
             const int b = j & 1;
             const bool ready = mbar_wait(tc_smem(&acc_full[b]), ((uint32_t)j >> 1) & 1u);
-            if (!ready || *(volatile int*)&abort_flag) {
+            // one outcome for the warp: the loads from tensor memory below are warp-wide
+            if (!__all_sync(0xffffffffu, ready && !*(volatile int*)&abort_flag)) {
                 if (!ready && lane == 0) {
                     atomicExch(error_word, 3);
                     abort_flag = 1;

@@ -10,7 +10,9 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#ifndef TC_SPIN_LIMIT
 #define TC_SPIN_LIMIT (1u << 24)
+#endif
 
 __device__ __forceinline__ uint32_t tc_smem(const void* p) {
     return (uint32_t)__cvta_generic_to_shared(p);

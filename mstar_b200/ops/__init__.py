@@ -312,13 +312,15 @@ def paged_decode_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, kv
         lib.add_launches(1)                     # the merge kernel
 
 
-def prefill_attention_kernel(has_kv_map: bool, head_dim: int, page_size: int) -> str:
+def prefill_attention_kernel(has_kv_map: bool, head_dim: int, page_size: int, group: int = 1) -> str:
     """"tcgen05" or "mma": which prefill attention kernel runs.  The tcgen05 kernel takes
-    head_dim 64, 128 or 256, no window and the page sizes of ``TMA_PAGE_SIZES``, and is the
-    faster one from the shortest portions on; MSTAR_PREFILL_ATTENTION=mma selects the other."""
+    head_dim 64, 128 or 256, no window, the page sizes of ``TMA_PAGE_SIZES`` and up to 128
+    query heads per kv head (``group``), and is the faster one from the shortest portions on;
+    MSTAR_PREFILL_ATTENTION=mma selects the other."""
     import os
 
-    takes = has_kv_map and head_dim in (64, 128, 256) and page_size in TMA_PAGE_SIZES
+    takes = (has_kv_map and head_dim in (64, 128, 256) and page_size in TMA_PAGE_SIZES
+             and group <= 128)
     if not takes or os.environ.get("MSTAR_PREFILL_ATTENTION") == "mma":
         return "mma"
     return "tcgen05"
@@ -334,9 +336,10 @@ def paged_prefill_attention(q: torch.Tensor, q_stride: int, out: torch.Tensor, k
     assert q.dtype == torch.bfloat16 and kv_cache.dtype == torch.bfloat16
     assert (q_stride * 2) % 16 == 0 and q.data_ptr() % 16 == 0 and out.is_contiguous()
     kv_map = kv_tensor_map(kv_cache) if not window else None
-    if prefill_attention_kernel(kv_map is not None, head_dim, page_size) == "tcgen05":
+    if prefill_attention_kernel(kv_map is not None, head_dim, page_size,
+                                num_heads // num_kv_heads) == "tcgen05":
         code = lib.get("attention_prefill_tc").mstar_paged_prefill_attention_tc(
-            kv_map, q.data_ptr(), q_stride, out.data_ptr(), block_table.data_ptr(),
+            kv_map, q.data_ptr(), q_stride, q.shape[0], out.data_ptr(), block_table.data_ptr(),
             block_table.stride(0), qo_indptr.data_ptr(), kv_len.data_ptr(), first_entry, entries,
             max_q_len, num_heads, num_kv_heads, head_dim, page_size, float(scale),
             tcgen05_error_word(q.device).data_ptr(), _stream())

@@ -44,8 +44,8 @@ _SIGNATURES = {
                                                _i, _i, _i, _i, _i, _i, _f, _vp, _vp],
     },
     "attention_prefill_tc": {
-        "mstar_paged_prefill_attention_tc": [_vp, _vp, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i, _i,
-                                             _i, _i, _i, _f, _vp, _vp],
+        "mstar_paged_prefill_attention_tc": [_vp, _vp, _i, _i, _vp, _vp, _i, _vp, _vp, _i, _i, _i,
+                                             _i, _i, _i, _i, _f, _vp, _vp],
     },
     "gemm_f32": {
         "mstar_sgemm_nt": [_vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _vp],

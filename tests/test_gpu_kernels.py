@@ -320,6 +320,32 @@ def test_prefill_attention_both_kernels(which, nq, nkv, page, hd, monkeypatch):
     assert tc_clean() == 0
 
 
+@pytest.mark.parametrize("nq,nkv,page,hd", [(24, 8, 16, 128), (5, 1, 8, 128), (14, 2, 64, 64),
+                                            (4, 2, 16, 256), (4, 4, 32, 128)])
+def test_prefill_attention_tcgen05_row_tiles(nq, nkv, page, hd, monkeypatch):
+    """The tcgen05 kernel's row tiles are whole tokens (128 // G of them, G query heads per kv
+    head: 126 rows at G 3, 125 at 5, 126 at 7) fetched by one TMA box per 64 features: prompts
+    and portions around those sizes, behind cached keys, with one far key early or late in
+    the context that the last token must find."""
+    monkeypatch.setenv("MSTAR_PREFILL_ATTENTION", "tcgen05")
+    per_tile = 128 // (nq // nkv)
+    lens_q = [1, per_tile - 1, per_tile, per_tile + 1, 2 * per_tile, 2, 700]
+    lens_kv = [33, per_tile - 1, 300, per_tile + 1, 2 * per_tile + 5, 130, 900]
+    for seed in (1, 2):
+        got, want, _ = paged_case(lens_q, lens_kv, nq, nkv, hd, page, torch.bfloat16, seed=seed,
+                                  kernel="prefill")
+        assert (got - want).abs().max() < 2e-2
+    for far_key in (3, 600):
+        got, want, vs = paged_case([300], [640], nq, nkv, hd, page, torch.bfloat16, seed=5,
+                                   spike=(0, far_key), kernel="prefill")
+        assert (got - want).abs().max() < 2e-2
+        # the last token sees the key, which carries most of its weight: a tile that lost it
+        # would be off by far more than the tolerance above
+        far = vs[0][far_key, 0].double()
+        assert hd > 128 or (want[299, 0] - far).abs().max() < 0.5 * far.abs().max()
+    assert tc_clean() == 0
+
+
 @pytest.mark.parametrize("page", [8, 16, 128])
 def test_attention_kernels_over_long_contexts(page):
     """Thousands of keys: the producers fetch block-table entries 32 at a time and wrap
