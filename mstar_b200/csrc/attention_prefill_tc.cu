@@ -13,18 +13,19 @@
 //     per page and 64-feature half, 128-byte swizzle, issued side by side from several
 //     lanes) into two rings of two stages;
 //   * a lane of the S warp issues S = Q K^T as tcgen05.mma (M 128, N 64, K 16 per step) into
-//     tensor memory, as soon as the softmax threads hold the tile before in registers;
+//     one of two buffers in tensor memory, a tile ahead of the softmax threads: the buffer
+//     is free when O += P V of the tile before last is done;
 //   * 128 softmax threads each own one row: they read their row of S from tensor memory
 //     (tcgen05.ld; the row maximum and sum need no shuffles), and write the probabilities
-//     as packed bfloat16 into one of two P buffers in tensor memory (tcgen05.st), so P
-//     never passes through shared memory; they rescale their row of the running output O
-//     in tensor memory only when the row maximum grew by more than 2^8;
+//     as packed bfloat16 over the first half of the same row (tcgen05.st), so P never
+//     passes through shared memory; they rescale their row of the running output O in
+//     tensor memory only when the row maximum grew by more than 2^8;
 //   * a lane of the O warp issues O += P V (M 128, N head_dim, K 16 x 4) with P as the A
 //     operand from tensor memory and V as the N-major B operand straight from the
 //     cache's [key][feature] tiles.
 // At the end each thread reads its row of O, divides by the softmax sum and stores.
 // At head_dim 128 two CTAs fit on an SM (97 KB of shared memory, 256 TMEM columns each:
-// S 64, P 2 x 32, O 128), so one CTA's softmax overlaps the other's MMAs; at 64 there is
+// S and P 2 x 64, O 128), so one CTA's softmax overlaps the other's MMAs; at 64 there is
 // room for more, at 256 (193 KB, 512 columns) for one.
 //
 // With one prompt alone the CTAs are few (a few hundred, of 1 to 32 key tiles) and the
@@ -149,7 +150,7 @@ __host__ __device__ constexpr int pt_smem(int hd) { return pt_q_bytes(hd) + 4 * 
 // What a launch asks for: at head_dim 64 more than the kernel uses, so that no more CTAs
 // land on an SM than its 512 TMEM columns serve (a further one would wait in its allocation).
 __host__ __device__ constexpr int pt_smem_launch(int hd) { return pt_smem(hd) < 77 * 1024 ? 77 * 1024 : pt_smem(hd); }
-// Tensor memory: S 64 columns, P 2 x 32, O head_dim; allocations are powers of two.
+// Tensor memory: S / P 2 x 64 columns, O head_dim; allocations are powers of two.
 __host__ __device__ constexpr uint32_t pt_tmem_cols(int hd) { return hd <= 128 ? 256u : 512u; }
 // The running maximum of a row follows the tile maxima only when they exceed it by more
 // than this (in powers of two): probabilities then reach 2^8 at most, which float sums and
@@ -176,13 +177,11 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map,
     uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + 2 * PT_KV_TILE);
     // k_full[2], v_full[2]: a stage's copies have landed.  k_empty[2]: S of the stage's tile
     // is done.  v_empty[2]: O += P V of the stage's tile is done (the values may be refilled,
-    // the tile's P overwritten, O rescaled or read).  s_full: S of a tile is done; s_read: all
-    // softmax threads hold it in registers (the next S may overwrite it).  p_ready[2]: P of a
-    // tile is written.  The last three take one arrival per softmax thread or per commit and
-    // go through one phase per tile (per two tiles for the pairs).
+    // the tile's S / P buffer overwritten by S of the tile after next, O rescaled or read).
+    // s_full[2]: S of a tile is done.  p_ready[2]: P of a tile is written (one arrival per
+    // softmax thread).  All go through one phase per two tiles.
     const uint32_t k_full = tc_smem(bars + 0), v_full = tc_smem(bars + 2), k_empty = tc_smem(bars + 4),
-                   v_empty = tc_smem(bars + 6), p_ready = tc_smem(bars + 8), s_full = tc_smem(bars + 10),
-                   s_read = tc_smem(bars + 11);
+                   v_empty = tc_smem(bars + 6), p_ready = tc_smem(bars + 8), s_full = tc_smem(bars + 10);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 13);
 
     // grid: x the kv head, y the row tile with the longest first (the tiles with the most keys
@@ -209,7 +208,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map,
     const uint32_t q_ready = tc_smem(bars + 12);
     if (tid == 0) {
         for (int i = 0; i < 13; ++i)
-            mbar_init(tc_smem(bars + i), i == 8 || i == 9 || i == 11 ? 128 : 1);
+            mbar_init(tc_smem(bars + i), i == 8 || i == 9 ? 128 : 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (tid >= RPT && tid < PT_ROWS) {
@@ -230,8 +229,9 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map,
     __syncthreads();
     pt_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_s = tmem;         // S: columns 0..63
-    const uint32_t tmem_p = tmem + 64;    // P: two buffers of 32 columns (64 packed keys each)
+    // S / P: two buffers of 64 columns; a tile's S (64 floats per row) is replaced in place by
+    // its P (64 packed bfloat16 = 32 columns), each thread overwriting what it alone has read
+    const uint32_t tmem_sp = tmem;
     const uint32_t tmem_o = tmem + 128;   // O: head_dim columns from 128 on
 
     if (warp == 5 || warp == 7) {
@@ -315,15 +315,17 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map,
                     dq[kk] = pt_desc(q_addr + (uint32_t)(kk >> 2) * (PT_ROWS * 128) + (uint32_t)(kk & 3) * 32, 16, 1024);
                     dk[kk] = pt_desc(k_addr + (uint32_t)(kk >> 2) * (PT_KEYS * 128) + (uint32_t)(kk & 3) * 32, 16, 1024);
                 }
-                // the softmax threads hold S of tile j-1 in registers
-                if (j >= 1 && !mbar_wait(s_read, (uint32_t)(j - 1) & 1u)) {
+                // the buffer is free once O += P V of tile j-2, which read P from it, is done:
+                // S runs a tile ahead of the softmax threads
+                if (j >= 2 && !mbar_wait(v_empty + 8 * s, (((uint32_t)j >> 1) & 1u) ^ 1u)) {
                     atomicExch(error_word, 8);
                     break;
                 }
                 pt_fence_after();
 #pragma unroll
-                for (int kk = 0; kk < HD / 16; ++kk) pt_mma(tmem_s, dq[kk], dk[kk], idesc_s, kk != 0);
-                pt_commit(s_full);
+                for (int kk = 0; kk < HD / 16; ++kk)
+                    pt_mma(tmem_sp + (uint32_t)s * 64, dq[kk], dk[kk], idesc_s, kk != 0);
+                pt_commit(s_full + 8 * s);
                 pt_commit(k_empty + 8 * s);
             }
         }
@@ -350,7 +352,7 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map,
 #pragma unroll
                 for (int kk = 0; kk < PT_KEYS / 16; ++kk) {
                     const uint64_t db = pt_desc(v_addr + (uint32_t)kk * 16 * 128, PT_KEYS * 128, 1024);
-                    pt_mma_ts(tmem_o, tmem_p + (uint32_t)s * 32 + (uint32_t)kk * 8, db, idesc_o, (j | kk) != 0);
+                    pt_mma_ts(tmem_o, tmem_sp + (uint32_t)s * 64 + (uint32_t)kk * 8, db, idesc_o, (j | kk) != 0);
                 }
                 pt_commit(v_empty + 8 * s);   // the values are consumed, O holds tiles 0..j
             }
@@ -367,18 +369,16 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map,
         float m = -INFINITY, l = 0.f;     // m: the reference maximum, in scaled (log2) units
         bool ok = true;
         for (int j = 0; j < ntiles; ++j) {
-            if (!pt_wait_warp(s_full, (uint32_t)j & 1u)) {
+            if (!pt_wait_warp(s_full + 8 * (j & 1), ((uint32_t)j >> 1) & 1u)) {
                 if (lane == 0) atomicExch(error_word, 10);
                 ok = false;
                 break;
             }
             pt_fence_after();
             uint32_t s0[32], s1[32];
-            pt_ld32(tmem_s + lane_off, s0);
-            pt_ld32(tmem_s + lane_off + 32, s1);
+            pt_ld32(tmem_sp + lane_off + (uint32_t)(j & 1) * 64, s0);
+            pt_ld32(tmem_sp + lane_off + (uint32_t)(j & 1) * 64 + 32, s1);
             pt_wait_ld();
-            pt_fence_before();
-            mbar_arrive(s_read);                          // the next S may be computed
             const int key0 = j * PT_KEYS;
             if (key0 + PT_KEYS - 1 > cp_min) {            // the tile touches the diagonal
 #pragma unroll
@@ -433,14 +433,8 @@ prefill_attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map,
                     pt_st32(tmem_o + lane_off + (uint32_t)c0, o);
                 }
             }
-            // P of tile j-2 lies in this tile's buffer until O += P V of that tile is done
-            if (j >= 2 && !pt_wait_warp(v_empty + 8 * (j & 1), ((uint32_t)(j - 2) >> 1) & 1u)) {
-                if (lane == 0) atomicExch(error_word, 11);
-                ok = false;
-                break;
-            }
-            // column c of the buffer holds keys 2c, 2c+1
-            pt_st32(tmem_p + lane_off + (uint32_t)(j & 1) * 32, packed);
+            // P over the first half of this row's S: column c holds keys 2c, 2c+1
+            pt_st32(tmem_sp + lane_off + (uint32_t)(j & 1) * 64, packed);
             pt_wait_st();
             pt_fence_before();
             mbar_arrive(p_ready + 8 * (j & 1));
