@@ -559,14 +559,16 @@ static int launch_decode_tma(const CUtensorMap& map, const DecodeArgs& a, int to
 // ------------------------------------------------------------- persistent ring variant
 // The same tiles and arithmetic once more, with the launch turned inside out: the grid is
 // what fits on the GPU at once, every CTA walks over work items (token, kv head, split),
-// and a producer warp keeps a ring of key/value tiles filled across item boundaries, so
-// that the copies of the next item are in flight while this one is computed.  With one
+// and two producer warps (one for the keys, one for the values) keep a ring of key/value
+// tiles filled across item boundaries, so that the copies of the next item are in flight
+// while this one is computed.  With one
 // CTA per item a CTA lives for a launch plus two or three DRAM latencies, and at small
 // batches most of a decode step's attention time was that; here the latencies overlap.
-// The producer's lanes fetch 32 block-table entries at a time and issue the copies of a
-// tile side by side; the four consumer warps take 16 keys of a tile each, as above, and
+// A producer's lanes fetch 32 block-table entries at a time and issue the copies of a
+// tile side by side (its loop has no division and no exchange but the page numbers: with
+// few tiles per CTA its length is the CTA's pace); the four consumer warps take 16 keys of a tile each, as above, and
 // are merged in shared memory at the end of an item.
-#define RING_THREADS (DEC_THREADS + 32)
+#define RING_THREADS (DEC_THREADS + 64)   // four consumer warps, a copy warp for the keys, one for the values
 
 struct RingLayout {   // byte offsets into dynamic shared memory, made on the host
     int stages, q_off, om_off, ml_off, bar_off, total;
@@ -608,16 +610,20 @@ decode_attention_ring_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeA
     if (tid == 0) {
         *failed = 0;
         for (int s = 0; s < S; ++s) {
-            mbar_init(full + 8 * s, 1);
+            mbar_init(full + 8 * s, 2);                     // the keys' warp and the values'
             mbar_init(empty + 8 * s, DEC_THREADS / 32);
         }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
-    if (warp == DEC_THREADS / 32) {
-        // ------------------------------------------------------------------ producer
-        int c = 0;
+    if (warp >= DEC_THREADS / 32) {
+        // ----------------------------------------- producers: a warp for the keys, one for the values
+        // st: the ring's stage, round: how often the ring has been filled before (counted, not
+        // divided: the loop is the pace of a CTA with few tiles); page sizes are powers of two
+        const int which = warp - DEC_THREADS / 32;
+        int st = 0, round = 0;
+        const int ps_log = 31 - __clz(ps);
         bool ok = true, waited = !a.keys_static;
         for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
             const int split = item % a.splits, kvh = (item / a.splits) % a.nkv, t = item / (a.splits * a.nkv);
@@ -627,44 +633,48 @@ decode_attention_ring_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeA
             if (ks >= ke) continue;
             const int* bt = a.block_table + (size_t)a.token_req[t] * a.bt_stride;
             // pages beyond the request's last one are replaced by it: masked keys stay finite
-            const int last_page = (hi - 1) / ps;
+            const int last_page = (hi - 1) >> ps_log;
             // a tile is DEC_TILE / ps whole pages, or, with pages of 128 or 256 keys, a part of one
-            const int per_tile = ps < DEC_TILE ? DEC_TILE / ps : 1;
+            const int per_tile = ps < DEC_TILE ? DEC_TILE >> ps_log : 1;
             const int box_rows = ps < DEC_TILE ? ps : DEC_TILE;
             const int ntiles = (ke - ks + DEC_TILE - 1) / DEC_TILE;
             int mine = 0, have_from = -1;              // lanes hold pages have_from .. +31
-            for (int it = 0; it < ntiles; ++it, ++c) {
-                const int st = c % S;
+            const int p = lane / HALVES, h = lane % HALVES;   // this lane's page and block of a tile
+            for (int it = 0; it < ntiles; ++it) {
                 const int key0 = ks + it * DEC_TILE;
                 if (!waited && key0 + DEC_TILE >= hi) {   // the tile with the token's own key
                     pdl_wait();
                     waited = true;
                 }
-                const int base_page = key0 / ps;
+                const int base_page = key0 >> ps_log;
                 if (have_from < 0 || base_page + per_tile > have_from + 32) {
                     have_from = base_page;
                     mine = bt[min(base_page + lane, last_page)];
                 }
-                if (lane == 0) {
-                    if (c >= S && !mbar_wait(empty + 8 * st, ((uint32_t)(c / S) - 1u) & 1u)) {
+                // lane HALVES p + h waits for the stage and copies 64-feature block h of page p
+                const int page = __shfl_sync(0xffffffffu, mine, (base_page + p - have_from) & 31);
+                if (p < per_tile) {
+                    if (round > 0 && !mbar_wait(empty + 8 * st, ((uint32_t)round - 1u) & 1u)) {
                         atomicExch(error_word, 4);
                         ok = false;
                     } else {
-                        mbar_expect_tx(full + 8 * st, 2 * TILE_BYTES);
+                        // the bytes may land before lane 0 has announced them: the phase cannot
+                        // end before the two warps' arrivals
+                        if (lane == 0) mbar_expect_tx(full + 8 * st, TILE_BYTES);
+                        unsigned char* dst = ring + (size_t)st * 2 * TILE_BYTES + which * TILE_BYTES +
+                                             h * (64 * 128) + p * box_rows * 128;
+                        const int in_page = key0 & (ps - 1);   // 0 unless the page is larger than the tile
+                        tma_load_2d(tc_smem(dst), &kv_map, full + 8 * st, h * 64,
+                                    ((page * 2 + which) * a.nkv + kvh) * ps + in_page);
                     }
                 }
-                ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
-                if (!ok) break;
-                // lane HALVES p + h copies 64-feature block h of page p, keys and values
-                const int p = lane / HALVES, h = lane % HALVES;
-                const int page = __shfl_sync(0xffffffffu, mine, (base_page + p - have_from) & 31);
-                if (p < per_tile) {
-                    unsigned char* kdst = ring + (size_t)st * 2 * TILE_BYTES + h * (64 * 128) + p * box_rows * 128;
-                    const int in_page = key0 % ps;      // 0 unless the page is larger than the tile
-                    tma_load_2d(tc_smem(kdst), &kv_map, full + 8 * st, h * 64,
-                                ((page * 2) * a.nkv + kvh) * ps + in_page);
-                    tma_load_2d(tc_smem(kdst + TILE_BYTES), &kv_map, full + 8 * st, h * 64,
-                                ((page * 2 + 1) * a.nkv + kvh) * ps + in_page);
+                if (!__all_sync(0xffffffffu, ok)) {
+                    ok = false;
+                    break;
+                }
+                if (++st == S) {
+                    st = 0;
+                    ++round;
                 }
             }
         }
@@ -674,7 +684,7 @@ decode_attention_ring_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeA
 
     // ---------------------------------------------------------------------- consumers
     if (a.keys_static) pdl_wait();        // the queries are the output of the kernel before
-    int c = 0;
+    int st = 0, round = 0;                // as the producer counts them
     for (int item = blockIdx.x; item < items; item += gridDim.x) {
         const int split = item % a.splits, kvh = (item / a.splits) % a.nkv, t = item / (a.splits * a.nkv);
         const int hi = a.cache_pos[t] + 1;
@@ -696,9 +706,8 @@ decode_attention_ring_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeA
         for (int n = 0; n < HD / 8; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
         float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
         const int ntiles = (ke - ks + DEC_TILE - 1) / DEC_TILE;
-        for (int it = 0; it < ntiles; ++it, ++c) {
-            const int st = c % S;
-            if (!mbar_wait(full + 8 * st, (uint32_t)(c / S) & 1u)) {
+        for (int it = 0; it < ntiles; ++it) {
+            if (!mbar_wait(full + 8 * st, (uint32_t)round & 1u)) {
                 // give up, but together with the other warps (they wait at the barrier below)
                 if (lane == 0) atomicExch(error_word, 4);
                 *failed = 1;
@@ -772,6 +781,10 @@ decode_attention_ring_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeA
             __syncwarp();
             if (lane == 0) {
                 asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(empty + 8 * st) : "memory");
+            }
+            if (++st == S) {
+                st = 0;
+                ++round;
             }
         }
 
