@@ -321,16 +321,21 @@ def test_prefill_attention_both_kernels(which, nq, nkv, page, hd, monkeypatch):
 
 
 @pytest.mark.parametrize("nq,nkv,page,hd", [(24, 8, 16, 128), (5, 1, 8, 128), (14, 2, 64, 64),
-                                            (4, 2, 16, 256), (4, 4, 32, 128)])
+                                            (4, 2, 16, 256), (4, 4, 32, 128), (9, 1, 16, 64),
+                                            (32, 2, 64, 128), (128, 1, 32, 64)])
 def test_prefill_attention_tcgen05_row_tiles(nq, nkv, page, hd, monkeypatch):
     """The tcgen05 kernel's row tiles are whole tokens (128 // G of them, G query heads per kv
     head: 126 rows at G 3, 125 at 5, 126 at 7) fetched by one TMA box per 64 features: prompts
     and portions around those sizes, behind cached keys, with one far key early or late in
     the context that the last token must find."""
+    from mstar_b200 import ops
+
     monkeypatch.setenv("MSTAR_PREFILL_ATTENTION", "tcgen05")
+    assert ops.prefill_attention_kernel(True, hd, page, nq // nkv) == "tcgen05"
+    assert ops.prefill_attention_kernel(True, hd, page, 129) == "mma"    # more heads than a tile has rows
     per_tile = 128 // (nq // nkv)
-    lens_q = [1, per_tile - 1, per_tile, per_tile + 1, 2 * per_tile, 2, 700]
-    lens_kv = [33, per_tile - 1, 300, per_tile + 1, 2 * per_tile + 5, 130, 900]
+    lens_q = [1, max(1, per_tile - 1), per_tile, per_tile + 1, 2 * per_tile, 2, 700 if nq < 100 else 90]
+    lens_kv = [33, max(1, per_tile - 1), 300, per_tile + 1, 2 * per_tile + 5, 130, 900 if nq < 100 else 200]
     for seed in (1, 2):
         got, want, _ = paged_case(lens_q, lens_kv, nq, nkv, hd, page, torch.bfloat16, seed=seed,
                                   kernel="prefill")
