@@ -707,7 +707,8 @@ decode_attention_ring_kernel(const __grid_constant__ CUtensorMap kv_map, DecodeA
         float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
         const int ntiles = (ke - ks + DEC_TILE - 1) / DEC_TILE;
         for (int it = 0; it < ntiles; ++it) {
-            if (!mbar_wait(full + 8 * st, (uint32_t)round & 1u)) {
+            // one outcome for the warp: the matrix instructions below are warp-wide
+            if (!__all_sync(0xffffffffu, mbar_wait(full + 8 * st, (uint32_t)round & 1u))) {
                 // give up, but together with the other warps (they wait at the barrier below)
                 if (lane == 0) atomicExch(error_word, 4);
                 *failed = 1;

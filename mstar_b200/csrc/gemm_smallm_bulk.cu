@@ -216,7 +216,8 @@ smallm_bulk_kernel(const bf16* __restrict__ x, const bf16* __restrict__ W, OutT*
             } else {
                 load_x(ch, xv, xw);
             }
-            if (!mbar_wait(full + 8 * st, (uint32_t)(c / SB_STAGES) & 1u)) {
+            // one outcome for the warp: the matrix instructions below are warp-wide
+            if (!__all_sync(0xffffffffu, mbar_wait(full + 8 * st, (uint32_t)(c / SB_STAGES) & 1u))) {
                 // give up, but only together with the other warps (they wait at the barrier below)
                 if (lane == 0) atomicExch(error_word, 14);
                 *failed = 1;
