@@ -348,9 +348,11 @@ def _time_graph(fn, reps: int = 20, rounds: int = 5) -> float:
     with torch.cuda.graph(graph):
         for _ in range(reps):
             fn()
-    # replays until the clocks have left their idle state (a kernel of tens of microseconds,
-    # timed from a cold start, runs at two thirds of the clock that it sees inside a step)
-    warm = float(os.environ.get("MSTAR_BENCH_WARM_MS", "50"))
+    # MSTAR_BENCH_WARM_MS=N replays for N ms first: short kernels then see the clocks of a busy
+    # GPU (a little faster), long ones its power cap (8,192-token attention 0.41 instead of
+    # 0.37 ms); the figures in profiles/ are taken without, like the burst peak they are
+    # compared with
+    warm = float(os.environ.get("MSTAR_BENCH_WARM_MS", "0"))
     t0 = time.perf_counter()
     while (time.perf_counter() - t0) * 1e3 < warm:
         for _ in range(10):
