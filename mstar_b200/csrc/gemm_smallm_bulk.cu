@@ -422,6 +422,22 @@ MSTAR_API int mstar_qkv_rope_write_bulk_bf16(const void* x, const void* W, void*
                     nq, nkv, hd, page_size, bt_stride};
     const int n_out = (nq + 2 * nkv) * hd;
     cudaStream_t s = (cudaStream_t)stream;
+    // Strips of 32 rows (two 8-row groups of each half) for 9 to 16 tokens where the head size
+    // allows: x is read half as often (12.0 -> 10.6 us at 16 tokens); with up to 8 tokens
+    // strips of 16 rows are faster (8.5 against 10.1 us).  MSTAR_ROPE_NT=1|2 forces one.
+    static int rope_nt = -1;
+    if (rope_nt < 0) {
+        const char* e = getenv("MSTAR_ROPE_NT");
+        rope_nt = e ? atoi(e) : 0;
+    }
+    const bool wide = rope_nt == 2 || (rope_nt != 1 && M > 8);
+    if (wide && hd % 32 == 0) {
+        if (M > 8)
+            return launch_bulk_nt<SB_ROPE, true, 2, bf16>((const bf16*)x, (const bf16*)W, (bf16*)q_out, M, n_out, K,
+                                                          ldx, ldw, ldo, hd / 2, w_static, error_word, s, rp);
+        return launch_bulk_nt<SB_ROPE, false, 2, bf16>((const bf16*)x, (const bf16*)W, (bf16*)q_out, M, n_out, K,
+                                                       ldx, ldw, ldo, hd / 2, w_static, error_word, s, rp);
+    }
     if (M > 8)
         return launch_bulk_nt<SB_ROPE, true, 1, bf16>((const bf16*)x, (const bf16*)W, (bf16*)q_out, M, n_out, K,
                                                       ldx, ldw, ldo, hd / 2, w_static, error_word, s, rp);
