@@ -602,43 +602,92 @@ MSTAR_API int mstar_sample(const float* logits, int ld, int rows, int vocab,
     return launch_status();
 }
 
-// Greedy only: argmax of each row (smallest index among equal maxima).
-__global__ void __launch_bounds__(SAMPLE_THREADS)
-argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out) {
+// Greedy only: argmax of each row (smallest index among equal maxima).  A row is cut into
+// `gridDim.y` pieces, a CTA each (one CTA alone reads a row of 157 k logits in some 15 us, at
+// the rate of a single SM); a piece's best is a 64-bit key, the value's ordered bits above the
+// complemented index, so that the maximum over keys is the largest value and, among equal
+// values, the smallest index; keys meet in `best[row]` by atomicMax, and the CTA that counts
+// itself last at `arrived[row]` writes the token and puts both back to zero for the next
+// launch.  Nobody waits.  `best` and `arrived` must be zero at the first launch and belong to
+// one stream at a time.
+#define ARGMAX_THREADS 256
+__global__ void __launch_bounds__(ARGMAX_THREADS)
+argmax_kernel(const float* __restrict__ logits, int ld, int vocab, int* __restrict__ out,
+              unsigned long long* __restrict__ best, int* __restrict__ arrived) {
     logits = pdl_after(logits, pdl_wait());   // written by the kernel before
-    __shared__ float best_v[32];
-    __shared__ int best_i[32];
+    __shared__ unsigned long long best_k[ARGMAX_THREADS / 32];
     const int row = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const float* x = logits + (size_t)row * ld;
-    float bv = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int i = tid; i < vocab; i += SAMPLE_THREADS) {
-        const float v = x[i];
-        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    // this CTA's piece: whole groups of four, so that aligned rows are read 16 bytes at a time
+    const int groups = (vocab + 3) / 4;
+    const int per = (groups + (int)gridDim.y - 1) / (int)gridDim.y;
+    const int g0 = (int)blockIdx.y * per, g1 = min(groups, g0 + per);
+    const bool vec = (ld % 4 == 0) && ((reinterpret_cast<uintptr_t>(logits) & 15) == 0);
+    unsigned long long key = 0ull;             // below every real key (ordered bits are never 0 for a number)
+    auto take = [&](float f, int i) {
+        f = f == f ? f : -INFINITY;                                   // a NaN never wins
+        const unsigned long long k =
+            ((unsigned long long)ordered_bits(f) << 32) | (unsigned long long)(0xffffffffu - (unsigned)i);
+        key = k > key ? k : key;
+    };
+    int g = g0 + tid;
+    if (vec) {
+        // four loads of 16 bytes in flight per thread
+        for (; g + 3 * ARGMAX_THREADS < g1 && 4 * (g + 3 * ARGMAX_THREADS) + 3 < vocab; g += 4 * ARGMAX_THREADS) {
+            float4 q[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) q[u] = *reinterpret_cast<const float4*>(x + 4 * (g + u * ARGMAX_THREADS));
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i0 = 4 * (g + u * ARGMAX_THREADS);
+                take(q[u].x, i0);
+                take(q[u].y, i0 + 1);
+                take(q[u].z, i0 + 2);
+                take(q[u].w, i0 + 3);
+            }
+        }
+    }
+    for (; g < g1; g += ARGMAX_THREADS) {
+        const int i0 = 4 * g;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (i0 + j < vocab) take(x[i0 + j], i0 + j);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
-        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
+        key = other > key ? other : key;
     }
-    if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
+    if (lane == 0) best_k[warp] = key;
     __syncthreads();
-    if (warp == 0) {
-        bv = best_v[lane]; bi = best_i[lane];
+    if (tid == 0) {
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        for (int w = 1; w < ARGMAX_THREADS / 32; ++w) key = best_k[w] > key ? best_k[w] : key;
+        atomicMax(best + row, key);
+        __threadfence();
+        if (atomicAdd(arrived + row, 1) == (int)gridDim.y - 1) {
+            __threadfence();
+            const unsigned long long top = atomicExch(best + row, 0ull);
+            out[row] = (int)(0xffffffffu - (unsigned)(top & 0xffffffffull));
+            arrived[row] = 0;
         }
-        if (lane == 0) out[row] = bi;
     }
 }
 
-MSTAR_API int mstar_argmax(const float* logits, int ld, int rows, int vocab, int* out,
-                           void* stream) {
+// `best` [rows] of 64 bits and `arrived` [rows] ints: scratch that is zero before the first
+// launch; the kernel leaves it zero.
+MSTAR_API int mstar_argmax(const float* logits, int ld, int rows, int vocab, int* out, void* best,
+                           int* arrived, void* stream) {
     if (rows <= 0) return 0;
-    mstar_launch((argmax_kernel), dim3(rows), dim3(SAMPLE_THREADS), 0, (cudaStream_t)stream, logits, ld, vocab, out);
+    if (vocab <= 0 || best == nullptr || arrived == nullptr) return -1;
+    // pieces of 8 k logits or more, as many CTAs as fill the GPU about once (eight of these
+    // CTAs fit on an SM)
+    int pieces = (vocab + 8191) / 8192;
+    const int fit = 8 * device_sm_count() / rows;
+    if (pieces > fit) pieces = fit;
+    if (pieces < 1) pieces = 1;
+    if (pieces > 64) pieces = 64;
+    mstar_launch((argmax_kernel), dim3(rows, pieces), dim3(ARGMAX_THREADS), 0, (cudaStream_t)stream, logits, ld,
+                 vocab, out, (unsigned long long*)best, arrived);
     return launch_status();
 }

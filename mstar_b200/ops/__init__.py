@@ -655,13 +655,30 @@ def gated_up(x: torch.Tensor, w_gate_up: torch.Tensor, static_weights: bool = Fa
     return silu_mul(linear(x, w_gate_up))
 
 
+_argmax_scratch: dict = {}
+
+
+def _argmax_buffers(device, rows: int):
+    """Zeroed scratch of the argmax kernel (a 64-bit key and a counter per row); the kernel
+    leaves it zeroed.  One per device: launches that share it run on one stream."""
+    key = torch.device(device).index or 0
+    have = _argmax_scratch.get(key)
+    if have is None or have[1].numel() < rows:
+        n = max(rows, 1024)
+        have = _argmax_scratch[key] = (torch.zeros(n, dtype=torch.int64, device=device),
+                                       torch.zeros(n, dtype=torch.int32, device=device))
+    return have
+
+
 def argmax(logits: torch.Tensor):
     _need_cuda(logits)
     assert logits.dtype == torch.float32 and logits.dim() == 2 and logits.stride(1) == 1
     rows, vocab = logits.shape
     out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    best, arrived = _argmax_buffers(logits.device, rows)
     check(lib.get("sampling").mstar_argmax(
-        logits.data_ptr(), logits.stride(0), rows, vocab, out.data_ptr(), _stream()), "argmax")
+        logits.data_ptr(), logits.stride(0), rows, vocab, out.data_ptr(), best.data_ptr(),
+        arrived.data_ptr(), _stream()), "argmax")
     return out
 
 

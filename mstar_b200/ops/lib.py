@@ -64,7 +64,7 @@ _SIGNATURES = {
     },
     "sampling": {
         "mstar_sample": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp],
-        "mstar_argmax": [_vp, _i, _i, _i, _vp, _vp],
+        "mstar_argmax": [_vp, _i, _i, _i, _vp, _vp, _vp, _vp],
     },
 }
 

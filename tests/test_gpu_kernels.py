@@ -471,6 +471,31 @@ def test_argmax_and_greedy_rows():
     assert torch.equal(ops.sample(logits, temp), want)
 
 
+@pytest.mark.parametrize("rows,vocab", [(1, 7), (8, 156940), (64, 50001), (300, 1024), (3, 32768)])
+def test_argmax_in_pieces(rows, vocab):
+    """The greedy kernel cuts a row into pieces that meet in a 64-bit atomic maximum: rows
+    whose width is no multiple of four and whose stride is not the width, equal maxima in
+    different pieces (the smaller index wins), a maximum in the last element, negative rows,
+    a NaN that must not win, and launch after launch on the same scratch."""
+    from mstar_b200 import ops
+
+    wide = rnd(rows, vocab + 3, seed=rows + vocab) - 3.0
+    logits = wide[:, 1:vocab + 1]                      # a view: odd offset, stride != width
+    assert logits.stride(0) != vocab and logits.data_ptr() % 16 != 0
+    if vocab > 100:
+        logits[0, 5] = logits[0, vocab - 2] = 40.0     # equal maxima far apart
+        logits[rows - 1, vocab - 1] = 41.0             # the last element
+        logits[rows // 2, 3] = float("nan")
+    want = torch.nan_to_num(logits, nan=-float("inf")).argmax(-1).int()
+    if vocab > 100:
+        want[0] = 5 if rows > 1 else want[0]
+    for _ in range(3):
+        assert torch.equal(ops.argmax(logits), want)
+    aligned = logits.contiguous() if vocab % 4 == 0 else None
+    if aligned is not None:
+        assert torch.equal(ops.argmax(aligned), want)  # the 16-byte loads
+
+
 def draw(logits, temperature, seed, offset, **kw):
     from mstar_b200 import ops
 
