@@ -299,7 +299,7 @@ def run_workload(name: str, page_size: int) -> dict:
               max_num_batched_tokens=w["budget"], max_concurrent_requests=w["requests"],
               max_batch_size=w["requests"])
     params = SamplingParams(temperature=0.0, ignore_eos=True, max_output_tokens=w["new_tokens"])
-    result = {}
+    result, before = {}, None
     for run in ("warm-up", "timed"):
         torch.cuda.synchronize()
         t0 = time.perf_counter()
@@ -319,7 +319,12 @@ def run_workload(name: str, page_size: int) -> dict:
         seconds = time.perf_counter() - t0
         assert done == len(ids) and len(first) == len(ids)
         generated = w["requests"] * w["new_tokens"]
-        result = {"tokens_per_s": generated / seconds, "seconds": seconds,
+        # the two runs decode the same prompts greedily: the same tokens, whatever the
+        # batches were that the scheduler formed
+        tokens = [list(waiting[rid].output) for rid in ids]
+        agree = None if run == "warm-up" else tokens == before
+        before = tokens
+        result = {"tokens_per_s": generated / seconds, "seconds": seconds, "runs_agree": agree,
                   "ttft_ms_median": statistics.median(first.values()) * 1e3,
                   "ttft_ms_max": max(first.values()) * 1e3,
                   "prompt_tokens": sum(lens), "generated_tokens": generated,
@@ -601,6 +606,7 @@ def main() -> int:
         points[f"{tag}_tok_s"] = round(w["tokens_per_s"], 1)
         points[f"{tag}_ttft_ms"] = round(w["ttft_ms_median"], 1)
         points[f"{tag}_seconds"] = round(w["seconds"], 3)
+        points[f"{tag}_runs_agree"] = 1.0 if w["runs_agree"] else 0.0
         print(f"[bench] {name}: {json.dumps(w)}", file=sys.stderr, flush=True)
 
     record = {
