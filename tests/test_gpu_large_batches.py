@@ -199,3 +199,63 @@ def test_many_requests_at_the_benchmark_sizes(big, dtype, page, live, skinny, mo
               f"{rounded_tol[0]:.3e}")
     del model
     torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_random_serving_schedules_at_the_benchmark_sizes(big, dtype):
+    """Schedules drawn at random: 3 to 13 requests of 1 to 40 or of 30 to 300 tokens, prompts of
+    5 to 95 % of them, 1 to 8 live at a time, token budgets from 2 to 700 (portions down to one
+    token beside decoded tokens), pages of 8, 16, 32 and 64, pools sized so that pages are
+    reused.  In bfloat16 the tolerance against the float64 plain model is measured on the very
+    rows compared (1.5 times what rounding activations to bfloat16 does to the plain model), as
+    in the test of 40 requests above."""
+    from mstar_b200 import ops
+    from mstar_b200.engine.model import load_model
+    from mstar_b200.engine.step import make_stepper
+
+    cfg, tensors = big[0], big[1]
+    head = tensors["model.embed_tokens.weight"].double()
+    model = load_model(None, dtype=dtype, device="cuda:0", config=cfg, tensors=tensors)
+    rng = np.random.default_rng(20)
+    for trial in range(5):
+        count = int(rng.integers(3, 14))
+        lo, hi = (1, 40) if trial % 3 == 0 else (30, 300)
+        reqs, prompt_len = {}, {}
+        for i in range(count):
+            n = int(rng.integers(lo, hi + 1))
+            reqs[f"q{i}"] = H.request_tokens(CFG["vocab_size"], n, seed=trial * 100 + i)
+            prompt_len[f"q{i}"] = max(1, int(n * rng.uniform(0.05, 0.95)))
+        live = int(rng.integers(1, 9))
+        budget = max(int(rng.choice([2, 7, 37, 64, 130, 256, 700])), live + 1)
+        page = int(rng.choice([16, 64, 8, 32]))
+        steps = H.serving(reqs, prompt_len, max_live=live, budget=budget)
+        pages = H.max_tokens_of(steps, page) // page
+        want, rounded, keep = {}, {}, set()
+        for rid, toks in reqs.items():
+            n, p = len(toks), prompt_len[rid]
+            rows = sorted({0, p - 1, min(p, n - 1), n - 1} | set(range(p, n, 5)))
+            exact = P.plain_hidden_states(tensors, CFG, toks)[rows] @ head.T
+            if dtype == "bfloat16":
+                bf16 = P.plain_hidden_states(tensors, CFG, toks, act=P.round_bf16)[rows] @ head.T
+            for i, r in enumerate(rows):
+                want[(rid, r)] = exact[i].cpu()
+                if dtype == "bfloat16":
+                    rounded[(rid, r)] = bf16[i].cpu()
+                keep.add((rid, r))
+        stepper = make_stepper(model, page_size=page, num_pages=pages, num_slots=live)
+        got = H.run_steps_in_process(stepper, steps, device_fed_seed=trial, keep=keep)
+        assert stepper.manager.check() == 0 and stepper.manager.num_requests() == 0
+        assert stepper.manager.free_pages(0) == pages
+        ops.check_error_word("cuda:0")
+        what = (f"trial {trial}: {count} requests of {lo}..{hi} tokens, {live} live, budget "
+                f"{budget}, pages of {page}")
+        if dtype == "float32":
+            tol, mean_tol = TOLS[dtype]
+        else:
+            noise = spread(rounded, want)
+            tol, mean_tol = 1.5 * noise[0], 1.5 * noise[1]
+        worst = H.compare(got, want, dtype, what, tol=tol, mean_tol=mean_tol)
+        print(f"{what} [{dtype}]: worst abs error {worst:.3e} of {tol:.3e}")
+        del stepper
+    del model
+    torch.cuda.empty_cache()
