@@ -4,6 +4,7 @@ than the engine's test models use (odd widths, head sizes in steps of 16, groups
 import math
 import os
 
+import numpy as np
 import pytest
 import torch
 
@@ -361,6 +362,29 @@ def test_attention_kernels_over_long_contexts(page):
     got, want, vs = paged_case([1, 1, 1], [9000, 70, 4097], 6, 2, 128, page, torch.bfloat16,
                                seed=4, spike=(0, 8000), kernel="decode")
     assert (got - want).abs().max() < 2e-2
+    assert tc_clean() == 0
+
+
+def test_attention_kernels_on_cases_drawn_at_random():
+    """Heads and groups, head sizes, page sizes (8 to 256), numbers of requests and their lengths
+    drawn at random (a fixed seed): whole prompts, portions behind cached keys and single
+    decoded tokens, against the plain attention; no bounded wait may run out."""
+    from mstar_b200 import ops
+
+    rng = np.random.default_rng(5)
+    shapes = [(24, 8, 128), (6, 2, 128), (5, 1, 128), (4, 4, 128), (14, 2, 64), (32, 8, 64),
+              (9, 1, 64), (4, 2, 256), (3, 3, 256), (12, 1, 128)]
+    for trial in range(60):
+        nq, nkv, hd = shapes[int(rng.integers(len(shapes)))]
+        page = int(rng.choice([8, 16, 32, 64, 128, 256]))
+        n_req = int(rng.integers(1, 6))
+        lens_kv = [int(rng.integers(1, 700 if hd < 256 else 300)) for _ in range(n_req)]
+        kind = "prefill" if trial % 2 == 0 else "decode"
+        lens_q = [int(rng.integers(1, kv + 1)) for kv in lens_kv] if kind == "prefill" else [1] * n_req
+        got, want, _ = paged_case(lens_q, lens_kv, nq, nkv, hd, page, torch.bfloat16, seed=trial,
+                                  kernel=kind)
+        err = (got - want).abs().max().item()
+        assert err < 2e-2, (trial, kind, nq, nkv, hd, page, lens_q, lens_kv, err)
     assert tc_clean() == 0
 
 
