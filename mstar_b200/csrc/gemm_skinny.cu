@@ -19,8 +19,16 @@
 // was built (partial tiles exchanged through scratch memory, summed in fixed order by the
 // CTA that arrives last at a counter) and measured at 64 rows: 17 to 22 us for the
 // attention and feed-forward projections of a 3072-wide model against 7 to 14 us of the
-// library GEMM, each extra slice costing about 5 us, so those stay with the library and
-// this kernel keeps one slice.
+// library GEMM, each extra slice costing about 5 us.  A second form cut K over the CTAs of a
+// thread-block cluster (each CTA its share of the k-blocks of one tile, its float partial
+// tile left in its own shared memory, every CTA adding up one share of the elements from all
+// of them through distributed shared memory, in rank order, 16 bytes a load): right in every
+// test and as fast as the library's kernels when timed alone (64 rows: O 8.4 against 7.3 us,
+// down 14.0 against 14.2, QKV 11.1 against 8.5), but a decode step of 64 requests took 4.49
+// instead of 4.28 ms with it.  A CTA with an SM to itself and a ring of 96 KB moves 64 GB/s;
+// twice the ring shuts the next kernel's CTAs out of the SM, and with them the overlap of
+// its weight copies with this kernel's end.  So those stay with the library and this kernel
+// keeps one slice.
 //
 // Every mbarrier wait is bounded and reports into an error word.  No cluster, no multicast.
 // The reference uses the library GEMM for every linear layer
